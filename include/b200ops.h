@@ -1,0 +1,185 @@
+/*
+ * b200ops.h -- C ABI of libb200ops.so: hand-written sm_100a CUDA kernels for the aten
+ * lowering hot path of torch-mojo-backend (torch.compile(backend=mojo_backend)).
+ *
+ * Contract shared by every entry point (it mirrors the contract of the reference's native
+ * bridges, torch_mojo_backend/eager_kernels/bf16_matmul_ops.mojo:1-8,25-63 and
+ * torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:1-6,20-61):
+ *   - arguments are raw device pointers (storage offset already applied), sizes and strides
+ *     in ELEMENTS, dtype enums, scalars, and the CUDA stream to enqueue on;
+ *   - the caller owns every buffer, outputs and workspace included; nothing is allocated,
+ *     nothing is synchronised and no tensor data is read on the host;
+ *   - all validation happens before the first launch, so a failing call leaves no partial work;
+ *   - the return value is B200_OK (0) or a negative status; no C++ exception crosses the ABI;
+ *   - device-side waits are bounded: a kernel that gives up sets a bit in a per-device status
+ *     word that b200_device_status() reads back.
+ */
+#ifndef B200OPS_H_
+#define B200OPS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+#define B200_ABI_VERSION 1
+
+/* status codes */
+#define B200_OK 0
+#define B200_ERR_INVALID_ARG (-1)   /* null pointer, negative size, bad enum */
+#define B200_ERR_UNSUPPORTED (-2)   /* valid request that no kernel covers (dtype mix, head_dim...) */
+#define B200_ERR_ALIGNMENT (-3)     /* pointer or stride not aligned as the chosen route needs */
+#define B200_ERR_WORKSPACE (-4)     /* workspace missing or too small */
+#define B200_ERR_CUDA (-5)          /* a CUDA runtime/driver call failed; see b200_last_error() */
+#define B200_ERR_DEVICE_TIMEOUT (-6)/* a bounded device-side wait gave up (b200_device_status) */
+
+/* element types */
+#define B200_F32 0
+#define B200_BF16 1
+
+/* reductions for b200_reduce_lastdim */
+#define B200_REDUCE_SUM 0
+#define B200_REDUCE_MEAN 1
+#define B200_REDUCE_AMAX 2
+
+/* GEMM epilogue activation */
+#define B200_EPILOGUE_NONE 0
+#define B200_EPILOGUE_GELU_TANH 1
+#define B200_EPILOGUE_GELU_ERF 2
+
+/* kernel routes (args.route: request; b200_*_route(): answer) */
+#define B200_ROUTE_AUTO 0
+#define B200_ROUTE_SIMT 1     /* generic strided CUDA-core kernel, any layout */
+#define B200_ROUTE_TCGEN05 2  /* TMA-fed tcgen05/TMEM tensor-core kernel */
+#define B200_ROUTE_SKINNY 3   /* small-M (decode) GEMM: weight-streaming, HBM bound */
+
+typedef void* b200_stream_t; /* cudaStream_t */
+
+/* ---- library ------------------------------------------------------------------------ */
+
+/* Replaces: the import-time handshake of the reference's lazily loaded CPython kernel
+ * modules (torch_mojo_backend/eager_kernels/aten_fast.py:4495-4534). */
+B200_API int32_t b200_abi_version(void);
+B200_API const char* b200_status_string(int32_t status);
+/* Thread-local detail text of the last non-OK status returned on this thread. */
+B200_API const char* b200_last_error(void);
+/* Reads (and clears) the current device's status word; *word == 0 means no kernel gave up.
+ * Synchronises the device: test/debug use only. */
+B200_API int32_t b200_device_status(uint32_t* word);
+
+/* ---- row kernels (HBM bound) -------------------------------------------------------- */
+
+/* LayerNorm over the last dim of x[rows, cols] (row stride x_row_stride, unit column
+ * stride). y is contiguous [rows, cols]; mean/rstd (fp32 [rows]) may be NULL; gamma/beta may
+ * be NULL. Two-pass centred variance in fp32, rstd = 1/sqrt(var + eps).
+ * Replaces: aten_native_layer_norm (torch_mojo_backend/aten_functions.py:2828-2868) and
+ * LayerNorm / _layer_norm_block_kernel (torch_mojo_backend/eager_kernels/nn_ops.mojo:208-326). */
+B200_API int32_t b200_layer_norm(const void* x, const void* gamma, const void* beta, void* y,
+                        float* mean, float* rstd, int64_t rows, int64_t cols,
+                        int64_t x_row_stride, float eps, int32_t in_dtype,
+                        int32_t param_dtype, int32_t out_dtype, b200_stream_t stream);
+
+/* Row softmax of x[rows, cols] * scale along the last dim, optionally causal: with
+ * causal != 0, row r attends to columns j <= r % q_len (top-left aligned) and masked
+ * columns are written as exact 0.
+ * Replaces: aten__softmax / aten_softmax (torch_mojo_backend/aten_functions.py:680-714) and
+ * SoftmaxRows (torch_mojo_backend/eager_kernels/nn_ops.mojo:385-493). */
+B200_API int32_t b200_softmax_lastdim(const void* x, void* y, int64_t rows, int64_t cols,
+                             int64_t x_row_stride, float scale, int32_t causal, int64_t q_len,
+                             int32_t in_dtype, int32_t out_dtype, b200_stream_t stream);
+
+/* Elementwise GELU over numel contiguous elements; approximate_tanh selects the tanh form.
+ * Replaces: aten_gelu (torch_mojo_backend/aten_functions.py:2062-2067) and
+ * _gelu_forward_bf16_{exact,tanh}
+ * (torch_mojo_backend/eager_kernels/activation_forward_kernels.mojo:22-56,137-154). */
+B200_API int32_t b200_gelu(const void* x, void* y, int64_t numel, int32_t approximate_tanh,
+                  int32_t dtype, b200_stream_t stream);
+
+/* sum / mean / amax over the last dim of x[rows, cols] -> y[rows]; fp32 accumulation.
+ * Replaces: aten_sum / aten_mean / aten_amax
+ * (torch_mojo_backend/aten_functions.py:3310-3346, 2554-2603, 1001-1020) and
+ * _reduce_block_kernel (torch_mojo_backend/eager_kernels/reduction_ops.mojo:161-263). */
+B200_API int32_t b200_reduce_lastdim(const void* x, void* y, int64_t rows, int64_t cols,
+                            int64_t x_row_stride, int32_t op, int32_t in_dtype,
+                            int32_t out_dtype, b200_stream_t stream);
+
+/* ---- GEMM ---------------------------------------------------------------------------- */
+
+/* C[b] = act(alpha * A[b] @ B[b] + beta * bias) + residual, fp32 accumulation.
+ * A is [m,k], B is [k,n], both with arbitrary element strides (a transposed view is just a
+ * stride pair); C is [m,n] with unit column stride. bias is NULL, a 1-D [n] row
+ * (bias_row_stride == 0) or a 2-D [m,n] matrix; residual is NULL or [m,n].
+ * Replaces: aten_mm / aten_addmm / aten_bmm
+ * (torch_mojo_backend/aten_functions.py:2631-2634, 970-992, 1414-1428) and the eager GEMM
+ * bridges Bf16GemmBF16 / MatmulBiasSpec
+ * (torch_mojo_backend/eager_kernels/bf16_matmul_ops.mojo:66-188,
+ *  torch_mojo_backend/eager_kernels/matmul_ops.mojo:3500). */
+typedef struct b200_gemm_args {
+  const void* a;
+  const void* b;
+  const void* bias;
+  const void* residual;
+  void* c;
+  int64_t m, n, k, batch;
+  int64_t a_row_stride, a_col_stride, a_batch_stride;
+  int64_t b_row_stride, b_col_stride, b_batch_stride;
+  int64_t c_row_stride, c_batch_stride;
+  int64_t bias_row_stride;     /* 0: bias is a [n] row broadcast over m */
+  int64_t residual_row_stride;
+  float alpha, beta;
+  int32_t in_dtype;            /* dtype of A and B */
+  int32_t bias_dtype;
+  int32_t residual_dtype;
+  int32_t out_dtype;
+  int32_t epilogue;            /* B200_EPILOGUE_* */
+  int32_t route;               /* B200_ROUTE_AUTO or a forced route */
+} b200_gemm_args;
+
+/* The route B200_ROUTE_AUTO resolves to for these arguments (no launch), or a negative status. */
+B200_API int32_t b200_gemm_route(const b200_gemm_args* args);
+/* Bytes of workspace the resolved route needs (0 for most routes). */
+B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_args* args);
+B200_API int32_t b200_gemm(const b200_gemm_args* args, void* workspace, size_t workspace_bytes,
+                  b200_stream_t stream);
+
+/* ---- attention ----------------------------------------------------------------------- */
+
+/* softmax(scale * Q K^T [+ causal mask]) V per (batch, head); fp32 online softmax; writes
+ * O (same dtype as Q) and, when lse != NULL, the natural-log LSE as fp32 [batch, heads, q_len].
+ * Strides are in elements for the (batch, head, position) dims; head_dim is contiguous.
+ * The causal mask is top-left aligned.
+ * Replaces: aten__scaled_dot_product_flash_attention
+ * (torch_mojo_backend/aten_functions.py:539-677) and the FA4 bridge
+ * (torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:20-61,480-498). */
+typedef struct b200_sdpa_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;
+  int64_t batch, heads, q_len, kv_len, head_dim;
+  int64_t q_strides[3]; /* batch, head, position */
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t o_strides[3];
+  float scale;
+  int32_t causal;
+  int32_t dtype;
+  int32_t route; /* B200_ROUTE_AUTO / SIMT / TCGEN05 */
+} b200_sdpa_args;
+
+B200_API int32_t b200_sdpa_route(const b200_sdpa_args* args);
+B200_API int32_t b200_sdpa_fwd(const b200_sdpa_args* args, b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200OPS_H_ */

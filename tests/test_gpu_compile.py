@@ -1,0 +1,134 @@
+"""torch.compile(backend=mojo_backend) end to end on the GPU, against PyTorch CPU eager."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+from conftest import assert_parity
+
+from oracle import ref_ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tmb():
+    import torch_mojo_backend
+
+    return torch_mojo_backend
+
+
+def run_compiled(tmb, fn, *inputs):
+    torch._dynamo.reset()
+    compiled = torch.compile(fn, backend=tmb.mojo_backend)
+    with torch.no_grad():
+        return compiled(*[i.cuda() for i in inputs])
+
+
+def test_layer_norm_gelu_softmax_chain(tmb, call_checker):
+    from torch_mojo_backend import aten_functions as af
+
+    call_checker.register(af.aten_native_layer_norm)
+
+    def fn(x, w, b, m):
+        h = F.layer_norm(x, (64,), w, b, 1e-5)
+        h = F.gelu(h @ m, approximate="tanh")
+        return torch.softmax(h, -1), h.sum(-1), h.mean(0), h.amax(1, keepdim=True)
+
+    g = torch.Generator().manual_seed(0)
+    x, w, b, m = (torch.randn(s, generator=g) for s in ((48, 64), (64,), (64,), (64, 40)))
+    outs = run_compiled(tmb, fn, x, w, b, m)
+    for got, want in zip(outs, fn(x, w, b, m)):
+        assert got.is_cuda
+        assert_parity(got, want, bf16=False)
+
+
+def test_addmm_alpha_beta_and_bmm(tmb, call_checker):
+    from torch_mojo_backend import aten_functions as af
+
+    call_checker.register(af.aten_addmm)
+
+    def fn(bias, a, b, p, q):
+        return torch.addmm(bias, a, b, beta=0.5, alpha=2.0), torch.bmm(p, q)
+
+    g = torch.Generator().manual_seed(1)
+    args = [torch.randn(s, generator=g) for s in ((65,), (33, 31), (31, 65), (3, 5, 7), (3, 7, 4))]
+    for got, want in zip(run_compiled(tmb, fn, *args), fn(*args)):
+        assert_parity(got, want, bf16=False)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sdpa_is_causal_reaches_the_kernel(tmb, dtype):
+    def fn(q, k, v):
+        return F.scaled_dot_product_attention(q, k, v, is_causal=True)
+
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn((2, 4, 128, 64), generator=g).to(dtype) for _ in range(3))
+    from torch_mojo_backend import native
+
+    before = native.launch_count
+    got = run_compiled(tmb, fn, q, k, v)
+    assert native.launch_count > before, "no b200 kernel was launched"
+    want = ref_ops.sdpa(q, k, v, True)[0]
+    assert_parity(got, want, bf16=dtype == torch.bfloat16)
+
+
+@pytest.mark.parametrize("attention", ["sdpa", "masked_softmax"])
+def test_gpt2_tiny_golden(tmb, golden, attention):
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+
+    cfg = GPTConfig(vocab_size=211, block_size=32, n_layer=2, n_head=4, n_embd=64)
+    model = GPT2(cfg, attention).init_weights(0).eval().cuda()
+    ids = torch.from_numpy(golden["gpt_ids"])
+    logits = run_compiled(tmb, model, ids)
+    assert_parity(logits, torch.from_numpy(golden[f"gpt_logits_{attention}"]), bf16=False)
+
+
+def test_gpt2_small_fp32_config(tmb):
+    """GPT-2 small, fp32, batch 1 x 128 tokens, seed-0 weights: logits within 1e-4 of CPU eager."""
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+
+    model = GPT2(GPTConfig.small()).init_weights(0).eval()
+    ids = torch.randint(0, 50257, (1, 128), generator=torch.Generator().manual_seed(0))
+    want = ref_ops.gpt2_logits_fp32(model, ids)
+    got = run_compiled(tmb, model.cuda(), ids)
+    assert got.shape == (1, 128, 50257) and got.dtype == torch.float32
+    assert_parity(got, want, bf16=False)
+    assert (got.argmax(-1).cpu() == want.argmax(-1)).float().mean().item() == 1.0
+
+
+def test_gpt2_small_bf16_policy_top1(tmb):
+    """bf16 operands with fp32 accumulation on 8 x 1024 tokens: within 2e-2 (allclose form) of the
+    fp32 oracle that shares the bf16-rounded weights, and >= 99 % top-1 agreement."""
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+
+    model = GPT2(GPTConfig.small()).init_weights(0).eval().set_precision("bf16")
+    ids = torch.randint(0, 50257, (8, 1024), generator=torch.Generator().manual_seed(0))
+    want = ref_ops.gpt2_logits_fp32(model, ids)
+    got = run_compiled(tmb, model.cuda(), ids).cpu()
+    assert_parity(got, want, bf16=True)
+    top1 = (got.argmax(-1) == want.argmax(-1)).float().mean().item()
+    rel_l2 = ((got - want).norm() / want.norm()).item()
+    print(f"bf16 policy: top-1 agreement {top1:.4f}, rel-L2 {rel_l2:.3e}")
+    assert top1 >= 0.99
+
+
+def test_cuda_graph_replay_matches_eager_plan(tmb, monkeypatch):
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+
+    cfg = GPTConfig(vocab_size=211, block_size=32, n_layer=2, n_head=4, n_embd=64)
+    model = GPT2(cfg).init_weights(0).eval().cuda()
+    ids = torch.randint(0, 211, (2, 16), generator=torch.Generator().manual_seed(3)).cuda()
+    eager = run_compiled(tmb, model, ids).clone()
+    monkeypatch.setenv("TORCH_MOJO_BACKEND_CUDA_GRAPHS", "1")
+    torch._dynamo.reset()
+    compiled = torch.compile(model, backend=tmb.mojo_backend)
+    with torch.no_grad():
+        for i in range(4):  # call 1 eager, call 2 captures, calls 3-4 replay with fresh input buffers
+            out = compiled(ids.clone())
+            assert torch.equal(out, eager), f"call {i}"
+
+
+def test_no_device_timeout_recorded():
+    from torch_mojo_backend import native
+
+    assert native.device_status() == 0

@@ -1,0 +1,175 @@
+"""GPU parity of mm / addmm / bmm: every route of b200_gemm against the CPU oracle."""
+
+import pytest
+import torch
+from conftest import assert_parity
+
+from oracle import ref_ops
+
+pytestmark = pytest.mark.gpu
+
+ROUTE_AUTO, ROUTE_SIMT, ROUTE_TC = 0, 1, 2
+
+
+def gen(shape, dtype, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from torch_mojo_backend import ops as _ops
+
+    return _ops
+
+
+def cpu_gemm(a, b, bias=None, alpha=1.0, beta=1.0, out_dtype=None):
+    """fp32 CPU matmul of the stored (possibly bf16-rounded) values: the oracle for big shapes."""
+    y = alpha * (a.float() @ b.float())
+    if bias is not None:
+        y = y + beta * bias.float()
+    return y.to(out_dtype or a.dtype)
+
+
+# ---- exact-fp32 route ------------------------------------------------------------------------
+def test_simt_golden_odd_shape(ops, golden):
+    a, b, bias = (torch.from_numpy(golden[k]).cuda() for k in ("mm_a", "mm_b", "mm_bias"))
+    assert_parity(ops.gemm(a, b), torch.from_numpy(golden["mm_y"]), bf16=False)
+    y = ops.gemm(a, b, bias, None, 2.0, 0.5)
+    assert_parity(y, torch.from_numpy(golden["addmm_y"]), bf16=False)
+    yb = ops.gemm(torch.from_numpy(golden["bmm_a"]).cuda(), torch.from_numpy(golden["bmm_b"]).cuda())
+    assert_parity(yb, torch.from_numpy(golden["bmm_y"]), bf16=False)
+
+
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+def test_simt_fp32_layouts(ops, ta, tb):
+    m, n, k = 257, 130, 75
+    a = gen((k, m) if ta else (m, k), torch.float32, 1)
+    b = gen((n, k) if tb else (k, n), torch.float32, 2)
+    a_cpu, a_gpu = (a.t(), a.cuda().t()) if ta else (a, a.cuda())
+    b_cpu, b_gpu = (b.t(), b.cuda().t()) if tb else (b, b.cuda())
+    assert_parity(ops.gemm(a_gpu, b_gpu), ref_ops.mm(a_cpu, b_cpu), bf16=False)
+
+
+def test_simt_fp32_gpt2_shape_and_2d_bias(ops):
+    a, b = gen((128, 768), torch.float32, 3), gen((768, 2304), torch.float32, 4, 0.02)
+    bias = gen((2304,), torch.float32, 5, 0.02)
+    assert_parity(ops.gemm(a.cuda(), b.cuda(), bias.cuda()), ref_ops.addmm(bias, a, b), bf16=False)
+    bias2 = gen((128, 2304), torch.float32, 6)
+    assert_parity(ops.gemm(a.cuda(), b.cuda(), bias2.cuda()), ref_ops.addmm(bias2, a, b), bf16=False)
+    col = gen((128, 1), torch.float32, 7)
+    assert_parity(ops.gemm(a.cuda(), b.cuda(), col.cuda()), ref_ops.addmm(col, a, b), bf16=False)
+
+
+def test_simt_degenerate(ops):
+    a = torch.empty((0, 8), device="cuda")
+    b = torch.randn((8, 5), device="cuda")
+    assert ops.gemm(a, b).shape == (0, 5)
+    z = ops.gemm(torch.randn((4, 0), device="cuda"), torch.randn((0, 5), device="cuda"))
+    assert torch.equal(z.cpu(), torch.zeros(4, 5))  # k == 0: empty sum
+    one = ops.gemm(torch.full((1, 1), 3.0, device="cuda"), torch.full((1, 1), 4.0, device="cuda"))
+    assert one.item() == 12.0
+
+
+def test_simt_bf16_forced(ops):
+    a, b = gen((100, 72), torch.bfloat16, 8), gen((72, 90), torch.bfloat16, 9)
+    y = ops.gemm(a.cuda(), b.cuda(), None, None, 1.0, 1.0, 0, None, ROUTE_SIMT)
+    assert_parity(y, cpu_gemm(a, b), bf16=True)
+
+
+# ---- tensor-core route -----------------------------------------------------------------------
+KN = [(768, 2304), (768, 768), (768, 3072), (3072, 768)]
+
+
+@pytest.mark.parametrize("k,n", KN)
+@pytest.mark.parametrize("b_layout", ["nk", "kn"])
+def test_tcgen05_addmm_m8192(ops, k, n, b_layout):
+    """M = 8192 GPT-2 shapes, both weight layouts: contiguous [K, N] (HF Conv1D) and the t() view
+    of a contiguous [N, K] (nn.Linear)."""
+    m = 8192
+    a = gen((m, k), torch.bfloat16, 10)
+    bias = gen((n,), torch.bfloat16, 12, 0.02)
+    if b_layout == "nk":
+        w = gen((n, k), torch.bfloat16, 11)
+        b_cpu, b_gpu = w.t(), w.cuda().t()
+    else:
+        b_cpu = gen((k, n), torch.bfloat16, 11)
+        b_gpu = b_cpu.cuda()
+    y = ops.gemm(a.cuda(), b_gpu, bias.cuda(), None, 1.0, 1.0, 0, None, ROUTE_TC)
+    want = cpu_gemm(a, b_cpu, bias)
+    # reference's bf16 GEMM bar: atol 0.03125, rtol 0.02 on N(0,1) operands (tests/test_eager_kernels.py:5126-5129)
+    torch.testing.assert_close(y.cpu(), want, atol=0.03125 * (k / 192) ** 0.5, rtol=0.02)
+    y32 = ops.gemm(a.cuda(), b_gpu, bias.cuda(), None, 1.0, 1.0, 0, torch.float32, ROUTE_TC)
+    assert y32.dtype == torch.float32
+    assert_parity(y32, cpu_gemm(a, b_cpu, bias, out_dtype=torch.float32), bf16=False, scale=k**0.5 * 4)
+
+
+@pytest.mark.parametrize("m,n,k", [(1000, 50257, 768), (129, 200, 72), (33, 72, 200), (128, 256, 64), (300, 1000, 1600)])
+def test_tcgen05_ragged(ops, m, n, k):
+    a = gen((m, k), torch.bfloat16, 13)
+    w = gen((n, k), torch.bfloat16, 14)
+    y = ops.gemm(a.cuda(), w.cuda().t(), None, None, 1.0, 1.0, 0, torch.float32, ROUTE_TC)
+    assert_parity(y, cpu_gemm(a, w.t(), out_dtype=torch.float32), bf16=False, scale=k**0.5 * 4)
+
+
+def test_tcgen05_epilogues(ops):
+    m, n, k = 512, 640, 256
+    a, w = gen((m, k), torch.bfloat16, 15, 0.5), gen((n, k), torch.bfloat16, 16, 0.1)
+    bias = gen((n,), torch.float32, 17)
+    res = gen((m, n), torch.float32, 18)
+    acc = a.float() @ w.float().t()
+    y = ops.gemm(a.cuda(), w.cuda().t(), bias.cuda(), res.cuda(), 0.5, 2.0, 1, torch.float32, ROUTE_TC)
+    want = torch.nn.functional.gelu(0.5 * acc + 2.0 * bias, approximate="tanh") + res
+    assert_parity(y, want, bf16=False)
+    y2 = ops.gemm(a.cuda(), w.cuda().t(), bias.cuda(), None, 1.0, 1.0, 2, torch.bfloat16, ROUTE_TC)
+    assert_parity(y2, torch.nn.functional.gelu(acc + bias), bf16=True)
+    bias2 = gen((m, n), torch.bfloat16, 19)
+    y3 = ops.gemm(a.cuda(), w.cuda().t(), bias2.cuda(), None, 1.0, 1.0, 0, None, ROUTE_TC)
+    assert_parity(y3, acc + bias2.float(), bf16=True)
+
+
+@pytest.mark.parametrize("shape", [((12, 128, 64), (12, 64, 128), True), ((12, 128, 128), (12, 128, 64), False),
+                                   ((5, 200, 72), (5, 72, 136), False)])
+def test_tcgen05_bmm(ops, shape):
+    """bmm shapes of the decomposed attention: Q K^T (B as a transposed view) and P V."""
+    sa, sb, b_transposed = shape
+    a = gen(sa, torch.bfloat16, 20)
+    if b_transposed:
+        bt = gen((sb[0], sb[2], sb[1]), torch.bfloat16, 21)
+        b_cpu, b_gpu = bt.transpose(1, 2), bt.cuda().transpose(1, 2)
+    else:
+        b_cpu = gen(sb, torch.bfloat16, 21)
+        b_gpu = b_cpu.cuda()
+    y = ops.gemm(a.cuda(), b_gpu, None, None, 1.0, 1.0, 0, torch.float32, ROUTE_TC)
+    assert_parity(y, torch.bmm(a.float(), b_cpu.float()), bf16=False, scale=sa[2] ** 0.5 * 4)
+
+
+def test_auto_route_choices(ops):
+    import ctypes
+
+    from torch_mojo_backend import native
+
+    def route(a, b):
+        c = torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device="cuda")
+        g = ops.fill_gemm_args(a, b, None, None, c, 1.0, 1.0, 0, 0)
+        return native.lib().b200_gemm_route(ctypes.byref(g))
+
+    bf = torch.bfloat16
+    assert route(torch.empty((256, 64), dtype=bf, device="cuda"), torch.empty((64, 256), dtype=bf, device="cuda")) == ROUTE_TC
+    assert route(torch.empty((256, 64), device="cuda"), torch.empty((64, 256), device="cuda")) == ROUTE_SIMT
+    # K-contiguity / 16-byte pitch rules of the TMA route
+    assert route(torch.empty((256, 60), dtype=bf, device="cuda"), torch.empty((60, 256), dtype=bf, device="cuda")) == ROUTE_SIMT
+    assert route(torch.empty((64, 256), dtype=bf, device="cuda").t(), torch.empty((64, 256), dtype=bf, device="cuda")) == ROUTE_SIMT
+
+
+def test_forced_route_refused_loudly(ops):
+    a, b = torch.randn((8, 8), device="cuda"), torch.randn((8, 8), device="cuda")
+    with pytest.raises(RuntimeError, match="tcgen05 route refused"):
+        ops.gemm(a, b, None, None, 1.0, 1.0, 0, None, ROUTE_TC)
+
+
+def test_no_device_timeout_recorded():
+    from torch_mojo_backend import native
+
+    assert native.device_status() == 0

@@ -1,0 +1,18 @@
+// Internal interfaces between the GEMM router (gemm.cu) and its kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+int32_t launch_gemm_simt(const b200_gemm_args& g, cudaStream_t stream);
+
+// Why the TMA/tcgen05 kernel cannot take these arguments, or nullptr when it can.
+const char* gemm_tcgen05_ineligible(const b200_gemm_args& g);
+int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream);
+
+// Small-M weight-streaming kernel (decode shapes).
+const char* gemm_skinny_ineligible(const b200_gemm_args& g);
+int32_t launch_gemm_skinny(const b200_gemm_args& g, cudaStream_t stream);
+
+}  // namespace b200

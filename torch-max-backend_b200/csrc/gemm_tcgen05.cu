@@ -1,0 +1,391 @@
+// bf16 GEMM on the 5th-generation tensor cores: TMA-fed shared-memory ring, tcgen05.mma with
+// fp32 accumulators in TMEM, persistent CTAs, warp-specialised roles.
+//
+//   warp 0      TMA producer: one lane streams 128xBK A tiles and BNxBK B tiles into a
+//               STAGES-deep ring (128-byte swizzle), signalling `full[s]` by transaction bytes.
+//   warp 1      MMA issuer: one lane waits `full[s]`, issues BK/16 tcgen05.mma (128 x BN x 16)
+//               per stage into one of two TMEM accumulators, and commits to `empty[s]`; after
+//               the last k-block it commits to `tmem_full[acc]`.
+//   warps 2-5   epilogue: wait `tmem_full[acc]`, pull the accumulator out of TMEM 32 columns at
+//               a time, apply alpha/bias/activation/residual, convert and store, then release the
+//               accumulator through `tmem_empty[acc]`. The two accumulators let the epilogue of
+//               tile i overlap the main loop of tile i+1.
+//
+// Tiles are walked M-fastest so that the CTAs running at any moment share a few B tiles in L2.
+// Every wait is bounded (ptx::mbar_wait); a CTA that gives up raises the device status word and
+// leaves through the common teardown, which frees its TMEM.
+#include "gemm_internal.cuh"
+#include "ptx.cuh"
+#include "tma.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators; 256 or 512 (powers of two)
+  static constexpr int kSmemA = 0;
+  static constexpr int kSmemB = kStages * A_STAGE_BYTES;
+  static constexpr int kSmemBar = kSmemB + kStages * B_STAGE_BYTES;
+  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kSmemMisc = kSmemBar + kNumBars * 8;
+  static constexpr int kSmemBytes = kSmemMisc + 16 + 1024;  // +1024: manual 1 KiB alignment
+};
+
+struct Params {
+  int64_t M, N, K, batch;
+  int64_t c_rs, c_bs;
+  const void* bias;
+  const void* residual;
+  int64_t bias_rs, residual_rs;
+  float alpha, beta;
+  int32_t bias_dtype, residual_dtype, epilogue;
+  int32_t tiles_m, tiles_n;
+  int64_t num_tiles;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float ld_param(const void* p, int64_t idx, int32_t dtype) {
+  return dtype == B200_F32 ? __ldg(static_cast<const float*>(p) + idx)
+                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+}
+
+__device__ __forceinline__ float act(float v, int32_t epilogue) {
+  if (epilogue == B200_EPILOGUE_GELU_TANH) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    const float u = k0 * (v + k1 * v * v * v);
+    return v / (1.0f + __expf(-2.0f * u));
+  }
+  if (epilogue == B200_EPILOGUE_GELU_ERF) return gelu_erf_f32(v);
+  return v;
+}
+
+__device__ __forceinline__ void store_chunk(float* dst, const float (&v)[32], int valid) {
+  if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid) dst[i] = v[i];
+  }
+}
+
+__device__ __forceinline__ void store_chunk(__nv_bfloat16* dst, const float (&v)[32], int valid) {
+  if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 t;
+      t.x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
+      t.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+      t.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+      t.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+      reinterpret_cast<uint4*>(dst)[i] = t;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+template <int BN, bool B_MN_MAJOR, typename Tout>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, Tout* __restrict__ C, Params p) {
+  using C_ = Cfg<BN>;
+  constexpr int kStages = C_::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled operand tiles need a 1 KiB aligned base.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t a_base = smem_base + C_::kSmemA;
+  const uint32_t b_base = smem_base + C_::kSmemB;
+  const uint32_t bar_base = smem_base + C_::kSmemBar;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + C_::kSmemMisc);
+  volatile uint32_t* tmem_holder = misc;      // TMEM base address written by tcgen05.alloc
+  volatile uint32_t* abort_flag = misc + 1;   // set by any thread whose bounded wait ran out
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tmem_full_bar(a), 1);
+      ptx::mbar_init(tmem_empty_bar(a), kEpilogueThreads);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), C_::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int64_t num_kb = (p.K + BK - 1) / BK;
+  const int64_t tiles_per_batch = (int64_t)p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const int64_t b = t / tiles_per_batch;
+        const int64_t r = t - b * tiles_per_batch;
+        const int32_t m0 = (int32_t)(r % p.tiles_m) * BM;
+        const int32_t n0 = (int32_t)(r / p.tiles_m) * BN;
+        for (int64_t kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + C_::B_STAGE_BYTES);
+          const int32_t k0 = (int32_t)(kb * BK);
+          ptx::tma_load_3d(a_base + s * A_STAGE_BYTES, &tmap_a, full_bar(s), k0, m0, (int32_t)b);
+          if (!B_MN_MAJOR) {
+            ptx::tma_load_3d(b_base + s * C_::B_STAGE_BYTES, &tmap_b, full_bar(s), k0, n0, (int32_t)b);
+          } else {
+            // B stored [K, N]: BN/64 boxes of 64(n) x 64(k), each one swizzle atom wide in n.
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_3d(b_base + s * C_::B_STAGE_BYTES + j * (64 * BK * 2), &tmap_b,
+                               full_bar(s), n0 + j * 64, k0, (int32_t)b);
+          }
+          if (++s == kStages) { s = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(BM, BN, 0, B_MN_MAJOR ? 1 : 0);
+      int s = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int64_t kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(full_bar(s), phase, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = a_base + s * A_STAGE_BYTES;
+          const uint32_t b_addr = b_base + s * C_::B_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = ptx::smem_desc_sw128(a_addr + k * (UMMA_K * 2), 0, 1024);
+            const uint64_t b_desc =
+                B_MN_MAJOR ? ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                           : ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 2), 0, 1024);
+            ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(empty_bar(s));  // frees the smem slot when these MMAs have read it
+          if (++s == kStages) { s = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        ptx::tc_commit(tmem_full_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int64_t t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      const int64_t b = t / tiles_per_batch;
+      const int64_t r = t - b * tiles_per_batch;
+      const int64_t m0 = (r % p.tiles_m) * BM;
+      const int64_t n0 = (r / p.tiles_m) * BN;
+      if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
+      ptx::tc_fence_after_sync();
+      const int64_t row = m0 + q * 32 + lane;
+      Tout* crow = C + b * p.c_bs + row * p.c_rs;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int64_t col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t raw[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + c * 32) + ((uint32_t)(q * 32) << 16), raw);
+        ptx::tmem_ld_wait();
+        const int64_t rem = p.N - col0;
+        const int valid = rem >= 32 ? 32 : (int)rem;
+        if (row < p.M) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = p.alpha * __uint_as_float(raw[i]);
+          if (p.bias != nullptr) {
+            // bias_rs == 0: a [n] row, the same address in every lane (one broadcast transaction)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) v[i] += p.beta * ld_param(p.bias, row * p.bias_rs + col0 + i, p.bias_dtype);
+          }
+          if (p.epilogue != B200_EPILOGUE_NONE) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = act(v[i], p.epilogue);
+          }
+          if (p.residual != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) v[i] += ld_param(p.residual, row * p.residual_rs + col0 + i, p.residual_dtype);
+          }
+          store_chunk(crow + col0, v, valid);
+        }
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(tmem_empty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  __syncthreads();
+  if (*abort_flag != 0) {
+    if (threadIdx.x == 0) atomicOr(p.status, STATUS_GEMM_TIMEOUT);
+    // Let copies and MMAs that may still be in flight drain before TMEM and smem go away.
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, C_::kTmemCols);
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+
+bool b_is_k_major(const b200_gemm_args& g) { return g.b_row_stride == 1 && (g.b_col_stride != 1 || g.n == 1); }
+bool b_is_n_major(const b200_gemm_args& g) { return g.b_col_stride == 1; }
+
+template <int BN, bool B_MN_MAJOR, typename Tout>
+int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
+  using C_ = Cfg<BN>;
+  CUtensorMap tmap_a, tmap_b;
+  {
+    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch};
+    const uint64_t strides[2] = {(uint64_t)g.a_row_stride * 2,
+                                 (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_row_stride * g.m) * 2};
+    const uint32_t box[3] = {BK, BM, 1};
+    int32_t st = encode_tensor_map(&tmap_a, B200_BF16, 3, g.a, dims, strides, box, true);
+    if (st != B200_OK) return st;
+  }
+  if (!B_MN_MAJOR) {
+    // B^T is [n, k] with row pitch b_col_stride.
+    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.batch};
+    const uint64_t strides[2] = {(uint64_t)g.b_col_stride * 2,
+                                 (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_col_stride * g.n) * 2};
+    const uint32_t box[3] = {BK, BN, 1};
+    int32_t st = encode_tensor_map(&tmap_b, B200_BF16, 3, g.b, dims, strides, box, true);
+    if (st != B200_OK) return st;
+  } else {
+    // B is [k, n] with row pitch b_row_stride.
+    const uint64_t dims[3] = {(uint64_t)g.n, (uint64_t)g.k, (uint64_t)g.batch};
+    const uint64_t strides[2] = {(uint64_t)g.b_row_stride * 2,
+                                 (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_row_stride * g.k) * 2};
+    const uint32_t box[3] = {64, BK, 1};
+    int32_t st = encode_tensor_map(&tmap_b, B200_BF16, 3, g.b, dims, strides, box, true);
+    if (st != B200_OK) return st;
+  }
+  Params p;
+  p.M = g.m; p.N = g.n; p.K = g.k; p.batch = g.batch;
+  p.c_rs = g.c_row_stride; p.c_bs = g.c_batch_stride;
+  p.bias = g.bias; p.residual = g.residual;
+  p.bias_rs = g.bias_row_stride; p.residual_rs = g.residual_row_stride;
+  p.alpha = g.alpha; p.beta = g.beta;
+  p.bias_dtype = g.bias_dtype; p.residual_dtype = g.residual_dtype; p.epilogue = g.epilogue;
+  p.tiles_m = (int32_t)((g.m + BM - 1) / BM);
+  p.tiles_n = (int32_t)((g.n + BN - 1) / BN);
+  p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * g.batch;
+  p.status = device_status_ptr();
+  B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "gemm(tcgen05): device status word unavailable");
+
+  auto kernel = gemm_tcgen05_kernel<BN, B_MN_MAJOR, Tout>;
+  static thread_local bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes);
+    if (e != cudaSuccess)
+      B200_FAIL(B200_ERR_CUDA, "gemm(tcgen05): cannot opt in to %d bytes of shared memory: %s",
+                C_::kSmemBytes, cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  const int64_t grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kernel<<<(unsigned)grid, kThreads, C_::kSmemBytes, stream>>>(tmap_a, tmap_b, static_cast<Tout*>(g.c), p);
+  B200_CHECK_LAUNCH("gemm(tcgen05)");
+  return B200_OK;
+}
+
+// Wave-quantisation cost of a tile width: waves of CTAs times the per-tile cost (main loop
+// proportional to BN plus a fixed epilogue/prologue share).
+int pick_bn(const b200_gemm_args& g) {
+  if (g.n <= 128) return 128;
+  const int sms = sm_count();
+  auto cost = [&](int bn) {
+    const int64_t tiles = ((g.m + BM - 1) / BM) * ((g.n + bn - 1) / bn) * g.batch;
+    const int64_t waves = (tiles + sms - 1) / sms;
+    return (double)waves * (bn + 32);
+  };
+  return cost(256) <= cost(128) ? 256 : 128;
+}
+
+}  // namespace
+
+const char* gemm_tcgen05_ineligible(const b200_gemm_args& g) {
+  if (g.in_dtype != B200_BF16) return "operands are not bf16";
+  if (g.k <= 0) return "k is zero";
+  if (g.a_col_stride != 1) return "A is not K-contiguous";
+  if (!b_is_k_major(g) && !b_is_n_major(g)) return "B has no unit stride";
+  if (!aligned_to(g.a, 16) || !aligned_to(g.b, 16)) return "operand pointer not 16-byte aligned";
+  if (g.a_row_stride % 8 != 0 || g.a_row_stride < g.k) return "A row pitch not a multiple of 16 bytes";
+  if (g.batch > 1 && (g.a_batch_stride % 8 != 0 || g.b_batch_stride % 8 != 0))
+    return "batch stride not a multiple of 16 bytes";
+  if (b_is_n_major(g)) {
+    if (g.b_row_stride % 8 != 0 || g.b_row_stride < g.n) return "B row pitch not a multiple of 16 bytes";
+  } else {
+    if (g.b_col_stride % 8 != 0 || g.b_col_stride < g.k) return "B column pitch not a multiple of 16 bytes";
+  }
+  if (g.m > INT32_MAX - 256 || g.n > INT32_MAX - 256 || g.k > INT32_MAX - 256 || g.batch > INT32_MAX)
+    return "extent exceeds TMA coordinate range";
+  if ((g.bias != nullptr && g.bias_row_stride != 0 && g.batch > 1) || (g.residual != nullptr && g.batch > 1))
+    return "matrix bias/residual with batch > 1";
+  return nullptr;
+}
+
+int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream) {
+  const bool mn = !b_is_k_major(g);
+  const int bn = pick_bn(g);
+  const bool f32 = g.out_dtype == B200_F32;
+#define TC_LAUNCH(BN_, MN_)                                                   \
+  (f32 ? launch_cfg<BN_, MN_, float>(g, stream) : launch_cfg<BN_, MN_, __nv_bfloat16>(g, stream))
+  if (bn == 256) return mn ? TC_LAUNCH(256, true) : TC_LAUNCH(256, false);
+  return mn ? TC_LAUNCH(128, true) : TC_LAUNCH(128, false);
+#undef TC_LAUNCH
+}
+
+}  // namespace b200

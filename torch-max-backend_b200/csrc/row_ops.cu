@@ -1,0 +1,632 @@
+// Bandwidth-bound row kernels: LayerNorm, row softmax, GELU, trailing-dim reductions.
+//
+// Fast paths keep one row per warp in registers (one HBM read, one HBM write per element),
+// move data as 16-byte vectors and reduce with warp shuffles. Rows that do not fit the
+// register budget, or whose pointers/strides are not 16-byte friendly, take a CTA-per-row
+// kernel with scalar accesses.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kWarpsPerCta = 4;
+constexpr int kRowThreads = kWarpsPerCta * 32;
+
+// ---- chunk load/store: N consecutive elements of T <-> N fp32 lanes ----------------------
+template <typename T, int N>
+struct Chunk;
+
+template <>
+struct Chunk<float, 4> {
+  __device__ static void load(const float* p, float (&v)[4]) { load16_stream(p, v); }
+  __device__ static void load_keep(const float* p, float (&v)[4]) { load16(p, v); }
+  __device__ static void store(float* p, const float (&v)[4]) { store16_stream(p, v); }
+};
+
+template <>
+struct Chunk<float, 8> {
+  __device__ static void load(const float* p, float (&v)[8]) {
+    float a[4], b[4];
+    load16_stream(p, a);
+    load16_stream(p + 4, b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[i] = a[i]; v[4 + i] = b[i]; }
+  }
+  __device__ static void load_keep(const float* p, float (&v)[8]) {
+    float a[4], b[4];
+    load16(p, a);
+    load16(p + 4, b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[i] = a[i]; v[4 + i] = b[i]; }
+  }
+  __device__ static void store(float* p, const float (&v)[8]) {
+    float a[4] = {v[0], v[1], v[2], v[3]}, b[4] = {v[4], v[5], v[6], v[7]};
+    store16_stream(p, a);
+    store16_stream(p + 4, b);
+  }
+};
+
+template <>
+struct Chunk<__nv_bfloat16, 8> {
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) { load16_stream(p, v); }
+  __device__ static void load_keep(const __nv_bfloat16* p, float (&v)[8]) { load16(p, v); }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) { store16_stream(p, v); }
+};
+
+template <>
+struct Chunk<__nv_bfloat16, 4> {
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[4]) {
+    uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+  }
+  __device__ static void load_keep(const __nv_bfloat16* p, float (&v)[4]) {
+    uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[4]) {
+    uint2 t;
+    t.x = pack_bf16x2(v[0], v[1]);
+    t.y = pack_bf16x2(v[2], v[3]);
+    __stcs(reinterpret_cast<uint2*>(p), t);
+  }
+};
+
+// CTA-wide reductions for the generic kernels (blockDim.x <= 1024, a multiple of 32).
+__device__ float block_sum(float v, float* smem) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarp) ? smem[lane] : 0.0f;
+  return warp_sum(t);
+}
+
+__device__ float block_max(float v, float* smem) {
+  v = warp_max(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarp) ? smem[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+// =========================================================================================
+// LayerNorm
+// =========================================================================================
+
+// One warp per row; the row lives in registers between the three uses (mean, variance,
+// normalise). N = elements per chunk (16 bytes of Tin), MAXC = chunks per lane.
+template <typename Tin, typename Tp, typename Tout, int N, int MAXC>
+__global__ void __launch_bounds__(kRowThreads)
+layer_norm_warp_kernel(const Tin* __restrict__ x, const Tp* __restrict__ gamma,
+                       const Tp* __restrict__ beta, Tout* __restrict__ y,
+                       float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t rows,
+                       int cols, int64_t x_row_stride, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nchunks = cols / N;
+  const Tin* xr = x + row * x_row_stride;
+
+  float v[MAXC][N];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunks) {
+      Chunk<Tin, N>::load(xr + c * N, v[i]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) sum += v[i][j];
+    }
+  }
+  const float mean = warp_sum(sum) / (float)cols;
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunks) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        const float d = v[i][j] - mean;
+        sq += d * d;
+      }
+    }
+  }
+  const float var = warp_sum(sq) / (float)cols;
+  const float rstd = 1.0f / sqrtf(var + eps);
+
+  Tout* yr = y + row * (int64_t)cols;
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunks) {
+      float g[N], b[N], o[N];
+      if (gamma != nullptr) {
+        Chunk<Tp, N>::load_keep(gamma + c * N, g);
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) g[j] = 1.0f;
+      }
+      if (beta != nullptr) {
+        Chunk<Tp, N>::load_keep(beta + c * N, b);
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) b[j] = 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
+      Chunk<Tout, N>::store(yr + c * N, o);
+    }
+  }
+  if (lane == 0) {
+    if (mean_out != nullptr) mean_out[row] = mean;
+    if (rstd_out != nullptr) rstd_out[row] = rstd;
+  }
+}
+
+// Generic: one CTA per row, scalar accesses, three passes over the row (L1/L2 serve the
+// re-reads).
+template <typename Tin, typename Tp, typename Tout>
+__global__ void layer_norm_block_kernel(const Tin* __restrict__ x, const Tp* __restrict__ gamma,
+                                        const Tp* __restrict__ beta, Tout* __restrict__ y,
+                                        float* __restrict__ mean_out,
+                                        float* __restrict__ rstd_out, int64_t cols,
+                                        int64_t x_row_stride, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const Tin* xr = x + row * x_row_stride;
+  float s = 0.0f;
+  for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) s += Elem<Tin>::to_f32(xr[j]);
+  const float mean = block_sum(s, red) / (float)cols;
+  float sq = 0.0f;
+  for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+    const float d = Elem<Tin>::to_f32(xr[j]) - mean;
+    sq += d * d;
+  }
+  const float var = block_sum(sq, red) / (float)cols;
+  const float rstd = 1.0f / sqrtf(var + eps);
+  Tout* yr = y + row * cols;
+  for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+    const float g = gamma != nullptr ? Elem<Tp>::to_f32(gamma[j]) : 1.0f;
+    const float b = beta != nullptr ? Elem<Tp>::to_f32(beta[j]) : 0.0f;
+    yr[j] = Elem<Tout>::from_f32((Elem<Tin>::to_f32(xr[j]) - mean) * rstd * g + b);
+  }
+  if (threadIdx.x == 0) {
+    if (mean_out != nullptr) mean_out[row] = mean;
+    if (rstd_out != nullptr) rstd_out[row] = rstd;
+  }
+}
+
+template <typename Tin, typename Tp, typename Tout>
+int32_t launch_layer_norm(const void* x, const void* gamma, const void* beta, void* y,
+                          float* mean, float* rstd, int64_t rows, int64_t cols,
+                          int64_t x_row_stride, float eps, cudaStream_t stream) {
+  constexpr int N = Elem<Tin>::kVec;
+  const Tin* xp = static_cast<const Tin*>(x);
+  const Tp* gp = static_cast<const Tp*>(gamma);
+  const Tp* bp = static_cast<const Tp*>(beta);
+  Tout* yp = static_cast<Tout*>(y);
+  const size_t out_align = N * sizeof(Tout) > 16 ? 16 : N * sizeof(Tout);
+  const size_t p_align = N * sizeof(Tp) > 16 ? 16 : N * sizeof(Tp);
+  const bool vec_ok = cols % N == 0 && x_row_stride % N == 0 && aligned_to(x, 16) &&
+                      aligned_to(y, out_align) && (gamma == nullptr || aligned_to(gamma, p_align)) &&
+                      (beta == nullptr || aligned_to(beta, p_align)) && cols <= 32 * N * 16 &&
+                      rows <= (int64_t)INT32_MAX * kWarpsPerCta;
+  if (vec_ok) {
+    const int per_lane = (int)((cols / N + 31) / 32);
+    const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+#define LN_LAUNCH(MAXC)                                                                   \
+  layer_norm_warp_kernel<Tin, Tp, Tout, N, MAXC><<<grid, kRowThreads, 0, stream>>>(         \
+      xp, gp, bp, yp, mean, rstd, rows, (int)cols, x_row_stride, eps)
+    if (per_lane <= 1) LN_LAUNCH(1);
+    else if (per_lane <= 2) LN_LAUNCH(2);
+    else if (per_lane <= 4) LN_LAUNCH(4);
+    else if (per_lane <= 8) LN_LAUNCH(8);
+    else LN_LAUNCH(16);
+#undef LN_LAUNCH
+  } else {
+    B200_REQUIRE(rows <= INT32_MAX, B200_ERR_UNSUPPORTED, "layer_norm: too many rows");
+    const int threads = cols >= 1024 ? 512 : 128;
+    layer_norm_block_kernel<Tin, Tp, Tout><<<(unsigned)rows, threads, 0, stream>>>(
+        xp, gp, bp, yp, mean, rstd, cols, x_row_stride, eps);
+  }
+  B200_CHECK_LAUNCH("layer_norm");
+  return B200_OK;
+}
+
+// =========================================================================================
+// Softmax over the last dim
+// =========================================================================================
+
+template <bool kAccurate>
+__device__ __forceinline__ float exp_sel(float x) {
+  return kAccurate ? expf(x) : __expf(x);
+}
+
+template <typename Tin, typename Tout, int N, int MAXC>
+__global__ void __launch_bounds__(kRowThreads)
+softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t rows, int cols,
+                    int64_t x_row_stride, float scale, int causal, int64_t q_len) {
+  constexpr bool kAccurate = sizeof(Tout) == 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nchunks = cols / N;
+  int allowed = cols;
+  if (causal) {
+    const int64_t a = row % q_len + 1;
+    allowed = a < cols ? (int)a : cols;
+  }
+  const Tin* xr = x + row * x_row_stride;
+
+  float v[MAXC][N];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = lane + 32 * i;
+    // Chunks entirely past the causal limit are never read.
+    if (c < nchunks && c * N < allowed) {
+      Chunk<Tin, N>::load(xr + c * N, v[i]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        v[i][j] = (c * N + j < allowed) ? v[i][j] * scale : -INFINITY;
+        m = nan_max(m, v[i][j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[i][j] = -INFINITY;
+    }
+  }
+  m = warp_max(m);
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      // masked lanes hold -inf: exp gives exactly 0 unless the whole row is -inf (NaN, as torch)
+      v[i][j] = exp_sel<kAccurate>(v[i][j] - m);
+      s += v[i][j];
+    }
+  }
+  s = warp_sum(s);
+  const float inv = 1.0f / s;
+  Tout* yr = y + row * (int64_t)cols;
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunks) {
+      float o[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = (c * N + j < allowed) ? v[i][j] * inv : 0.0f;
+      Chunk<Tout, N>::store(yr + c * N, o);
+    }
+  }
+}
+
+template <typename Tin, typename Tout>
+__global__ void softmax_block_kernel(const Tin* __restrict__ x, Tout* __restrict__ y,
+                                     int64_t cols, int64_t x_row_stride, float scale, int causal,
+                                     int64_t q_len) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  int64_t allowed = cols;
+  if (causal) {
+    const int64_t a = row % q_len + 1;
+    allowed = a < cols ? a : cols;
+  }
+  const Tin* xr = x + row * x_row_stride;
+  float m = -INFINITY;
+  for (int64_t j = threadIdx.x; j < allowed; j += blockDim.x)
+    m = nan_max(m, Elem<Tin>::to_f32(xr[j]) * scale);
+  m = block_max(m, red);
+  float s = 0.0f;
+  for (int64_t j = threadIdx.x; j < allowed; j += blockDim.x)
+    s += expf(Elem<Tin>::to_f32(xr[j]) * scale - m);
+  s = block_sum(s, red);
+  const float inv = 1.0f / s;
+  Tout* yr = y + row * cols;
+  for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+    const float o = j < allowed ? expf(Elem<Tin>::to_f32(xr[j]) * scale - m) * inv : 0.0f;
+    yr[j] = Elem<Tout>::from_f32(o);
+  }
+}
+
+template <typename Tin, typename Tout>
+int32_t launch_softmax(const void* x, void* y, int64_t rows, int64_t cols, int64_t x_row_stride,
+                       float scale, int causal, int64_t q_len, cudaStream_t stream) {
+  constexpr int N = Elem<Tin>::kVec;
+  const Tin* xp = static_cast<const Tin*>(x);
+  Tout* yp = static_cast<Tout*>(y);
+  const size_t out_align = N * sizeof(Tout) > 16 ? 16 : N * sizeof(Tout);
+  const bool vec_ok = cols % N == 0 && x_row_stride % N == 0 && aligned_to(x, 16) &&
+                      aligned_to(y, out_align) && cols <= 32 * N * 8 &&
+                      rows <= (int64_t)INT32_MAX * kWarpsPerCta;
+  if (vec_ok) {
+    const int per_lane = (int)((cols / N + 31) / 32);
+    const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+#define SM_LAUNCH(MAXC)                                                              \
+  softmax_warp_kernel<Tin, Tout, N, MAXC><<<grid, kRowThreads, 0, stream>>>(           \
+      xp, yp, rows, (int)cols, x_row_stride, scale, causal, q_len)
+    if (per_lane <= 1) SM_LAUNCH(1);
+    else if (per_lane <= 2) SM_LAUNCH(2);
+    else if (per_lane <= 4) SM_LAUNCH(4);
+    else SM_LAUNCH(8);
+#undef SM_LAUNCH
+  } else {
+    B200_REQUIRE(rows <= INT32_MAX, B200_ERR_UNSUPPORTED, "softmax: too many rows");
+    const int threads = cols >= 2048 ? 1024 : (cols >= 512 ? 256 : 128);
+    softmax_block_kernel<Tin, Tout><<<(unsigned)rows, threads, 0, stream>>>(
+        xp, yp, cols, x_row_stride, scale, causal, q_len);
+  }
+  B200_CHECK_LAUNCH("softmax_lastdim");
+  return B200_OK;
+}
+
+// =========================================================================================
+// GELU
+// =========================================================================================
+
+// tanh form rewritten as x * sigmoid(2u): 0.5 x (1 + tanh(u)) == x / (1 + exp(-2u)).
+// Signed zero, +inf (-> +inf) and -inf / NaN (-> NaN) come out as torch's formula gives them.
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float u = k0 * (x + k1 * x * x * x);
+  return x / (1.0f + expf(-2.0f * u));
+}
+
+constexpr int kGeluUnroll = 4;
+constexpr int kGeluThreads = 256;
+
+template <typename T, bool kTanh>
+__global__ void __launch_bounds__(kGeluThreads)
+gelu_vec_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nvec) {
+  constexpr int N = Elem<T>::kVec;
+  // Each CTA owns kGeluUnroll consecutive slabs of blockDim vectors; all loads issue first.
+  const int64_t base = (int64_t)blockIdx.x * (kGeluThreads * kGeluUnroll) + threadIdx.x;
+  float v[kGeluUnroll][N];
+#pragma unroll
+  for (int u = 0; u < kGeluUnroll; ++u) {
+    const int64_t i = base + (int64_t)u * kGeluThreads;
+    if (i < nvec) load16_stream(x + i * N, v[u]);
+  }
+#pragma unroll
+  for (int u = 0; u < kGeluUnroll; ++u) {
+    const int64_t i = base + (int64_t)u * kGeluThreads;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[u][j] = kTanh ? gelu_tanh_fast(v[u][j]) : gelu_erf_f32(v[u][j]);
+      store16_stream(y + i * N, v[u]);
+    }
+  }
+}
+
+template <typename T, bool kTanh>
+__global__ void gelu_scalar_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t start,
+                                   int64_t numel) {
+  const int64_t i = start + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < numel) {
+    const float v = Elem<T>::to_f32(x[i]);
+    y[i] = Elem<T>::from_f32(kTanh ? gelu_tanh_fast(v) : gelu_erf_f32(v));
+  }
+}
+
+template <typename T, bool kTanh>
+int32_t launch_gelu(const void* x, void* y, int64_t numel, cudaStream_t stream) {
+  constexpr int N = Elem<T>::kVec;
+  const T* xp = static_cast<const T*>(x);
+  T* yp = static_cast<T*>(y);
+  int64_t nvec = 0;
+  if (aligned_to(x, 16) && aligned_to(y, 16)) nvec = numel / N;
+  if (nvec > 0) {
+    const int64_t per_cta = (int64_t)kGeluThreads * kGeluUnroll;
+    const int64_t grid = (nvec + per_cta - 1) / per_cta;
+    B200_REQUIRE(grid <= INT32_MAX, B200_ERR_UNSUPPORTED, "gelu: tensor too large");
+    gelu_vec_kernel<T, kTanh><<<(unsigned)grid, kGeluThreads, 0, stream>>>(xp, yp, nvec);
+    B200_CHECK_LAUNCH("gelu");
+  }
+  const int64_t tail_start = nvec * N;
+  if (tail_start < numel) {
+    const int64_t tail = numel - tail_start;
+    const int64_t grid = (tail + 255) / 256;
+    B200_REQUIRE(grid <= INT32_MAX, B200_ERR_UNSUPPORTED, "gelu: tensor too large");
+    gelu_scalar_kernel<T, kTanh><<<(unsigned)grid, 256, 0, stream>>>(xp, yp, tail_start, numel);
+    B200_CHECK_LAUNCH("gelu(tail)");
+  }
+  return B200_OK;
+}
+
+// =========================================================================================
+// Trailing-dim reductions
+// =========================================================================================
+
+template <int OP>
+__device__ __forceinline__ float red_init() { return OP == B200_REDUCE_AMAX ? -INFINITY : 0.0f; }
+template <int OP>
+__device__ __forceinline__ float red_step(float a, float b) {
+  return OP == B200_REDUCE_AMAX ? nan_max(a, b) : a + b;
+}
+
+template <typename Tin, typename Tout, int OP>
+__global__ void __launch_bounds__(kRowThreads)
+reduce_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t rows, int cols,
+                   int64_t x_row_stride) {
+  constexpr int N = Elem<Tin>::kVec;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nchunks = cols / N;
+  const Tin* xr = x + row * x_row_stride;
+  // Four independent accumulators keep four 16-byte loads in flight per lane.
+  float acc[4] = {red_init<OP>(), red_init<OP>(), red_init<OP>(), red_init<OP>()};
+  int c = lane;
+  for (; c + 96 < nchunks; c += 128) {
+    float v[4][N];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) load16_stream(xr + (c + 32 * u) * N, v[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[u] = red_step<OP>(acc[u], v[u][j]);
+  }
+  for (; c < nchunks; c += 32) {
+    float v[N];
+    load16_stream(xr + c * N, v);
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[0] = red_step<OP>(acc[0], v[j]);
+  }
+  float r = red_step<OP>(red_step<OP>(acc[0], acc[1]), red_step<OP>(acc[2], acc[3]));
+  r = OP == B200_REDUCE_AMAX ? warp_max(r) : warp_sum(r);
+  if (OP == B200_REDUCE_MEAN) r = r / (float)cols;
+  if (lane == 0) y[row] = Elem<Tout>::from_f32(r);
+}
+
+template <typename Tin, typename Tout, int OP>
+__global__ void reduce_block_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t cols,
+                                    int64_t x_row_stride) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const Tin* xr = x + row * x_row_stride;
+  float r = red_init<OP>();
+  for (int64_t j = threadIdx.x; j < cols; j += blockDim.x)
+    r = red_step<OP>(r, Elem<Tin>::to_f32(xr[j]));
+  r = OP == B200_REDUCE_AMAX ? block_max(r, red) : block_sum(r, red);
+  if (OP == B200_REDUCE_MEAN) r = r / (float)cols;
+  if (threadIdx.x == 0) y[row] = Elem<Tout>::from_f32(r);
+}
+
+template <typename Tin, typename Tout, int OP>
+int32_t launch_reduce(const void* x, void* y, int64_t rows, int64_t cols, int64_t x_row_stride,
+                      cudaStream_t stream) {
+  constexpr int N = Elem<Tin>::kVec;
+  const Tin* xp = static_cast<const Tin*>(x);
+  Tout* yp = static_cast<Tout*>(y);
+  const bool vec_ok = cols % N == 0 && x_row_stride % N == 0 && aligned_to(x, 16) &&
+                      cols <= (1 << 20) && rows >= 512 &&
+                      rows <= (int64_t)INT32_MAX * kWarpsPerCta;
+  if (vec_ok) {
+    const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+    reduce_warp_kernel<Tin, Tout, OP><<<grid, kRowThreads, 0, stream>>>(xp, yp, rows, (int)cols,
+                                                                       x_row_stride);
+  } else {
+    B200_REQUIRE(rows <= INT32_MAX, B200_ERR_UNSUPPORTED, "reduce: too many rows");
+    const int threads = cols >= 4096 ? 1024 : (cols >= 512 ? 256 : 64);
+    reduce_block_kernel<Tin, Tout, OP><<<(unsigned)rows, threads, 0, stream>>>(xp, yp, cols,
+                                                                              x_row_stride);
+  }
+  B200_CHECK_LAUNCH("reduce_lastdim");
+  return B200_OK;
+}
+
+template <typename Tin, typename Tout>
+int32_t dispatch_reduce(int32_t op, const void* x, void* y, int64_t rows, int64_t cols,
+                        int64_t x_row_stride, cudaStream_t stream) {
+  switch (op) {
+    case B200_REDUCE_SUM:
+      return launch_reduce<Tin, Tout, B200_REDUCE_SUM>(x, y, rows, cols, x_row_stride, stream);
+    case B200_REDUCE_MEAN:
+      return launch_reduce<Tin, Tout, B200_REDUCE_MEAN>(x, y, rows, cols, x_row_stride, stream);
+    default:
+      return launch_reduce<Tin, Tout, B200_REDUCE_AMAX>(x, y, rows, cols, x_row_stride, stream);
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+using bf16 = __nv_bfloat16;
+
+extern "C" B200_API int32_t b200_layer_norm(const void* x, const void* gamma, const void* beta, void* y,
+                                   float* mean, float* rstd, int64_t rows, int64_t cols,
+                                   int64_t x_row_stride, float eps, int32_t in_dtype,
+                                   int32_t param_dtype, int32_t out_dtype,
+                                   b200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(rows >= 0 && cols >= 0, B200_ERR_INVALID_ARG, "layer_norm: negative size");
+  B200_REQUIRE(valid_dtype(in_dtype) && valid_dtype(param_dtype) && valid_dtype(out_dtype),
+               B200_ERR_INVALID_ARG, "layer_norm: bad dtype enum");
+  if (rows == 0) return B200_OK;
+  B200_REQUIRE(cols > 0, B200_ERR_INVALID_ARG, "layer_norm: cols must be positive");
+  B200_REQUIRE(x != nullptr && y != nullptr, B200_ERR_INVALID_ARG, "layer_norm: null pointer");
+  B200_REQUIRE(x_row_stride >= cols || rows == 1, B200_ERR_INVALID_ARG,
+               "layer_norm: row stride smaller than cols");
+  B200_REQUIRE(aligned_to(x, dtype_size(in_dtype)) && aligned_to(y, dtype_size(out_dtype)),
+               B200_ERR_ALIGNMENT, "layer_norm: pointer not element aligned");
+#define LN_CASE(TI, TP, TO) \
+  return launch_layer_norm<TI, TP, TO>(x, gamma, beta, y, mean, rstd, rows, cols, x_row_stride, eps, stream)
+  const int key = in_dtype * 4 + param_dtype * 2 + out_dtype;
+  switch (key) {
+    case 0: LN_CASE(float, float, float);
+    case 1: LN_CASE(float, float, bf16);
+    case 2: LN_CASE(float, bf16, float);
+    case 3: LN_CASE(float, bf16, bf16);
+    case 4: LN_CASE(bf16, float, float);
+    case 5: LN_CASE(bf16, float, bf16);
+    case 6: LN_CASE(bf16, bf16, float);
+    default: LN_CASE(bf16, bf16, bf16);
+  }
+#undef LN_CASE
+}
+
+extern "C" B200_API int32_t b200_softmax_lastdim(const void* x, void* y, int64_t rows, int64_t cols,
+                                        int64_t x_row_stride, float scale, int32_t causal,
+                                        int64_t q_len, int32_t in_dtype, int32_t out_dtype,
+                                        b200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(rows >= 0 && cols >= 0, B200_ERR_INVALID_ARG, "softmax: negative size");
+  B200_REQUIRE(valid_dtype(in_dtype) && valid_dtype(out_dtype), B200_ERR_INVALID_ARG,
+               "softmax: bad dtype enum");
+  B200_REQUIRE(!(in_dtype == B200_F32 && out_dtype == B200_BF16), B200_ERR_UNSUPPORTED,
+               "softmax: fp32 input with bf16 output is not a torch softmax signature");
+  if (rows == 0 || cols == 0) return B200_OK;
+  B200_REQUIRE(x != nullptr && y != nullptr, B200_ERR_INVALID_ARG, "softmax: null pointer");
+  B200_REQUIRE(!causal || q_len > 0, B200_ERR_INVALID_ARG, "softmax: causal needs q_len > 0");
+  B200_REQUIRE(x_row_stride >= cols || rows == 1, B200_ERR_INVALID_ARG,
+               "softmax: row stride smaller than cols");
+  if (in_dtype == B200_F32)
+    return launch_softmax<float, float>(x, y, rows, cols, x_row_stride, scale, causal, q_len, stream);
+  if (out_dtype == B200_F32)
+    return launch_softmax<bf16, float>(x, y, rows, cols, x_row_stride, scale, causal, q_len, stream);
+  return launch_softmax<bf16, bf16>(x, y, rows, cols, x_row_stride, scale, causal, q_len, stream);
+}
+
+extern "C" B200_API int32_t b200_gelu(const void* x, void* y, int64_t numel, int32_t approximate_tanh,
+                             int32_t dtype, b200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(numel >= 0, B200_ERR_INVALID_ARG, "gelu: negative size");
+  B200_REQUIRE(valid_dtype(dtype), B200_ERR_INVALID_ARG, "gelu: bad dtype enum");
+  if (numel == 0) return B200_OK;
+  B200_REQUIRE(x != nullptr && y != nullptr, B200_ERR_INVALID_ARG, "gelu: null pointer");
+  if (dtype == B200_F32)
+    return approximate_tanh ? launch_gelu<float, true>(x, y, numel, stream)
+                            : launch_gelu<float, false>(x, y, numel, stream);
+  return approximate_tanh ? launch_gelu<bf16, true>(x, y, numel, stream)
+                          : launch_gelu<bf16, false>(x, y, numel, stream);
+}
+
+extern "C" B200_API int32_t b200_reduce_lastdim(const void* x, void* y, int64_t rows, int64_t cols,
+                                       int64_t x_row_stride, int32_t op, int32_t in_dtype,
+                                       int32_t out_dtype, b200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(rows >= 0 && cols >= 0, B200_ERR_INVALID_ARG, "reduce: negative size");
+  B200_REQUIRE(valid_dtype(in_dtype) && valid_dtype(out_dtype), B200_ERR_INVALID_ARG,
+               "reduce: bad dtype enum");
+  B200_REQUIRE(op >= B200_REDUCE_SUM && op <= B200_REDUCE_AMAX, B200_ERR_INVALID_ARG,
+               "reduce: bad op enum");
+  if (rows == 0) return B200_OK;
+  B200_REQUIRE(x != nullptr || cols == 0, B200_ERR_INVALID_ARG, "reduce: null input");
+  B200_REQUIRE(y != nullptr, B200_ERR_INVALID_ARG, "reduce: null output");
+  B200_REQUIRE(cols > 0 || op == B200_REDUCE_SUM, B200_ERR_INVALID_ARG,
+               "reduce: mean/amax over an empty dim");
+  if (in_dtype == B200_F32 && out_dtype == B200_F32)
+    return dispatch_reduce<float, float>(op, x, y, rows, cols, x_row_stride, stream);
+  if (in_dtype == B200_BF16 && out_dtype == B200_BF16)
+    return dispatch_reduce<bf16, bf16>(op, x, y, rows, cols, x_row_stride, stream);
+  if (in_dtype == B200_BF16 && out_dtype == B200_F32)
+    return dispatch_reduce<bf16, float>(op, x, y, rows, cols, x_row_stride, stream);
+  return dispatch_reduce<float, bf16>(op, x, y, rows, cols, x_row_stride, stream);
+}

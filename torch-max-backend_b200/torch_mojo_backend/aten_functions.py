@@ -1,0 +1,439 @@
+"""The aten -> kernel registry: `MAPPING_TORCH_ATEN_TO_MOJO`, `map_to`, `DECOMPOSITION_TABLE`.
+
+Same surface and semantics as the reference registry (torch_mojo_backend/aten_functions.py:98-198):
+a dict keyed by `OpOverload` / `OpOverloadPacket` / python operator / `"ns.op"` string whose values
+are called as `fn(*args, **kwargs)` by the graph walk (torch_compile_backend/compiler.py), and a
+`@map_to(op)` decorator that also removes the op (every overload of a packet) from the
+decomposition table handed to AOTAutograd so that mapped ops reach the lowering whole.
+
+What differs is what the values do. The reference re-expresses each op as MAX graph ops; here the
+values run on `torch.Tensor`s that live on a CUDA device and the ops this backend is about --
+mm/addmm/bmm, _softmax, native_layer_norm, gelu, sum/mean/amax and the scaled-dot-product
+attention family -- enqueue hand-written sm_100a kernels through `torch.ops.b200.*`. Shape glue
+(views, slices, casts, small elementwise ops) stays on stock torch CUDA ops working on views.
+"""
+
+from __future__ import annotations
+
+import contextvars
+import functools
+import math
+import operator
+import os
+
+import torch
+from torch._decomp import core_aten_decompositions
+from torch._ops import OpOverload, OpOverloadPacket
+
+import torch_mojo_backend.is_running_tests
+from torch_mojo_backend import native, ops
+from torch_mojo_backend.flags import verbose_enabled
+
+aten = torch.ops.aten
+
+# The fx node being lowered, set by the graph walk. Multi-output lowerings use it to see which
+# outputs are consumed (reference: torch_mojo_backend/aten_functions.py:94-110).
+CURRENT_FX_NODE: contextvars.ContextVar = contextvars.ContextVar("CURRENT_FX_NODE", default=None)
+
+
+def _only_first_output_used() -> bool:
+    node = CURRENT_FX_NODE.get()
+    if node is None:
+        return False
+    return all(user.target is operator.getitem and user.args[1] == 0 for user in node.users)
+
+
+# Ops that are not mapped get decomposed by AOTAutograd with this table.
+DECOMPOSITION_TABLE = core_aten_decompositions()
+original_decomposition_table_size = len(DECOMPOSITION_TABLE)
+MAPPING_TORCH_ATEN_TO_MOJO: dict = {}
+
+IDENTICAL_FUNCTIONS = [
+    operator.add, operator.sub, operator.mul, operator.truediv, operator.floordiv, operator.pow,
+    operator.mod, operator.matmul, operator.neg, operator.gt, operator.ge, operator.lt,
+    operator.le, operator.eq, operator.ne, operator.and_, operator.or_, operator.xor,
+    operator.iadd, operator.isub, operator.imul, operator.ifloordiv, operator.ipow,
+    operator.imod, operator.getitem, str, max, min,
+]
+for _func in IDENTICAL_FUNCTIONS:
+    MAPPING_TORCH_ATEN_TO_MOJO[_func] = _func
+
+number_of_decompositions_removed = 0
+
+
+def map_to(func):
+    """Register the decorated function as the lowering of `func` (OpOverload or OpOverloadPacket)."""
+
+    def decorator(func_to_map):
+        registered = func_to_map
+        if torch_mojo_backend.is_running_tests.IS_RUNNING_TESTS:
+            # Call counters let tests assert that the registered lowering really ran
+            # (reference: torch_mojo_backend/aten_functions.py:167-176).
+            @functools.wraps(func_to_map)
+            def counted(*args, **kwargs):
+                counted.call_count += 1
+                return func_to_map(*args, **kwargs)
+
+            counted.call_count = 0
+            registered = counted
+        MAPPING_TORCH_ATEN_TO_MOJO[func] = registered
+        if isinstance(func, OpOverload):
+            DECOMPOSITION_TABLE.pop(func, None)
+        elif isinstance(func, OpOverloadPacket):
+            global number_of_decompositions_removed
+            for overload_name in func.overloads():
+                popped = DECOMPOSITION_TABLE.pop(getattr(func, overload_name), None)
+                if popped is not None:
+                    number_of_decompositions_removed += 1
+        else:
+            raise TypeError(f"Expected OpOverload or OpOverloadPacket, got {type(func)}")
+        return registered
+
+    return decorator
+
+
+def _kernel_dtype(*tensors) -> bool:
+    """True when every given tensor has a dtype the b200 kernels take (fp32 / bf16)."""
+    return all(t is None or native.supported_dtype(t.dtype) for t in tensors)
+
+
+# ==============================================================================================
+# GEMM family
+# ==============================================================================================
+
+
+# mm(Tensor self, Tensor mat2) -> Tensor
+@map_to(aten.mm)
+def aten_mm(x, y):
+    if not _kernel_dtype(x, y):
+        return aten.mm.default(x, y)
+    return ops.gemm(x, y)
+
+
+# addmm(Tensor self, Tensor mat1, Tensor mat2, *, Scalar beta=1, Scalar alpha=1) -> Tensor
+@map_to(aten.addmm)
+def aten_addmm(input, mat1, mat2, *, beta=1.0, alpha=1.0):
+    # beta * input + alpha * (mat1 @ mat2), input broadcast to [m, n]; the scaling and the add
+    # happen in the GEMM epilogue on the fp32 accumulator.
+    if not _kernel_dtype(input, mat1, mat2):
+        return aten.addmm.default(input, mat1, mat2, beta=beta, alpha=alpha)
+    return ops.gemm(mat1, mat2, input, None, float(alpha), float(beta))
+
+
+# bmm(Tensor self, Tensor mat2) -> Tensor
+@map_to(aten.bmm)
+def aten_bmm(input, mat2):
+    if not _kernel_dtype(input, mat2):
+        return aten.bmm.default(input, mat2)
+    return ops.gemm(input, mat2)
+
+
+# ==============================================================================================
+# Row kernels
+# ==============================================================================================
+
+
+def _move_dim_last(x, dim):
+    dim = dim % x.dim() if x.dim() > 0 else 0
+    if x.dim() == 0 or dim == x.dim() - 1:
+        return x, None
+    return x.movedim(dim, -1), dim
+
+
+# _softmax(Tensor self, int dim, bool half_to_float) -> Tensor
+@map_to(aten._softmax)
+def aten__softmax(self, dim: int, half_to_float: bool):
+    return aten_softmax(self, dim=dim, dtype=torch.float32 if half_to_float else None)
+
+
+# softmax.int(Tensor self, int dim, ScalarType? dtype=None) -> Tensor
+@map_to(aten.softmax)
+def aten_softmax(input, dim=-1, dtype=None):
+    if not _kernel_dtype(input) or (dtype is not None and dtype not in (torch.float32, input.dtype)):
+        return torch.softmax(input, dim, dtype=dtype)
+    if input.dim() == 0:
+        return torch.ones_like(input, dtype=dtype or input.dtype)
+    if input.dtype == torch.float32:
+        dtype = None
+    x, moved = _move_dim_last(input, dim)
+    y = ops.softmax(x, 1.0, False, 0, dtype)
+    return y if moved is None else y.movedim(-1, moved)
+
+
+# native_layer_norm(Tensor input, SymInt[] normalized_shape, Tensor? weight, Tensor? bias, float eps)
+#   -> (Tensor, Tensor, Tensor)
+@map_to(aten.native_layer_norm)
+def aten_native_layer_norm(input, normalized_shape, weight, bias, eps):
+    if not _kernel_dtype(input, weight, bias):
+        return aten.native_layer_norm.default(input, normalized_shape, weight, bias, eps)
+    k = len(normalized_shape)
+    lead = input.shape[: input.dim() - k]
+    cols = math.prod(normalized_shape)
+    x = input.reshape(*lead, cols)
+    w = weight.reshape(cols) if weight is not None else None
+    b = bias.reshape(cols) if bias is not None else None
+    y, mean, rstd = ops.layer_norm(x, w, b, eps)
+    y = y.reshape(input.shape)
+    if _only_first_output_used():
+        # Statistics are dead in inference graphs (same observation as the reference makes to
+        # pick its fused kernel, torch_mojo_backend/aten_functions.py:2837-2849).
+        return y, None, None
+    stat_shape = (*lead, *([1] * k))
+    # torch reports the statistics in the input dtype on CPU and in fp32 for reduced-precision
+    # CUDA inputs; follow what the traced graph recorded for this node.
+    stat_dtype = _traced_output_dtype(1, torch.float32)
+    return y, mean.reshape(stat_shape).to(stat_dtype), rstd.reshape(stat_shape).to(stat_dtype)
+
+
+def _traced_output_dtype(index: int, default: torch.dtype) -> torch.dtype:
+    node = CURRENT_FX_NODE.get()
+    if node is None:
+        return default
+    val = node.meta.get("val")
+    if isinstance(val, (tuple, list)) and index < len(val) and isinstance(val[index], torch.Tensor):
+        return val[index].dtype
+    return default
+
+
+# gelu(Tensor self, *, str approximate='none') -> Tensor
+@map_to(aten.gelu)
+def aten_gelu(input, approximate="none"):
+    if not _kernel_dtype(input):
+        return aten.gelu.default(input, approximate=approximate)
+    return ops.gelu(input, approximate)
+
+
+def _reduce_dims(input, dim, keepdim, op, dtype):
+    """sum/mean/amax over `dim` (list, int or None): the reduced dims are moved to the end and
+    flattened so that one trailing-dim kernel launch covers any dim list."""
+    nd = input.dim()
+    if dim is None or (isinstance(dim, (list, tuple)) and len(dim) == 0):
+        dims = list(range(nd))
+    elif isinstance(dim, int):
+        dims = [dim % nd if nd > 0 else 0]
+    else:
+        dims = sorted({d % nd if nd > 0 else 0 for d in dim})
+    if nd == 0:
+        x = input.reshape(1)
+        out = ops.reduce(x, op, dtype)
+        return out
+    kept = [d for d in range(nd) if d not in dims]
+    x = input.permute(*kept, *dims) if kept + dims != list(range(nd)) else input
+    lead = [input.shape[d] for d in kept]
+    x = x.reshape(*lead, -1)
+    out = ops.reduce(x, op, dtype)
+    if keepdim:
+        shape = [1 if d in dims else input.shape[d] for d in range(nd)]
+        out = out.reshape(shape)
+    return out
+
+
+# sum.dim_IntList(Tensor self, int[1]? dim, bool keepdim=False, *, ScalarType? dtype=None) -> Tensor
+@map_to(aten.sum)
+def aten_sum(input, dim=None, keepdim=False, *, dtype=None):
+    out_dtype = dtype or input.dtype
+    if not _kernel_dtype(input) or not native.supported_dtype(out_dtype) or input.numel() == 0:
+        # Integer/bool sums (promoted to int64 by torch) and empty reductions are shape glue.
+        if dim is None:
+            return torch.sum(input, dtype=dtype)
+        return torch.sum(input, dim, keepdim, dtype=dtype)
+    return _reduce_dims(input, dim, keepdim, native.REDUCE_SUM, out_dtype)
+
+
+# mean(Tensor self, *, ScalarType? dtype=None) -> Tensor
+# mean.dim(Tensor self, int[1]? dim, bool keepdim=False, *, ScalarType? dtype=None) -> Tensor
+@map_to(aten.mean)
+def aten_mean(input, dim=None, keepdim=False, *, dtype=None):
+    out_dtype = dtype or input.dtype
+    if not _kernel_dtype(input) or not native.supported_dtype(out_dtype) or input.numel() == 0:
+        if dim is None:
+            return torch.mean(input, dtype=dtype)
+        return torch.mean(input, dim, keepdim, dtype=dtype)
+    return _reduce_dims(input, dim, keepdim, native.REDUCE_MEAN, out_dtype)
+
+
+# amax(Tensor self, int[1] dim=[], bool keepdim=False) -> Tensor
+@map_to(aten.amax)
+def aten_amax(input, dim=[], keepdim=False):
+    if not _kernel_dtype(input) or input.numel() == 0:
+        return torch.amax(input, dim, keepdim)
+    return _reduce_dims(input, dim, keepdim, native.REDUCE_AMAX, input.dtype)
+
+
+# ==============================================================================================
+# Attention
+# ==============================================================================================
+
+
+def _sdpa_kernel(query, key, value, is_causal, scale):
+    """[B, H, T, D] attention through the kernel; 3-D inputs are treated as one batch."""
+    squeeze = query.dim() == 3
+    if squeeze:
+        query, key, value = query.unsqueeze(0), key.unsqueeze(0), value.unsqueeze(0)
+    if key.shape[1] != query.shape[1]:
+        rep = query.shape[1] // key.shape[1]
+        key = key.repeat_interleave(rep, dim=1)
+        value = value.repeat_interleave(rep, dim=1)
+    out, lse = ops.sdpa(query, key, value, bool(is_causal), scale)
+    if squeeze:
+        out, lse = out.squeeze(0), lse.squeeze(0)
+    return out, lse
+
+
+# _scaled_dot_product_flash_attention(Tensor query, Tensor key, Tensor value, float dropout_p=0.0,
+#   bool is_causal=False, bool return_debug_mask=False, *, float? scale=None)
+#   -> (Tensor, Tensor, Tensor, Tensor, SymInt, SymInt, Tensor, Tensor, Tensor)
+@map_to(aten._scaled_dot_product_flash_attention)
+def aten__scaled_dot_product_flash_attention(
+    query, key, value, dropout_p=0.0, is_causal=False, return_debug_mask=False, scale=None
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention dropout is not supported (inference forward only)")
+    out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
+    # The remaining outputs exist for the backward/dropout replay; the reference fabricates
+    # placeholders for them too (torch_mojo_backend/aten_functions.py:609-677). Here logsumexp
+    # is the real one.
+    dev = out.device
+    rng = torch.zeros((2,), dtype=torch.int64, device=dev)
+    unused = torch.zeros((), dtype=torch.int64, device=dev)
+    debug_mask = torch.zeros((), dtype=out.dtype, device=dev)
+    return (out, lse, None, None, query.shape[2], key.shape[2], rng, unused, debug_mask)
+
+
+# _scaled_dot_product_efficient_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_bias,
+#   bool compute_log_sumexp, float dropout_p=0.0, bool is_causal=False, *, float? scale=None)
+#   -> (Tensor output, Tensor log_sumexp, Tensor philox_seed, Tensor philox_offset)
+@map_to(aten._scaled_dot_product_efficient_attention)
+def aten__scaled_dot_product_efficient_attention(
+    query, key, value, attn_bias, compute_log_sumexp, dropout_p=0.0, is_causal=False, *, scale=None
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention dropout is not supported (inference forward only)")
+    if attn_bias is not None:
+        out = _sdpa_math(query, key, value, attn_bias, is_causal, scale)
+        lse = torch.zeros(query.shape[:-1], dtype=torch.float32, device=query.device)
+    else:
+        out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
+    dev = out.device
+    seed = torch.zeros((), dtype=torch.int64, device=dev)
+    return out, lse, seed, seed.clone()
+
+
+# _scaled_dot_product_cudnn_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_bias,
+#   bool compute_log_sumexp, float dropout_p=0.0, bool is_causal=False, bool return_debug_mask=False,
+#   *, float? scale=None) -> (Tensor, Tensor, Tensor, Tensor, SymInt, SymInt, Tensor, Tensor, Tensor)
+@map_to(aten._scaled_dot_product_cudnn_attention)
+def aten__scaled_dot_product_cudnn_attention(
+    query, key, value, attn_bias, compute_log_sumexp, dropout_p=0.0, is_causal=False,
+    return_debug_mask=False, *, scale=None,
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention dropout is not supported (inference forward only)")
+    if attn_bias is not None:
+        out = _sdpa_math(query, key, value, attn_bias, is_causal, scale)
+        lse = torch.zeros(query.shape[:-1], dtype=torch.float32, device=query.device)
+    else:
+        out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
+    dev = out.device
+    rng = torch.zeros((), dtype=torch.int64, device=dev)
+    return (out, lse, None, None, query.shape[2], key.shape[2], rng, rng.clone(), None)
+
+
+def _sdpa_math(query, key, value, attn_mask, is_causal, scale):
+    """Attention with an explicit mask: GEMM -> masked softmax kernel -> GEMM
+    (reference: aten__scaled_dot_product_attention_math, torch_mojo_backend/aten_functions.py:443-504)."""
+    d = query.shape[-1]
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    lead = query.shape[:-2]
+    L, S = query.shape[-2], key.shape[-2]
+    if key.dim() == 4 and key.shape[1] != query.shape[1]:
+        rep = query.shape[1] // key.shape[1]
+        key = key.repeat_interleave(rep, dim=1)
+        value = value.repeat_interleave(rep, dim=1)
+    q3 = query.reshape(-1, L, d)
+    k3 = key.reshape(-1, S, d)
+    v3 = value.reshape(-1, S, value.shape[-1])
+    scores = aten_bmm(q3, k3.transpose(1, 2)).reshape(*lead, L, S)
+    if attn_mask is not None:
+        if attn_mask.dtype == torch.bool:
+            scores = (scores * scale).masked_fill(~attn_mask, float("-inf"))
+        else:
+            scores = scores * scale + attn_mask
+        if is_causal:
+            causal = torch.ones(L, S, dtype=torch.bool, device=query.device).tril()
+            scores = scores.masked_fill(~causal, float("-inf"))
+        probs = aten_softmax(scores, -1)
+    else:
+        probs = ops.softmax(scores, scale, bool(is_causal), L)
+    out = aten_bmm(probs.reshape(-1, L, S).to(v3.dtype), v3)
+    return out.reshape(*lead, L, value.shape[-1])
+
+
+# _scaled_dot_product_attention_math(Tensor query, Tensor key, Tensor value, Tensor? attn_mask=None,
+#   float dropout_p=0.0, bool is_causal=False, Tensor? dropout_mask=None, *, float? scale=None,
+#   bool enable_gqa=False) -> (Tensor, Tensor)
+@map_to(aten._scaled_dot_product_attention_math)
+def aten__scaled_dot_product_attention_math(
+    query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, dropout_mask=None, *,
+    scale=None, enable_gqa=False,
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention dropout is not supported (inference forward only)")
+    out = _sdpa_math(query, key, value, attn_mask, is_causal, scale)
+    return out, torch.zeros((), dtype=out.dtype, device=out.device)
+
+
+# scaled_dot_product_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_mask=None,
+#   float dropout_p=0.0, bool is_causal=False, *, float? scale=None, bool enable_gqa=False) -> Tensor
+@map_to(aten.scaled_dot_product_attention)
+def aten_scaled_dot_product_attention(
+    query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None, enable_gqa=False
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention dropout is not supported (inference forward only)")
+    if attn_mask is None and _kernel_dtype(query, key, value) and query.dim() in (3, 4):
+        return _sdpa_kernel(query, key, value, is_causal, scale)[0]
+    return _sdpa_math(query, key, value, attn_mask, is_causal, scale)
+
+
+# ==============================================================================================
+# Glue: ops kept whole and executed by stock torch on CUDA views
+# ==============================================================================================
+
+
+def _passthrough(op):
+    def run(*args, **kwargs):
+        return op(*args, **kwargs)
+
+    run.__name__ = "aten_" + str(op).split(".")[-1]
+    run.__qualname__ = run.__name__
+    # Lets the graph walk call the node's exact OpOverload instead of re-resolving the packet.
+    run.passthrough_of = op
+    return run
+
+
+_GLUE_OPS = [
+    aten.view, aten._unsafe_view, aten.reshape, aten.transpose, aten.t, aten.permute, aten.expand,
+    aten.clone, aten.contiguous, aten.split, aten.split_with_sizes, aten.slice, aten.select,
+    aten.unsqueeze, aten.squeeze, aten.cat, aten.stack, aten.alias, aten.detach, aten.arange,
+    aten.full, aten.full_like, aten.zeros, aten.zeros_like, aten.ones, aten.ones_like, aten.empty,
+    aten.empty_like, aten.scalar_tensor, aten.tril, aten.triu, aten.eq, aten.ne, aten.lt, aten.le,
+    aten.gt, aten.ge, aten.masked_fill, aten.where, aten.add, aten.sub, aten.mul, aten.div,
+    aten.neg, aten.pow, aten.tanh, aten.exp, aten.log, aten.sqrt, aten.rsqrt, aten.abs,
+    aten.sigmoid, aten.relu, aten.silu, aten.erf, aten.reciprocal, aten.minimum, aten.maximum,
+    aten.clamp, aten._to_copy, aten.embedding, aten.argmax, aten.logical_not, aten.logical_and,
+    aten.logical_or, aten.bitwise_and, aten.bitwise_or, aten.bitwise_not, aten.cumsum, aten.all,
+    aten.any, aten.index, aten.index_select, aten.gather, aten.sym_size, aten.sym_numel,
+    aten.lift_fresh_copy, aten.copy, aten.repeat, aten.flip, aten.unbind, aten.max, aten.min,
+    aten.amin, aten.topk, aten.sort, aten.squeeze_copy, aten.native_dropout, aten._local_scalar_dense,
+]
+
+for _packet in _GLUE_OPS:
+    map_to(_packet)(_passthrough(_packet))
+
+if verbose_enabled():
+    print(
+        f"Removed {number_of_decompositions_removed}/{original_decomposition_table_size} decompositions "
+        "from the table (mapped ops stay whole)."
+    )

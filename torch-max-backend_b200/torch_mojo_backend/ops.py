@@ -1,0 +1,364 @@
+"""torch custom ops (`torch.ops.b200.*`) that marshal tensors into the libb200ops C ABI.
+
+Shape of the boundary: the reference exposes user kernels as `torch.library.custom_op`s whose
+Python body allocates the outputs and hands raw buffers to native code
+(torch_mojo_backend/custom_torch_ops_in_mojo/torch_custom_ops.py:52-87), and its eager bridges
+allocate outputs in Python before the native call (torch_mojo_backend/eager_kernels/aten_fast.py:4587-4600).
+The same split is used here: every op below allocates with `torch.empty` (caching allocator,
+stream ordered), validates, and enqueues exactly one C-ABI call on the current stream.
+
+Each op has a Meta implementation so that it can run under FakeTensorMode at compile time, and
+refuses CPU tensors: there is no CPU fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from torch_mojo_backend import native
+
+_lib = torch.library.Library("b200", "DEF")
+
+_lib.define(
+    "layer_norm(Tensor x, Tensor? weight, Tensor? bias, float eps, ScalarType? out_dtype=None)"
+    " -> (Tensor, Tensor, Tensor)"
+)
+_lib.define(
+    "softmax(Tensor x, float scale=1.0, bool causal=False, int q_len=0, ScalarType? out_dtype=None) -> Tensor"
+)
+_lib.define("gelu(Tensor x, str approximate='none') -> Tensor")
+_lib.define("reduce(Tensor x, int op, ScalarType? out_dtype=None) -> Tensor")
+_lib.define(
+    "gemm(Tensor a, Tensor b, Tensor? bias=None, Tensor? residual=None, float alpha=1.0, float beta=1.0,"
+    " int epilogue=0, ScalarType? out_dtype=None, int route=0) -> Tensor"
+)
+_lib.define(
+    "sdpa(Tensor q, Tensor k, Tensor v, bool causal=False, float? scale=None, int route=0) -> (Tensor, Tensor)"
+)
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _nbytes(*tensors) -> float:
+    return float(sum(t.numel() * t.element_size() for t in tensors if t is not None))
+
+
+def _launched(device, start, name, flops, bytes_):
+    """Bookkeeping after a successful launch: launch counter and, when installed, the profiler."""
+    native.launch_count += 1
+    if start is not None:
+        native.profiler.end(device, start, name, flops, bytes_)
+
+
+def _prof_begin(device):
+    return native.profiler.begin(device) if native.profiler is not None else None
+
+
+def _as_rows(x: torch.Tensor) -> tuple[torch.Tensor, int, int, int]:
+    """View x as [rows, cols] with a unit column stride and one row stride (copying only when
+    the layout cannot be described that way). Returns (tensor, rows, cols, row_stride)."""
+    cols = x.shape[-1] if x.dim() > 0 else 1
+    rows = x.numel() // cols if cols > 0 else 0
+    if x.dim() == 0:
+        return x.reshape(1, 1), 1, 1, 1
+    if x.is_contiguous():
+        return x, rows, cols, cols
+    if x.dim() == 2 and x.stride(1) == 1 and x.stride(0) >= cols:
+        return x, rows, cols, x.stride(0)
+    x = x.contiguous()
+    return x, rows, cols, cols
+
+
+# ---- layer_norm -----------------------------------------------------------------------------
+
+
+def _layer_norm_cuda(x, weight, bias, eps, out_dtype=None):
+    device = native.require_cuda("layer_norm", x, weight, bias)
+    out_dtype = out_dtype or x.dtype
+    xr, rows, cols, row_stride = _as_rows(x)
+    param_dtype = weight.dtype if weight is not None else (bias.dtype if bias is not None else x.dtype)
+    if weight is not None and bias is not None and weight.dtype != bias.dtype:
+        bias = bias.to(weight.dtype)
+    if weight is not None:
+        weight = weight.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    y = torch.empty(x.shape, dtype=out_dtype, device=device)
+    stat_shape = x.shape[:-1]
+    mean = torch.empty(stat_shape, dtype=torch.float32, device=device)
+    rstd = torch.empty(stat_shape, dtype=torch.float32, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_layer_norm(
+            xr.data_ptr(), _ptr(weight), _ptr(bias), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+            rows, cols, row_stride, eps, native.dtype_enum(x.dtype), native.dtype_enum(param_dtype),
+            native.dtype_enum(out_dtype), native.current_stream(device),
+        )
+    native.check("layer_norm", status)
+    _launched(device, start, "layer_norm", 0.0, _nbytes(xr, y) + 8.0 * rows)
+    return y, mean, rstd
+
+
+def _layer_norm_meta(x, weight, bias, eps, out_dtype=None):
+    y = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    mean = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    return y, mean, torch.empty_like(mean)
+
+
+# ---- softmax --------------------------------------------------------------------------------
+
+
+def _softmax_cuda(x, scale=1.0, causal=False, q_len=0, out_dtype=None):
+    device = native.require_cuda("softmax", x)
+    out_dtype = out_dtype or x.dtype
+    xr, rows, cols, row_stride = _as_rows(x)
+    y = torch.empty(x.shape, dtype=out_dtype, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_softmax_lastdim(
+            xr.data_ptr(), y.data_ptr(), rows, cols, row_stride, scale, int(causal), q_len,
+            native.dtype_enum(x.dtype), native.dtype_enum(out_dtype), native.current_stream(device),
+        )
+    native.check("softmax", status)
+    _launched(device, start, "softmax", 0.0, _nbytes(xr, y))
+    return y
+
+
+def _softmax_meta(x, scale=1.0, causal=False, q_len=0, out_dtype=None):
+    return torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+
+
+# ---- gelu -----------------------------------------------------------------------------------
+
+
+def _gelu_cuda(x, approximate="none"):
+    device = native.require_cuda("gelu", x)
+    if approximate not in ("none", "tanh"):
+        raise ValueError(f"gelu: approximate must be 'none' or 'tanh', got {approximate!r}")
+    xc = x if x.is_contiguous() else x.contiguous()
+    y = torch.empty(x.shape, dtype=x.dtype, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_gelu(
+            xc.data_ptr(), y.data_ptr(), xc.numel(), int(approximate == "tanh"),
+            native.dtype_enum(x.dtype), native.current_stream(device),
+        )
+    native.check("gelu", status)
+    _launched(device, start, "gelu", 0.0, _nbytes(xc, y))
+    return y
+
+
+def _gelu_meta(x, approximate="none"):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+# ---- reduce over the last dim ---------------------------------------------------------------
+
+
+def _reduce_cuda(x, op, out_dtype=None):
+    device = native.require_cuda("reduce", x)
+    out_dtype = out_dtype or x.dtype
+    xr, rows, cols, row_stride = _as_rows(x)
+    y = torch.empty(x.shape[:-1], dtype=out_dtype, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_reduce_lastdim(
+            xr.data_ptr(), y.data_ptr(), rows, cols, row_stride, op, native.dtype_enum(x.dtype),
+            native.dtype_enum(out_dtype), native.current_stream(device),
+        )
+    native.check("reduce", status)
+    _launched(device, start, "reduce", 0.0, _nbytes(xr, y))
+    return y
+
+
+def _reduce_meta(x, op, out_dtype=None):
+    return torch.empty(x.shape[:-1], dtype=out_dtype or x.dtype, device=x.device)
+
+
+# ---- gemm -----------------------------------------------------------------------------------
+
+
+def _gemm_out_shape(a, b):
+    if a.dim() == 2 and b.dim() == 2:
+        if a.shape[1] != b.shape[0]:
+            raise RuntimeError(f"gemm: shapes {tuple(a.shape)} and {tuple(b.shape)} cannot be multiplied")
+        return (a.shape[0], b.shape[1])
+    if a.dim() == 3 and b.dim() == 3:
+        if a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
+            raise RuntimeError(f"gemm: batched shapes {tuple(a.shape)} and {tuple(b.shape)} cannot be multiplied")
+        return (a.shape[0], a.shape[1], b.shape[2])
+    raise RuntimeError(f"gemm: operands must both be 2-D or both 3-D, got {a.dim()}-D and {b.dim()}-D")
+
+
+def fill_gemm_args(a, b, bias, residual, c, alpha, beta, epilogue, route) -> native.GemmArgs:
+    """Marshals tensors into the C struct; separate from the launch so that tests can inspect it."""
+    g = native.GemmArgs()
+    batched = a.dim() == 3
+    g.a, g.b, g.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    g.m, g.k = a.shape[-2], a.shape[-1]
+    g.n = b.shape[-1]
+    g.batch = a.shape[0] if batched else 1
+    g.a_row_stride, g.a_col_stride = a.stride(-2), a.stride(-1)
+    g.b_row_stride, g.b_col_stride = b.stride(-2), b.stride(-1)
+    g.a_batch_stride = a.stride(0) if batched else 0
+    g.b_batch_stride = b.stride(0) if batched else 0
+    g.c_row_stride = c.stride(-2)
+    g.c_batch_stride = c.stride(0) if batched else 0
+    g.bias = _ptr(bias)
+    g.bias_row_stride = 0
+    g.bias_dtype = native.F32
+    if bias is not None:
+        g.bias_dtype = native.dtype_enum(bias.dtype)
+        g.bias_row_stride = 0 if bias.dim() == 1 else bias.stride(0)
+    g.residual = _ptr(residual)
+    g.residual_row_stride = 0
+    g.residual_dtype = native.F32
+    if residual is not None:
+        g.residual_dtype = native.dtype_enum(residual.dtype)
+        g.residual_row_stride = residual.stride(0)
+    g.alpha, g.beta = alpha, beta
+    g.in_dtype = native.dtype_enum(a.dtype)
+    g.out_dtype = native.dtype_enum(c.dtype)
+    g.epilogue = epilogue
+    g.route = route
+    return g
+
+
+def _normalise_bias(bias, m, n):
+    """1-D [n] stays a broadcast row; anything else becomes an [m, n] matrix with unit column stride."""
+    if bias is None:
+        return None
+    if bias.dim() == 1 and bias.shape[0] == n:
+        return bias if bias.stride(0) == 1 else bias.contiguous()
+    if bias.dim() == 2 and bias.shape[0] == 1 and bias.shape[1] == n:
+        row = bias[0]
+        return row if row.stride(0) == 1 else row.contiguous()
+    full = bias.expand(m, n)
+    if full.stride(1) != 1 or full.stride(0) < n:
+        full = full.contiguous()
+    return full
+
+
+def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, out_dtype=None, route=0):
+    device = native.require_cuda("gemm", a, b, bias, residual)
+    if a.dtype != b.dtype:
+        raise RuntimeError(f"gemm: operand dtypes differ ({a.dtype} and {b.dtype})")
+    out_shape = _gemm_out_shape(a, b)
+    out_dtype = out_dtype or a.dtype
+    c = torch.empty(out_shape, dtype=out_dtype, device=device)
+    if c.numel() == 0:
+        return c
+    m, n = out_shape[-2], out_shape[-1]
+    if a.dim() == 2:
+        bias = _normalise_bias(bias, m, n)
+        if residual is not None and (residual.shape != c.shape or residual.stride(-1) != 1):
+            residual = residual.expand(m, n).contiguous()
+    elif bias is not None or residual is not None:
+        if residual is not None or not (bias.dim() == 1 and bias.shape[0] == n):
+            raise RuntimeError("gemm: batched gemm takes only a 1-D [n] bias")
+        bias = bias.contiguous()
+    g = fill_gemm_args(a, b, bias, residual, c, alpha, beta, epilogue, route)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_gemm(ctypes.byref(g), None, 0, native.current_stream(device))
+    native.check("gemm", status)
+    _launched(device, start, "gemm", 2.0 * g.m * g.n * g.k * g.batch, _nbytes(a, b, c, bias, residual))
+    return c
+
+
+def _gemm_meta(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, out_dtype=None, route=0):
+    return torch.empty(_gemm_out_shape(a, b), dtype=out_dtype or a.dtype, device=a.device)
+
+
+# ---- sdpa -----------------------------------------------------------------------------------
+
+
+def _unit_last_stride(t):
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def fill_sdpa_args(q, k, v, o, lse, causal, scale, route) -> native.SdpaArgs:
+    s = native.SdpaArgs()
+    s.q, s.k, s.v, s.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    s.lse = _ptr(lse)
+    s.batch, s.heads, s.q_len, s.head_dim = q.shape
+    s.kv_len = k.shape[2]
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o)):
+        arr = getattr(s, name)
+        arr[0], arr[1], arr[2] = t.stride(0), t.stride(1), t.stride(2)
+    s.scale = scale
+    s.causal = int(causal)
+    s.dtype = native.dtype_enum(q.dtype)
+    s.route = route
+    return s
+
+
+def _sdpa_cuda(q, k, v, causal=False, scale=None, route=0):
+    device = native.require_cuda("sdpa", q, k, v)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise RuntimeError("sdpa: q, k, v must be [batch, heads, length, head_dim]")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("sdpa: q, k, v dtypes differ")
+    if k.shape[1] != q.shape[1] or v.shape[1] != q.shape[1]:
+        raise RuntimeError("sdpa: q, k, v must have the same number of heads (expand GQA heads first)")
+    if k.shape[2] != v.shape[2] or k.shape[3] != q.shape[3] or v.shape[3] != q.shape[3]:
+        raise RuntimeError("sdpa: inconsistent kv_len / head_dim")
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    q, k, v = _unit_last_stride(q), _unit_last_stride(k), _unit_last_stride(v)
+    B, H, T, D = q.shape
+    # Output laid out [B, T, H, D] in memory (returned as its [B, H, T, D] view): the layout the
+    # following `transpose(1, 2).view(B, T, C)` wants, so that it stays a view.
+    o = torch.empty((B, T, H, D), dtype=q.dtype, device=device).transpose(1, 2)
+    lse = torch.empty((B, H, T), dtype=torch.float32, device=device)
+    if o.numel() == 0:
+        return o, lse
+    s = fill_sdpa_args(q, k, v, o, lse, causal, scale, route)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_sdpa_fwd(ctypes.byref(s), native.current_stream(device))
+    native.check("sdpa", status)
+    flops = 4.0 * B * H * T * k.shape[2] * D * (0.5 if causal else 1.0)
+    _launched(device, start, "sdpa", flops, _nbytes(q, k, v, o))
+    return o, lse
+
+
+def _sdpa_meta(q, k, v, causal=False, scale=None, route=0):
+    B, H, T, D = q.shape
+    o = torch.empty((B, T, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
+    return o, torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+
+
+def _refuse_cpu(name):
+    def impl(*args, **kwargs):
+        raise RuntimeError(
+            f"b200::{name} was called with CPU tensors; the b200 kernels run on CUDA tensors only "
+            "and there is no CPU fallback."
+        )
+
+    return impl
+
+
+for _name, _cuda, _meta in (
+    ("layer_norm", _layer_norm_cuda, _layer_norm_meta),
+    ("softmax", _softmax_cuda, _softmax_meta),
+    ("gelu", _gelu_cuda, _gelu_meta),
+    ("reduce", _reduce_cuda, _reduce_meta),
+    ("gemm", _gemm_cuda, _gemm_meta),
+    ("sdpa", _sdpa_cuda, _sdpa_meta),
+):
+    _lib.impl(_name, _cuda, "CUDA")
+    _lib.impl(_name, _refuse_cpu(_name), "CPU")
+    torch.library.register_fake(f"b200::{_name}", _meta, lib=_lib)
+
+layer_norm = torch.ops.b200.layer_norm
+softmax = torch.ops.b200.softmax
+gelu = torch.ops.b200.gelu
+reduce = torch.ops.b200.reduce
+gemm = torch.ops.b200.gemm
+sdpa = torch.ops.b200.sdpa
