@@ -61,6 +61,38 @@ def test_sdpa_fused_qkv_strided_views_and_kv_longer(ops):
     assert_parity(out2, ref_ops.sdpa(q2, k2, v2, True)[0], bf16=False)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("q_len,kv_len", [(1, 1), (77, 300), (64, 200), (129, 129), (300, 77), (128, 64)])
+def test_sdpa_tensor_core_route_ragged_lengths(ops, causal, q_len, kv_len):
+    """head_dim 64 bf16 takes the tcgen05 kernel: ragged tiles, kv_len != q_len (causal mask is
+    top-left aligned), single-row and single-key cases; forced route so that a silent reroute fails."""
+    q = gen((2, 3, q_len, 64), torch.bfloat16, 30)
+    k = gen((2, 3, kv_len, 64), torch.bfloat16, 31)
+    v = gen((2, 3, kv_len, 64), torch.bfloat16, 32)
+    out, lse = ops.sdpa(q.cuda(), k.cuda(), v.cuda(), causal, None, 2)
+    want, want_lse = ref_ops.sdpa(q, k, v, causal)
+    assert_parity(out, want, bf16=True)
+    assert_parity(lse, want_lse, bf16=False, scale=max(want_lse.abs().max().item(), 1.0) * 10)
+
+
+def test_sdpa_route_selection(ops):
+    import ctypes
+
+    from torch_mojo_backend import native
+
+    def route(shape, dtype):
+        q = torch.empty(shape, dtype=dtype, device="cuda")
+        o = torch.empty(shape, dtype=dtype, device="cuda")
+        lse = torch.empty(shape[:3], device="cuda")
+        s = ops.fill_sdpa_args(q, q, q, o, lse, True, 0.125, 0)
+        return native.lib().b200_sdpa_route(ctypes.byref(s))
+
+    assert route((8, 12, 1024, 64), torch.bfloat16) == 2
+    assert route((4, 25, 2048, 64), torch.bfloat16) == 2
+    assert route((8, 12, 1024, 64), torch.float32) == 1   # exact-fp32 route
+    assert route((2, 2, 128, 128), torch.bfloat16) == 1   # head_dim other than 64
+
+
 @pytest.mark.parametrize("shape", [(8, 12, 1024, 64), (4, 25, 2048, 64)])
 def test_sdpa_benchmark_shapes_bf16(ops, shape):
     """The two causal bf16 configurations; oracle = PyTorch CPU SDPA in fp32 on the bf16 values."""

@@ -1,0 +1,220 @@
+"""Per-kernel timings for the GEMM sweep, the row ops and causal attention at the benchmark
+shapes, each reported against its roofline (measured HBM copy bandwidth / measured bf16 peak).
+
+  python torch-max-backend_b200/bench_kernels.py [--ops gemm,layer_norm,...] [--iters 50] [--quick]
+  python torch-max-backend_b200/bench_kernels.py --ops gemm --only "8192x768x2304" --iters 3 --no-graph   # for ncu
+
+Method (the reference's own protocol, bench_gemm.py:152-169, plus L2 hygiene): inputs rotate over
+enough copies to exceed twice the 126 MB L2, so every launch reads cold data; `iters` launches
+are captured in one CUDA graph and the replay is timed with CUDA events, so that microsecond
+kernels are not hidden behind Python launch overhead; at least 5 warm-up replays. Algorithmic
+work per launch: GEMM 2*M*N*K flops and s*(M*K + K*N + M*N + N) bytes (bench_gemm.py:239-240),
+row ops numel*size*(reads + writes), causal SDPA 4*B*H*T^2*d/2 flops.
+One JSON line per case on stdout.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT.parent):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import torch  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def peaks():
+    path = ROOT.parent / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def rotations(bytes_per_copy: float) -> int:
+    return int(max(2, min(64, -(-2 * L2_BYTES // max(1, int(bytes_per_copy))))))
+
+
+def time_case(make_inputs, run, bytes_per_copy, iters, use_graph):
+    """make_inputs(i) -> inputs of copy i; run(inputs) launches the kernel once."""
+    r = rotations(bytes_per_copy)
+    copies = [make_inputs(i) for i in range(r)]
+    for i in range(5):
+        run(copies[i % r])
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run(copies[0])
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                run(copies[i % r])
+        for _ in range(5):
+            graph.replay()
+        torch.cuda.synchronize()
+        reps = 3
+        start.record()
+        for _ in range(reps):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) * 1e3 / (iters * reps), r
+    start.record()
+    for i in range(iters):
+        run(copies[i % r])
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) * 1e3 / iters, r
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ops", default="gemm,layer_norm,softmax,gelu,reduce,sdpa")
+    ap.add_argument("--iters", type=int, default=40)
+    ap.add_argument("--only", default="", help="substring filter on the case name")
+    ap.add_argument("--no-graph", action="store_true", help="plain launches (what an ncu capture wants)")
+    ap.add_argument("--quick", action="store_true", help="skip the largest GEMM (N=50257 at M=8192)")
+    args = ap.parse_args()
+
+    from torch_mojo_backend import native, ops
+
+    native.lib()
+    dev = torch.device("cuda")
+    hbm, tf, src = peaks()
+    wanted = set(args.ops.split(","))
+    gen = torch.Generator(device="cuda").manual_seed(0)
+
+    def randn(shape, dtype, std=1.0, mean=0.0):
+        return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std + mean).to(dtype)
+
+    def report(name, us, rot, flops=0.0, nbytes=0.0, bound="hbm"):
+        line = {"case": name, "us": round(us, 3), "rotating_copies": rot, "bound": bound}
+        if flops:
+            line["tflops"] = round(flops / us / 1e6, 2)
+        if nbytes:
+            line["gbs"] = round(nbytes / us / 1e3, 1)
+        if bound == "tensor":
+            line["frac"] = round(flops / us / 1e6 / tf, 4)
+            line["peak"] = f"{tf} TFLOP/s bf16 burst, {src}"
+        else:
+            line["frac"] = round(nbytes / us / 1e3 / hbm, 4)
+            line["peak"] = f"{hbm} GB/s copy, {src}"
+        print(json.dumps(line), flush=True)
+
+    def keep(name):
+        return args.only in name
+
+    use_graph = not args.no_graph
+
+    if "gemm" in wanted:
+        kn = [(768, 2304), (768, 768), (768, 3072), (3072, 768), (1600, 4800), (1600, 6400), (6400, 1600)]
+        if not args.quick:
+            kn += [(768, 50257), (1600, 50257)]
+        for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+            for m in (8192, 64, 16, 1):
+                for k, n in kn:
+                    if dtype == torch.float32 and (n > 6400 or k > 3072) and m == 8192:
+                        continue
+                    for layout in ("nk", "kn"):
+                        name = f"gemm {dname} {m}x{k}x{n} B={layout} +bias"
+                        if not keep(name):
+                            continue
+                        s = 2 if dtype == torch.bfloat16 else 4
+                        nbytes = s * (m * k + k * n + m * n + n)
+
+                        def make(i, m=m, k=k, n=n, layout=layout, dtype=dtype):
+                            a = randn((m, k), dtype)
+                            b = randn((n, k), dtype).t() if layout == "nk" else randn((k, n), dtype)
+                            return a, b, randn((n,), dtype, 0.02)
+
+                        us, rot = time_case(make, lambda t: ops.gemm(t[0], t[1], t[2]), nbytes, args.iters, use_graph)
+                        bound = "tensor" if m >= 512 else "hbm"
+                        report(name, us, rot, 2.0 * m * n * k, nbytes, bound)
+
+    if "layer_norm" in wanted:
+        for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+            for rows, cols in ((8192, 768), (8192, 1600), (65536, 1600)):
+                name = f"layer_norm {dname} {rows}x{cols}"
+                if not keep(name):
+                    continue
+                s = 2 if dtype == torch.bfloat16 else 4
+                nbytes = 2 * rows * cols * s + 8 * rows
+                make = lambda i, rows=rows, cols=cols, dtype=dtype: (randn((rows, cols), dtype), randn((cols,), dtype, 0.02, 1.0), randn((cols,), dtype, 0.02))
+                us, rot = time_case(make, lambda t: ops.layer_norm(t[0], t[1], t[2], 1e-5), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+
+    if "softmax" in wanted:
+        for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+            shape = (96, 1024, 1024)
+            s = 2 if dtype == torch.bfloat16 else 4
+            nbytes = 2 * 96 * 1024 * 1024 * s
+            mask = torch.ones(1024, 1024, dtype=torch.bool, device=dev).tril()
+            name = f"softmax {dname} 96x1024x1024 pre-masked(-inf)"
+            if keep(name):
+                make = lambda i, dtype=dtype: (randn(shape, dtype).masked_fill_(~mask, float("-inf")),)
+                us, rot = time_case(make, lambda t: ops.softmax(t[0]), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+            name = f"softmax {dname} 96x1024x1024 fused scale+causal"
+            if keep(name):
+                make = lambda i, dtype=dtype: (randn(shape, dtype),)
+                us, rot = time_case(make, lambda t: ops.softmax(t[0], 0.125, True, 1024), nbytes, args.iters, use_graph)
+                # masked columns are never read: algorithmic bytes = half the reads + all the writes
+                report(name, us, rot, nbytes=0.75 * nbytes)
+
+    if "gelu" in wanted:
+        for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+            for approx in ("tanh", "none"):
+                name = f"gelu {dname} {approx} 8192x3072"
+                if not keep(name):
+                    continue
+                s = 2 if dtype == torch.bfloat16 else 4
+                nbytes = 2 * 8192 * 3072 * s
+                make = lambda i, dtype=dtype: (randn((8192, 3072), dtype),)
+                us, rot = time_case(make, lambda t, approx=approx: ops.gelu(t[0], approx), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+
+    if "reduce" in wanted:
+        for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+            for op, oname in ((0, "sum"), (1, "mean"), (2, "amax")):
+                name = f"reduce {oname} {dname} 8192x768"
+                if not keep(name):
+                    continue
+                s = 2 if dtype == torch.bfloat16 else 4
+                nbytes = 8192 * 768 * s
+                make = lambda i, dtype=dtype: (randn((8192, 768), dtype),)
+                us, rot = time_case(make, lambda t, op=op: ops.reduce(t[0], op), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+
+    if "sdpa" in wanted:
+        for B, H, T, D in ((8, 12, 1024, 64), (4, 25, 2048, 64), (8, 25, 1024, 64)):
+            name = f"sdpa bf16 causal {B}x{H}x{T}x{D}"
+            if not keep(name):
+                continue
+            nbytes = 4 * B * H * T * D * 2
+            flops = 4.0 * B * H * T * T * D / 2
+
+            def make(i, B=B, H=H, T=T, D=D):
+                qkv = randn((B, T, 3 * H * D), torch.bfloat16)
+                return tuple(t.view(B, T, H, D).transpose(1, 2) for t in qkv.split(H * D, dim=2))
+
+            us, rot = time_case(make, lambda t: ops.sdpa(t[0], t[1], t[2], True), nbytes, args.iters, use_graph)
+            report(name, us, rot, flops, nbytes, "tensor")
+
+    status = native.device_status()
+    if status != 0:
+        raise SystemExit(f"a kernel reported a bounded-wait timeout (status word {status:#x})")
+
+
+if __name__ == "__main__":
+    main()

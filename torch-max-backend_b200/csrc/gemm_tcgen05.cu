@@ -222,7 +222,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int64_t r = t - b * tiles_per_batch;
       const int64_t m0 = (r % p.tiles_m) * BM;
       const int64_t n0 = (r / p.tiles_m) * BN;
-      if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
+      // warp-uniform result: the TMEM loads below need the whole warp
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag))) break;
       ptx::tc_fence_after_sync();
       const int64_t row = m0 + q * 32 + lane;
       Tout* crow = C + b * p.c_bs + row * p.c_rs;

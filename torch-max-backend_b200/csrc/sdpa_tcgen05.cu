@@ -1,13 +1,439 @@
-// Causal attention forward on tcgen05/TMEM. Placeholder until the kernel lands: reports itself
-// ineligible so that the router never selects it.
+// Attention forward on the 5th-generation tensor cores for head_dim 64, bf16.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the 64-key tiles it may attend to.
+//   warp 0      TMA producer: Q once, then K_j / V_j into two 3-deep rings (128-byte swizzle).
+//   warp 1      MMA issuer: S_j = Q K_j^T into one of two TMEM score buffers, and, once the
+//               softmax warps have published P_j, O += P_j V_j into the TMEM output accumulator.
+//               S_{j+1} is issued before P_j is waited for, so the tensor core works on the next
+//               scores while the softmax of the current tile runs.
+//   warps 2-5   softmax, one thread per query row: pull S_j out of TMEM, online softmax in the
+//               exp2 domain with fp32 statistics, write P_j (rounded to bf16) into shared memory
+//               as the K-major A operand of the second MMA, and rescale O in TMEM when the
+//               running maximum moved. The rescale is lazy: the reference maximum only follows
+//               the true maximum when it is more than 8 (a factor 256) behind, which keeps P
+//               inside bf16/fp32 range and skips most TMEM round trips.
+// Two CTAs fit on one SM (80 KB of shared memory and 256 TMEM columns each), so the softmax of
+// one overlaps the MMAs of the other. The heaviest (last) query tiles are scheduled first.
+//
+// Numerics: scores scaled by scale*log2(e), P = exp2(s - m), masked scores are -inf, P is rounded
+// to bf16 before the second MMA, O is divided by the fp32 row sum once at the end, and the
+// natural-log LSE is (m + log2(l)) * ln 2.
+#include "ptx.cuh"
 #include "sdpa_internal.cuh"
+#include "tma.cuh"
 
 namespace b200 {
+namespace {
 
-const char* sdpa_tcgen05_ineligible(const b200_sdpa_args&) { return "no tensor-core attention kernel in this build"; }
+constexpr int BM = 128;   // query rows per CTA
+constexpr int BN = 64;    // keys per tile
+constexpr int D = 64;     // head_dim
+constexpr int kStages = 3;
+constexpr int kThreads = 192;
+constexpr int kSoftmaxThreads = 128;
+constexpr int Q_BYTES = BM * D * 2;     // 16 KiB
+constexpr int KV_BYTES = BN * D * 2;    // 8 KiB
+constexpr int P_BYTES = BM * BN * 2;    // 16 KiB
+constexpr int kTmemCols = 256;
+constexpr int TMEM_S0 = 0, TMEM_S1 = 64, TMEM_O = 128;
 
-int32_t launch_sdpa_tcgen05(const b200_sdpa_args&, cudaStream_t) {
-  B200_FAIL(B200_ERR_UNSUPPORTED, "sdpa(tcgen05): not built");
+constexpr int SMEM_Q = 0;
+constexpr int SMEM_K = SMEM_Q + Q_BYTES;
+constexpr int SMEM_V = SMEM_K + kStages * KV_BYTES;
+constexpr int SMEM_P = SMEM_V + kStages * KV_BYTES;
+constexpr int SMEM_BAR = SMEM_P + P_BYTES;
+// barriers: q_full, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], s_empty[2], p_full, pv_done
+constexpr int kNumBars = 1 + 4 * kStages + 4 + 2;
+constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
+constexpr int SMEM_BYTES = SMEM_MISC + 16 + 1024;
+
+struct Params {
+  __nv_bfloat16* o;
+  float* lse;
+  int64_t heads, q_len, kv_len;
+  int64_t os_b, os_h, os_t;
+  float scale_log2;  // scale * log2(e)
+  int causal;
+  int q_tiles;
+  int q_heads_inner, k_heads_inner, v_heads_inner;  // tensor map dim order is (d, head, pos, batch)
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ int kv_tiles_for(int64_t q0, int64_t q_len, int64_t kv_len, int causal) {
+  int64_t last_key = kv_len;  // exclusive
+  if (causal) {
+    const int64_t lim = q0 + BM;  // rows q0..q0+127 see keys <= row
+    if (lim < last_key) last_key = lim;
+  }
+  return (int)((last_key + BN - 1) / BN);
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t base = ptx::smem_u32(smem);
+  const uint32_t q_smem = base + SMEM_Q, k_smem = base + SMEM_K, v_smem = base + SMEM_V, p_smem = base + SMEM_P;
+  const uint32_t bar = base + SMEM_BAR;
+  const uint32_t q_full = bar;
+  auto k_full = [&](int s) { return bar + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar + 8u * (1 + kStages + s); };
+  auto v_full = [&](int s) { return bar + 8u * (1 + 2 * kStages + s); };
+  auto v_empty = [&](int s) { return bar + 8u * (1 + 3 * kStages + s); };
+  auto s_full = [&](int b) { return bar + 8u * (1 + 4 * kStages + b); };
+  auto s_empty = [&](int b) { return bar + 8u * (1 + 4 * kStages + 2 + b); };
+  const uint32_t p_full = bar + 8u * (1 + 4 * kStages + 4);
+  const uint32_t pv_done = bar + 8u * (1 + 4 * kStages + 5);
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + SMEM_MISC);
+  volatile uint32_t* tmem_holder = misc;
+  volatile uint32_t* abort_flag = misc + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heaviest query tiles first
+  const int q_tile = p.q_tiles - 1 - (int)blockIdx.x;
+  const int64_t bh = blockIdx.y;
+  const int32_t b = (int32_t)(bh / p.heads), h = (int32_t)(bh % p.heads);
+  const int64_t q0 = (int64_t)q_tile * BM;
+  const int n_tiles = kv_tiles_for(q0, p.q_len, p.kv_len, p.causal);
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(k_full(s), 1);
+      ptx::mbar_init(k_empty(s), 1);
+      ptx::mbar_init(v_full(s), 1);
+      ptx::mbar_init(v_empty(s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(s_full(i), 1);
+      ptx::mbar_init(s_empty(i), kSoftmaxThreads);
+    }
+    ptx::mbar_init(p_full, kSoftmaxThreads);
+    ptx::mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tmap_q);
+    ptx::prefetch_tensormap(&tmap_k);
+    ptx::prefetch_tensormap(&tmap_v);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem = *tmem_holder;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      ptx::mbar_arrive_expect_tx(q_full, Q_BYTES);
+      if (p.q_heads_inner) ptx::tma_load_4d(q_smem, &tmap_q, q_full, 0, h, (int32_t)q0, b);
+      else ptx::tma_load_4d(q_smem, &tmap_q, q_full, 0, (int32_t)q0, h, b);
+      int s = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int32_t kv0 = j * BN;
+        if (!ptx::mbar_wait(k_empty(s), phase ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(k_full(s), KV_BYTES);
+        if (p.k_heads_inner) ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, h, kv0, b);
+        else ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, kv0, h, b);
+        if (!ptx::mbar_wait(v_empty(s), phase ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(v_full(s), KV_BYTES);
+        if (p.v_heads_inner) ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, h, kv0, b);
+        else ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, kv0, h, b);
+        if (++s == kStages) { s = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = ptx::idesc_bf16_f32(BM, BN, 0, 0);
+      constexpr uint32_t idesc_pv = ptx::idesc_bf16_f32(BM, D, 0, 1);
+      auto issue_qk = [&](int j, int stage, uint32_t stage_phase) -> bool {
+        const int buf = j & 1;
+        // the score buffer must have been drained by the softmax warps (tile j-2)
+        if (!ptx::mbar_wait(s_empty(buf), ((uint32_t)(j >> 1) & 1) ^ 1, abort_flag)) return false;
+        if (!ptx::mbar_wait(k_full(stage), stage_phase, abort_flag)) return false;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem + (buf ? TMEM_S1 : TMEM_S0);
+        const uint32_t kb = k_smem + stage * KV_BYTES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
+          const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
+          ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
+        }
+        ptx::tc_commit(k_empty(stage));
+        ptx::tc_commit(s_full(buf));
+        return true;
+      };
+      bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
+      int ks = 0;
+      uint32_t kphase = 0;  // ring position of the next K tile to multiply
+      int vs = 0;
+      uint32_t vphase = 0;  // ring position of the next V tile to multiply
+      if (ok && n_tiles > 0) {
+        ok = issue_qk(0, ks, kphase);
+        if (++ks == kStages) { ks = 0; kphase ^= 1; }
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          ok = issue_qk(j + 1, ks, kphase);
+          if (++ks == kStages) { ks = 0; kphase ^= 1; }
+          if (!ok) break;
+        }
+        if (!ptx::mbar_wait(p_full, (uint32_t)j & 1, abort_flag)) { ok = false; break; }
+        if (!ptx::mbar_wait(v_full(vs), vphase, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t vb = v_smem + vs * KV_BYTES;
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint64_t a_desc = ptx::smem_desc_sw128(p_smem + k * 32, 0, 1024);
+          // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
+          const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
+          ptx::mma_f16_ss(tmem + TMEM_O, a_desc, b_desc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        ptx::tc_commit(v_empty(vs));
+        ptx::tc_commit(pv_done);
+        if (++vs == kStages) { vs = 0; vphase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------- softmax + output (warps 2..5), one thread per query row ----------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;          // row inside the tile == TMEM lane
+    const int64_t row = q0 + r;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    float m_ref = -INFINITY;  // maximum the stored P / O are relative to (log2 domain)
+    float l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int buf = j & 1;
+      // wait results are made warp-uniform: the TMEM loads and votes below need the whole warp
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(buf), (uint32_t)(j >> 1) & 1, abort_flag))) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      uint32_t raw[2][32];
+      const uint32_t s_addr = tmem + (buf ? TMEM_S1 : TMEM_S0) + lane_addr;
+      ptx::tmem_ld_32x32b_x32(s_addr, raw[0]);
+      ptx::tmem_ld_32x32b_x32(s_addr + 32, raw[1]);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(s_empty(buf));
+
+      const int64_t kv0 = (int64_t)j * BN;
+      const bool need_mask = (p.causal && kv0 + BN - 1 > q0) || (kv0 + BN > p.kv_len);
+      float x[64];
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float v = __uint_as_float(raw[c >> 5][c & 31]) * p.scale_log2;
+        if (need_mask) {
+          const int64_t key = kv0 + c;
+          if (key >= p.kv_len || (p.causal && key > row)) v = -INFINITY;
+        }
+        x[c] = v;
+        tile_max = fmaxf(tile_max, v);
+      }
+      // lazy rescale: follow the true maximum only when it ran away by more than 2^8
+      float alpha = 1.0f;
+      if (tile_max > m_ref + 8.0f) {
+        alpha = ex2(m_ref - tile_max);  // m_ref == -inf on the first tile: alpha = 0
+        m_ref = tile_max;
+        l *= alpha;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+      uint32_t packed[32];
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = ex2(x[c] - m_use);
+        const float p1 = ex2(x[c + 1] - m_use);
+        sum += p0 + p1;
+        packed[c >> 1] = pack_bf16x2(p0, p1);
+      }
+      l += sum;
+
+      // P buffer and O accumulator are free once the previous P V has completed
+      if (j > 0) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag))) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+          uint32_t o[2][32];
+          ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
+          ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            o[0][c] = __float_as_uint(__uint_as_float(o[0][c]) * alpha);
+            o[1][c] = __float_as_uint(__uint_as_float(o[1][c]) * alpha);
+          }
+          ptx::tmem_st_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
+          ptx::tmem_st_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
+          ptx::tmem_st_wait();
+        }
+      }
+      // P row r, 64 bf16 = 8 chunks of 16 bytes, 128-byte swizzle: chunk index XOR (row mod 8)
+      {
+        uint8_t* prow = smem + SMEM_P + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v4;
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(p_full);
+    }
+
+    if (ok && n_tiles > 0)
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag));
+    if (ok) {
+      ptx::tc_fence_after_sync();
+      float ov[64];
+      if (n_tiles > 0) {
+        uint32_t o[2][32];
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 64; ++c) ov[c] = __uint_as_float(o[c >> 5][c & 31]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) ov[c] = 0.0f;
+      }
+      if (row < p.q_len) {
+        const float inv = 1.0f / l;  // l == 0 (no visible key) gives NaN like torch
+        __nv_bfloat16* orow = p.o + b * p.os_b + h * p.os_h + row * p.os_t;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 t;
+          t.x = pack_bf16x2(ov[8 * c] * inv, ov[8 * c + 1] * inv);
+          t.y = pack_bf16x2(ov[8 * c + 2] * inv, ov[8 * c + 3] * inv);
+          t.z = pack_bf16x2(ov[8 * c + 4] * inv, ov[8 * c + 5] * inv);
+          t.w = pack_bf16x2(ov[8 * c + 6] * inv, ov[8 * c + 7] * inv);
+          reinterpret_cast<uint4*>(orow)[c] = t;
+        }
+        if (p.lse != nullptr)
+          p.lse[((int64_t)b * p.heads + h) * p.q_len + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    if (threadIdx.x == 0) atomicOr(p.status, STATUS_SDPA_TIMEOUT);
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// Byte strides of the (position, head, batch) dims with legal stand-ins for size-1 dims.
+void byte_strides(const int64_t* s, int64_t batch, int64_t heads, int64_t len, uint64_t* st, uint64_t* sh,
+                  uint64_t* sb) {
+  *st = (uint64_t)(len > 1 ? s[2] : D) * 2;
+  *sh = heads > 1 ? (uint64_t)s[1] * 2 : *st * (uint64_t)(len > 0 ? len : 1);
+  const uint64_t big = (*st * (uint64_t)len > *sh * (uint64_t)heads) ? *st * (uint64_t)len : *sh * (uint64_t)heads;
+  *sb = batch > 1 ? (uint64_t)s[0] * 2 : big;
+}
+
+// Tensor map over [batch, heads, len, 64]. Dims are listed innermost first with ascending
+// strides: (d, pos, head, batch) for a [B, H, T, D]-contiguous tensor, (d, head, pos, batch) for
+// views of a [B, T, H*D] projection. *heads_inner tells the kernel which coordinate order to use.
+int32_t make_map(CUtensorMap* map, const void* ptr, int64_t batch, int64_t heads, int64_t len,
+                 const int64_t* strides, int rows_per_box, int* heads_inner) {
+  uint64_t st, sh, sb;
+  byte_strides(strides, batch, heads, len, &st, &sh, &sb);
+  *heads_inner = sh < st ? 1 : 0;
+  if (*heads_inner) {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)heads, (uint64_t)len, (uint64_t)batch};
+    const uint64_t str[3] = {sh, st, sb};
+    const uint32_t box[4] = {(uint32_t)D, 1, (uint32_t)rows_per_box, 1};
+    return encode_tensor_map(map, B200_BF16, 4, ptr, dims, str, box, true);
+  }
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)len, (uint64_t)heads, (uint64_t)batch};
+  const uint64_t str[3] = {st, sh, sb};
+  const uint32_t box[4] = {(uint32_t)D, (uint32_t)rows_per_box, 1, 1};
+  return encode_tensor_map(map, B200_BF16, 4, ptr, dims, str, box, true);
+}
+
+bool strides_ok(const int64_t* s, int64_t batch, int64_t heads, int64_t len) {
+  if (len > 1 && (s[2] % 8 != 0 || s[2] < D)) return false;
+  if (heads > 1 && (s[1] % 8 != 0 || s[1] < D)) return false;
+  if (batch > 1 && (s[0] % 8 != 0 || s[0] < D)) return false;
+  uint64_t st, sh, sb;
+  byte_strides(s, batch, heads, len, &st, &sh, &sb);
+  if (sb < st || sb < sh) return false;  // batch must be the outermost dim
+  return true;
+}
+
+}  // namespace
+
+const char* sdpa_tcgen05_ineligible(const b200_sdpa_args& a) {
+  if (a.dtype != B200_BF16) return "tensors are not bf16";
+  if (a.head_dim != D) return "head_dim is not 64";
+  if (a.kv_len == 0) return "kv_len is zero";
+  if (!aligned_to(a.q, 16) || !aligned_to(a.k, 16) || !aligned_to(a.v, 16) || !aligned_to(a.o, 16))
+    return "pointer not 16-byte aligned";
+  if (!strides_ok(a.q_strides, a.batch, a.heads, a.q_len) || !strides_ok(a.k_strides, a.batch, a.heads, a.kv_len) ||
+      !strides_ok(a.v_strides, a.batch, a.heads, a.kv_len))
+    return "stride not a multiple of 16 bytes";
+  if (a.o_strides[2] % 8 != 0 || a.o_strides[1] % 8 != 0 || a.o_strides[0] % 8 != 0)
+    return "output stride not a multiple of 16 bytes";
+  if (a.batch * a.heads > 65535) return "batch*heads above 65535";
+  if (a.q_len > INT32_MAX - 256 || a.kv_len > INT32_MAX - 256) return "sequence too long";
+  return nullptr;
+}
+
+int32_t launch_sdpa_tcgen05(const b200_sdpa_args& a, cudaStream_t stream) {
+  CUtensorMap mq, mk, mv;
+  Params p;
+  int32_t st = make_map(&mq, a.q, a.batch, a.heads, a.q_len, a.q_strides, BM, &p.q_heads_inner);
+  if (st != B200_OK) return st;
+  st = make_map(&mk, a.k, a.batch, a.heads, a.kv_len, a.k_strides, BN, &p.k_heads_inner);
+  if (st != B200_OK) return st;
+  st = make_map(&mv, a.v, a.batch, a.heads, a.kv_len, a.v_strides, BN, &p.v_heads_inner);
+  if (st != B200_OK) return st;
+
+  p.o = static_cast<__nv_bfloat16*>(a.o);
+  p.lse = a.lse;
+  p.heads = a.heads; p.q_len = a.q_len; p.kv_len = a.kv_len;
+  p.os_b = a.o_strides[0]; p.os_h = a.o_strides[1]; p.os_t = a.o_strides[2];
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.causal = a.causal;
+  p.q_tiles = (int)((a.q_len + BM - 1) / BM);
+  p.status = device_status_ptr();
+  B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "sdpa(tcgen05): device status word unavailable");
+
+  static thread_local bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(sdpa_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess)
+      B200_FAIL(B200_ERR_CUDA, "sdpa(tcgen05): cannot opt in to %d bytes of shared memory: %s", SMEM_BYTES,
+                cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  dim3 grid((unsigned)p.q_tiles, (unsigned)(a.batch * a.heads));
+  sdpa_tcgen05_kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(mq, mk, mv, p);
+  B200_CHECK_LAUNCH("sdpa(tcgen05)");
+  return B200_OK;
 }
 
 }  // namespace b200

@@ -265,6 +265,22 @@ def aten_amax(input, dim=[], keepdim=False):
 # ==============================================================================================
 
 
+def _lse_as_traced(lse, index=1):
+    """The log-sum-exp output in the shape the traced graph recorded for this overload
+    ([B, H, T] for flash, [B, H, T, 1] for cuDNN, [B, H, 0] for efficient attention without
+    compute_log_sumexp)."""
+    node = CURRENT_FX_NODE.get()
+    val = node.meta.get("val") if node is not None else None
+    if not isinstance(val, (tuple, list)) or index >= len(val) or not isinstance(val[index], torch.Tensor):
+        return lse
+    want = tuple(val[index].shape)
+    if want == tuple(lse.shape):
+        return lse
+    if all(isinstance(d, int) for d in want) and math.prod(want) == lse.numel():
+        return lse.reshape(want)
+    return lse.new_empty(want)
+
+
 def _sdpa_kernel(query, key, value, is_causal, scale):
     """[B, H, T, D] attention through the kernel; 3-D inputs are treated as one batch."""
     squeeze = query.dim() == 3
@@ -297,7 +313,7 @@ def aten__scaled_dot_product_flash_attention(
     rng = torch.zeros((2,), dtype=torch.int64, device=dev)
     unused = torch.zeros((), dtype=torch.int64, device=dev)
     debug_mask = torch.zeros((), dtype=out.dtype, device=dev)
-    return (out, lse, None, None, query.shape[2], key.shape[2], rng, unused, debug_mask)
+    return (out, _lse_as_traced(lse), None, None, query.shape[2], key.shape[2], rng, unused, debug_mask)
 
 
 # _scaled_dot_product_efficient_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_bias,
@@ -315,8 +331,10 @@ def aten__scaled_dot_product_efficient_attention(
     else:
         out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
     dev = out.device
+    if not compute_log_sumexp:
+        lse = lse.new_empty((*lse.shape[:-1], 0))
     seed = torch.zeros((), dtype=torch.int64, device=dev)
-    return out, lse, seed, seed.clone()
+    return out, _lse_as_traced(lse), seed, seed.clone()
 
 
 # _scaled_dot_product_cudnn_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_bias,
@@ -336,7 +354,7 @@ def aten__scaled_dot_product_cudnn_attention(
         out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
     dev = out.device
     rng = torch.zeros((), dtype=torch.int64, device=dev)
-    return (out, lse, None, None, query.shape[2], key.shape[2], rng, rng.clone(), None)
+    return (out, _lse_as_traced(lse.unsqueeze(-1)), None, None, query.shape[2], key.shape[2], rng, rng.clone(), None)
 
 
 def _sdpa_math(query, key, value, attn_mask, is_causal, scale):

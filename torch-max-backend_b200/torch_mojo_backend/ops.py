@@ -63,7 +63,7 @@ def _as_rows(x: torch.Tensor) -> tuple[torch.Tensor, int, int, int]:
     """View x as [rows, cols] with a unit column stride and one row stride (copying only when
     the layout cannot be described that way). Returns (tensor, rows, cols, row_stride)."""
     cols = x.shape[-1] if x.dim() > 0 else 1
-    rows = x.numel() // cols if cols > 0 else 0
+    rows = math.prod(x.shape[:-1]) if x.dim() > 0 else 1
     if x.dim() == 0:
         return x.reshape(1, 1), 1, 1, 1
     if x.is_contiguous():
