@@ -416,6 +416,58 @@ def aten_scaled_dot_product_attention(
 
 
 # ==============================================================================================
+# Fused forms produced by torch_compile_backend/fusion.py (registered under themselves)
+# ==============================================================================================
+
+
+def _count_calls(fn):
+    if not torch_mojo_backend.is_running_tests.IS_RUNNING_TESTS:
+        return fn
+
+    @functools.wraps(fn)
+    def counted(*args, **kwargs):
+        counted.call_count += 1
+        return fn(*args, **kwargs)
+
+    counted.call_count = 0
+    return counted
+
+
+@_count_calls
+def fused_layer_norm(input, normalized_shape, weight, bias, eps, *, out_dtype):
+    """native_layer_norm whose only consumer was a dtype cast of output 0: the kernel writes
+    `out_dtype` directly from its fp32 registers."""
+    k = len(normalized_shape)
+    lead = input.shape[: input.dim() - k]
+    cols = math.prod(normalized_shape)
+    w = weight.reshape(cols) if weight is not None else None
+    b = bias.reshape(cols) if bias is not None else None
+    y, _, _ = ops.layer_norm(input.reshape(*lead, cols), w, b, eps, out_dtype)
+    return y.reshape(input.shape)
+
+
+@_count_calls
+def fused_gemm(a, b, bias, residual, *, alpha, beta, epilogue, out_dtype, out_shape):
+    """addmm / mm followed by (views,) gelu, an fp32 cast and/or a residual add, as one GEMM:
+    out = act(alpha * a @ b + beta * bias) + residual, stored as `out_dtype`, viewed as `out_shape`."""
+    n = b.shape[-1]
+    res2d = residual.reshape(-1, n) if residual is not None else None
+    y = ops.gemm(a, b, bias, res2d, alpha, beta, epilogue, out_dtype)
+    return y.view(out_shape)
+
+
+@_count_calls
+def contiguous_or_alias(x):
+    """`clone(memory_format=contiguous)` of a fresh kernel output: no copy when the memory is
+    already in that order."""
+    return x if x.is_contiguous() else x.contiguous()
+
+
+for _fused in (fused_layer_norm, fused_gemm, contiguous_or_alias):
+    MAPPING_TORCH_ATEN_TO_MOJO[_fused] = _fused
+
+
+# ==============================================================================================
 # Glue: ops kept whole and executed by stock torch on CUDA views
 # ==============================================================================================
 

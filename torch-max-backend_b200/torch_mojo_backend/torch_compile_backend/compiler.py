@@ -37,7 +37,7 @@ from torch_mojo_backend.aten_functions import (
     MAPPING_TORCH_ATEN_TO_MOJO,
 )
 from torch_mojo_backend.flags import cuda_graphs_enabled, profiling_enabled, verbose_enabled
-from torch_mojo_backend.torch_compile_backend import debug
+from torch_mojo_backend.torch_compile_backend import debug, fusion
 from torch_mojo_backend.torch_compile_backend.utils import (
     get_accelerators,
     get_error_message,
@@ -472,6 +472,10 @@ class BaseMaxCompiler:
             gather_stats_on_graph(gm)
             gm.graph.print_tabular()
 
+        if fusion.fusion_enabled():
+            fusion_stats = fusion.fuse_graph(gm)
+            if verbose_enabled():
+                print(f"Fused chains: {fusion_stats}")
         self.plan, self.output_blueprint = _GraphFactory().create_graph(gm.graph)
         self._graph_runner = None
         if verbose_enabled():

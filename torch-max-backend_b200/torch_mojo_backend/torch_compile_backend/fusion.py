@@ -1,0 +1,213 @@
+"""Graph-level fusion run on the aten FX graph before the launch plan is built.
+
+The reference leaves fusion to MAX (its lowerings emit separate matmul / mul / add graph ops,
+torch_mojo_backend/aten_functions.py:970-992, and MAX fuses elementwise chains). Here the kernels
+are hand-written, so the chains that matter are matched explicitly and folded into kernel
+epilogues:
+
+  * `native_layer_norm -> getitem[0] -> _to_copy(dtype)`         => LayerNorm that writes `dtype`
+  * `addmm | mm -> views -> [gelu] -> views -> [_to_copy(float32)] -> views -> [add(residual, .)]`
+        => one GEMM whose epilogue applies bias, GELU, the residual add and the output dtype to
+           the fp32 accumulator (an fp32 result is stored as computed, without the intermediate
+           bf16 rounding the unfused graph would do)
+  * `sdpa -> getitem[0] -> transpose -> clone(contiguous)`        => no copy: the attention kernel
+        already writes its output in the [B, T, H, D] order that `clone` would produce
+
+Every intermediate node of a chain must have exactly one user; chains with symbolic shapes are
+left alone. Fused nodes call functions registered in MAPPING_TORCH_ATEN_TO_MOJO under themselves,
+so the graph walk treats them like any other lowering. TORCH_MOJO_BACKEND_NO_FUSION=1 disables
+the pass.
+"""
+
+from __future__ import annotations
+
+import operator
+import os
+
+import torch
+
+from torch_mojo_backend import aten_functions as af
+from torch_mojo_backend import native
+
+aten = torch.ops.aten
+
+VIEW_OPS = (aten.view.default, aten._unsafe_view.default, aten.reshape.default)
+ALIAS_OPS = VIEW_OPS + (aten.transpose.int, aten.permute.default, aten.t.default, operator.getitem)
+SDPA_OPS = (
+    aten._scaled_dot_product_flash_attention.default,
+    aten._scaled_dot_product_efficient_attention.default,
+    aten._scaled_dot_product_cudnn_attention.default,
+    aten.scaled_dot_product_attention.default,
+)
+
+
+def fusion_enabled() -> bool:
+    return os.environ.get("TORCH_MOJO_BACKEND_NO_FUSION", "0").lower() not in ("1", "true", "yes")
+
+
+def _val(node):
+    return node.meta.get("val") if isinstance(node, torch.fx.Node) else None
+
+
+def _static_tensor(node) -> bool:
+    v = _val(node)
+    return isinstance(v, torch.Tensor) and all(isinstance(d, int) for d in v.shape)
+
+
+def _only_user(node):
+    if len(node.users) != 1:
+        return None
+    return next(iter(node.users))
+
+
+def _is_call(node, *targets) -> bool:
+    return node is not None and node.op == "call_function" and node.target in targets
+
+
+def _skip_views(node):
+    while True:
+        user = _only_user(node)
+        if _is_call(user, *VIEW_OPS) and user.args[0] is node and _static_tensor(user):
+            node = user
+        else:
+            return node
+
+
+def _plain_cast(node) -> torch.dtype | None:
+    """dtype of a `_to_copy` that only changes dtype, else None."""
+    if not _is_call(node, aten._to_copy.default):
+        return None
+    for key, value in node.kwargs.items():
+        if key == "dtype":
+            continue
+        if value not in (None, False):
+            return None
+    return node.kwargs.get("dtype")
+
+
+def _replace(graph, old, func, args, kwargs):
+    with graph.inserting_after(old):
+        new = graph.call_function(func, args=args, kwargs=kwargs)
+    new.meta = dict(old.meta)
+    old.replace_all_uses_with(new)
+    return new
+
+
+def _fuse_layer_norm(graph) -> int:
+    count = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten.native_layer_norm.default):
+            continue
+        get0 = _only_user(node)
+        if not (_is_call(get0, operator.getitem) and get0.args[1] == 0):
+            continue
+        cast = _only_user(get0)
+        dtype = _plain_cast(cast)
+        x = _val(node.args[0])
+        if dtype is None or not native.supported_dtype(dtype) or not isinstance(x, torch.Tensor):
+            continue
+        if not native.supported_dtype(x.dtype):
+            continue
+        _replace(graph, cast, af.fused_layer_norm, tuple(node.args), {"out_dtype": dtype})
+        count += 1
+    return count
+
+
+def _fuse_gemm_epilogues(graph) -> int:
+    count = 0
+    for node in list(graph.nodes):
+        if _is_call(node, aten.addmm.default):
+            bias, a, b = node.args[:3]
+            alpha, beta = node.kwargs.get("alpha", 1), node.kwargs.get("beta", 1)
+        elif _is_call(node, aten.mm.default):
+            a, b = node.args[:2]
+            bias, alpha, beta = None, 1, 1
+        else:
+            continue
+        va, vb = _val(a), _val(b)
+        if not (_static_tensor(node) and isinstance(va, torch.Tensor) and isinstance(vb, torch.Tensor)):
+            continue
+        if va.dtype != vb.dtype or not native.supported_dtype(va.dtype):
+            continue
+        if bias is not None and not native.supported_dtype(_val(bias).dtype):
+            continue
+        if not isinstance(alpha, (int, float)) or not isinstance(beta, (int, float)):
+            continue
+
+        epilogue, out_dtype, residual = native.EPILOGUE_NONE, None, None
+        cur = _skip_views(node)
+        user = _only_user(cur)
+        if _is_call(user, aten.gelu.default) and user.args[0] is cur:
+            approximate = user.kwargs.get("approximate", "none")
+            epilogue = native.EPILOGUE_GELU_TANH if approximate == "tanh" else native.EPILOGUE_GELU_ERF
+            cur = _skip_views(user)
+            user = _only_user(cur)
+        if _plain_cast(user) == torch.float32 and user.args[0] is cur and _static_tensor(user):
+            out_dtype = torch.float32
+            cur = _skip_views(user)
+            user = _only_user(cur)
+        if (
+            _is_call(user, aten.add.Tensor)
+            and user.kwargs.get("alpha", 1) == 1
+            and len(user.args) == 2
+            and all(isinstance(x, torch.fx.Node) for x in user.args)
+            and _static_tensor(user)
+        ):
+            other = user.args[1] if user.args[0] is cur else user.args[0]
+            vo, vc = _val(other), _val(cur)
+            if (
+                other is not cur
+                and isinstance(vo, torch.Tensor)
+                and tuple(vo.shape) == tuple(vc.shape) == tuple(_val(user).shape)
+                and native.supported_dtype(vo.dtype)
+                and _val(user).dtype == (out_dtype or va.dtype)
+            ):
+                residual = other
+                cur = user
+        if epilogue == native.EPILOGUE_NONE and out_dtype is None and residual is None:
+            continue
+        out_val = _val(cur)
+        _replace(
+            graph, cur, af.fused_gemm, (a, b, bias, residual),
+            {"alpha": float(alpha), "beta": float(beta), "epilogue": epilogue,
+             "out_dtype": out_val.dtype, "out_shape": [int(d) for d in out_val.shape]},
+        )
+        count += 1
+    return count
+
+
+def _alias_root(node):
+    while _is_call(node, *ALIAS_OPS):
+        node = node.args[0]
+    return node
+
+
+def _drop_attention_output_copies(graph) -> int:
+    count = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten.clone.default):
+            continue
+        if node.kwargs.get("memory_format") not in (None, torch.contiguous_format):
+            continue
+        root = _alias_root(node.args[0])
+        if not _is_call(root, *SDPA_OPS):
+            continue
+        # a fresh kernel output that nothing mutates: an alias is indistinguishable from a copy
+        _replace(graph, node, af.contiguous_or_alias, (node.args[0],), {})
+        count += 1
+    return count
+
+
+def fuse_graph(gm: torch.fx.GraphModule) -> dict[str, int]:
+    """Rewrites gm.graph in place and returns how many chains of each kind were folded."""
+    graph = gm.graph
+    stats = {
+        "layer_norm_cast": _fuse_layer_norm(graph),
+        "gemm_epilogue": _fuse_gemm_epilogues(graph),
+        "attention_output_copy": _drop_attention_output_copies(graph),
+    }
+    if any(stats.values()):
+        graph.eliminate_dead_code()
+        graph.lint()
+        gm.recompile()
+    return stats
