@@ -6,12 +6,17 @@
 //   warp 1      MMA issuer: one lane waits `full[s]`, issues BK/16 tcgen05.mma (128 x BN x 16)
 //               per stage into one of two TMEM accumulators, and commits to `empty[s]`; after
 //               the last k-block it commits to `tmem_full[acc]`.
-//   warps 2-5   epilogue: wait `tmem_full[acc]`, pull the accumulator out of TMEM 32 columns at
-//               a time, apply alpha/bias/activation/residual, convert and store, then release the
-//               accumulator through `tmem_empty[acc]`. The two accumulators let the epilogue of
-//               tile i overlap the main loop of tile i+1.
+//   warps 2-9   epilogue: wait `tmem_full[acc]`; each warp owns 32 rows (its TMEM lane quadrant)
+//               and half of the tile's columns. 32x32 chunks leave TMEM one row per lane, pass
+//               through a per-warp swizzled shared-memory staging buffer and come back one
+//               16-byte column group per lane, so that bias, residual and output accesses are
+//               coalesced (8 lanes cover a 128-byte row segment); alpha/bias/activation/residual
+//               are applied there, then the accumulator is released through `tmem_empty[acc]`.
+//               Two accumulators let the epilogue of tile i overlap the main loop of tile i+1.
 //
-// Tiles are walked M-fastest so that the CTAs running at any moment share a few B tiles in L2.
+// Tiles are walked in bands of kBandM row-tiles (column-tile outer, row-tile inner inside a band):
+// a band's slice of A is re-used from L2 across all its column tiles while the (smaller) B stays
+// L2-resident.
 // Every wait is bounded (ptx::mbar_wait); a CTA that gives up raises the device status word and
 // leaves through the common teardown, which frees its TMEM.
 #include "gemm_internal.cuh"
@@ -24,8 +29,11 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;                  // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kThreads = 64 + kEpilogueThreads;
+constexpr int kStageChunkBytes = 32 * 32 * 4;  // one 32x32 fp32 chunk per epilogue warp
+constexpr int kBandM = 16;                     // row-tiles per raster band
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 
 template <int BN>
@@ -35,7 +43,8 @@ struct Cfg {
   static constexpr int kTmemCols = 2 * BN;  // two accumulators; 256 or 512 (powers of two)
   static constexpr int kSmemA = 0;
   static constexpr int kSmemB = kStages * A_STAGE_BYTES;
-  static constexpr int kSmemBar = kSmemB + kStages * B_STAGE_BYTES;
+  static constexpr int kSmemStaging = kSmemB + kStages * B_STAGE_BYTES;
+  static constexpr int kSmemBar = kSmemStaging + kEpilogueWarps * kStageChunkBytes;
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kSmemMisc = kSmemBar + kNumBars * 8;
   static constexpr int kSmemBytes = kSmemMisc + 16 + 1024;  // +1024: manual 1 KiB alignment
@@ -54,11 +63,6 @@ struct Params {
   unsigned int* status;
 };
 
-__device__ __forceinline__ float ld_param(const void* p, int64_t idx, int32_t dtype) {
-  return dtype == B200_F32 ? __ldg(static_cast<const float*>(p) + idx)
-                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
-}
-
 __device__ __forceinline__ float act(float v, int32_t epilogue) {
   if (epilogue == B200_EPILOGUE_GELU_TANH) {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
@@ -69,33 +73,63 @@ __device__ __forceinline__ float act(float v, int32_t epilogue) {
   return v;
 }
 
-__device__ __forceinline__ void store_chunk(float* dst, const float (&v)[32], int valid) {
-  if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+// Tile index -> (batch, row-tile, column-tile): bands of kBandM row-tiles, column-tile outer,
+// row-tile inner inside a band.
+__device__ __forceinline__ void tile_coords(int64_t t, const Params& p, int64_t& b, int32_t& mt, int32_t& nt) {
+  const int64_t per_batch = (int64_t)p.tiles_m * p.tiles_n;
+  b = t / per_batch;
+  const int64_t r = t - b * per_batch;
+  const int64_t band_tiles = (int64_t)kBandM * p.tiles_n;
+  const int32_t band = (int32_t)(r / band_tiles);
+  const int32_t in_band = (int32_t)(r - (int64_t)band * band_tiles);
+  const int32_t rows_in_band = min(kBandM, p.tiles_m - band * kBandM);
+  nt = in_band / rows_in_band;
+  mt = band * kBandM + in_band % rows_in_band;
+}
+
+__device__ __forceinline__ void load4(const void* p, int64_t idx, int32_t dtype, int valid, float (&out)[4]) {
+  if (dtype == B200_F32) {
+    const float* q = static_cast<const float*>(p) + idx;
+    if (valid == 4 && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
+      const float4 t = __ldg(reinterpret_cast<const float4*>(q));
+      out[0] = t.x; out[1] = t.y; out[2] = t.z; out[3] = t.w;
+    } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      for (int j = 0; j < 4; ++j) out[j] = j < valid ? __ldg(q + j) : 0.0f;
+    }
   } else {
+    const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(p) + idx;
+    if (valid == 4 && (reinterpret_cast<uintptr_t>(q) & 7) == 0) {
+      const uint2 t = __ldg(reinterpret_cast<const uint2*>(q));
+      out[0] = __uint_as_float(t.x << 16); out[1] = __uint_as_float(t.x & 0xffff0000u);
+      out[2] = __uint_as_float(t.y << 16); out[3] = __uint_as_float(t.y & 0xffff0000u);
+    } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < valid) dst[i] = v[i];
+      for (int j = 0; j < 4; ++j) out[j] = j < valid ? __bfloat162float(q[j]) : 0.0f;
+    }
   }
 }
 
-__device__ __forceinline__ void store_chunk(__nv_bfloat16* dst, const float (&v)[32], int valid) {
-  if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint4 t;
-      t.x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
-      t.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-      t.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-      t.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-      reinterpret_cast<uint4*>(dst)[i] = t;
-    }
+__device__ __forceinline__ void store4(float* dst, const float (&v)[4], int valid) {
+  if (valid == 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
+    for (int j = 0; j < 4; ++j)
+      if (j < valid) dst[j] = v[j];
+  }
+}
+
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, const float (&v)[4], int valid) {
+  if (valid == 4 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+    uint2 t;
+    t.x = pack_bf16x2(v[0], v[1]);
+    t.y = pack_bf16x2(v[2], v[3]);
+    *reinterpret_cast<uint2*>(dst) = t;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (j < valid) dst[j] = __float2bfloat16_rn(v[j]);
   }
 }
 
@@ -147,7 +181,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = *tmem_holder;
 
   const int64_t num_kb = (p.K + BK - 1) / BK;
-  const int64_t tiles_per_batch = (int64_t)p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -156,12 +189,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        const int64_t b = t / tiles_per_batch;
-        const int64_t r = t - b * tiles_per_batch;
-        const int32_t m0 = (int32_t)(r % p.tiles_m) * BM;
-        const int32_t n0 = (int32_t)(r / p.tiles_m) * BN;
+        int64_t b;
+        int32_t mt, nt;
+        tile_coords(t, p, b, mt, nt);
+        const int32_t m0 = mt * BM, n0 = nt * BN;
         for (int64_t kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait_relaxed(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
           ptx::mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + C_::B_STAGE_BYTES);
           const int32_t k0 = (int32_t)(kb * BK);
           ptx::tma_load_3d(a_base + s * A_STAGE_BYTES, &tmap_a, full_bar(s), k0, m0, (int32_t)b);
@@ -213,50 +246,78 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    const int q = warp & 3;  // TMEM lane quadrant this warp may access
+    // ---------------- epilogue (warps 2..9) ----------------
+    const int q = warp & 3;              // TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;    // which half of the tile's columns
+    constexpr int kChunks = BN / 64;     // 32-column chunks per warp
+    float* stage = reinterpret_cast<float*>(smem + C_::kSmemStaging + (warp - 2) * kStageChunkBytes);
+    const int rr = lane >> 3;            // row inside a group of 4 rows
+    const int c4 = lane & 7;             // 16-byte column group inside the chunk
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int64_t t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
-      const int64_t b = t / tiles_per_batch;
-      const int64_t r = t - b * tiles_per_batch;
-      const int64_t m0 = (r % p.tiles_m) * BM;
-      const int64_t n0 = (r / p.tiles_m) * BN;
+      int64_t b;
+      int32_t mt, nt;
+      tile_coords(t, p, b, mt, nt);
+      const int64_t m0 = (int64_t)mt * BM, n0 = (int64_t)nt * BN;
       // warp-uniform result: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag))) break;
       ptx::tc_fence_after_sync();
-      const int64_t row = m0 + q * 32 + lane;
-      Tout* crow = C + b * p.c_bs + row * p.c_rs;
+      Tout* cbase = C + b * p.c_bs;
+      const int64_t row0 = m0 + q * 32;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int64_t col0 = n0 + c * 32;
-        if (col0 >= p.N) break;  // uniform across the warp
+      for (int c = 0; c < kChunks; ++c) {
+        const int col_in_tile = half * (BN / 2) + c * 32;
+        const int64_t col0 = n0 + col_in_tile;
+        if (col0 >= p.N || row0 >= p.M) break;  // uniform across the warp
         uint32_t raw[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + c * 32) + ((uint32_t)(q * 32) << 16), raw);
+        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + col_in_tile) + ((uint32_t)(q * 32) << 16), raw);
         ptx::tmem_ld_wait();
-        const int64_t rem = p.N - col0;
-        const int valid = rem >= 32 ? 32 : (int)rem;
-        if (row < p.M) {
-          float v[32];
+        // lane == row: row `lane`, 8 groups of 4 columns, group index XOR (row mod 8)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = p.alpha * __uint_as_float(raw[i]);
-          if (p.bias != nullptr) {
-            // bias_rs == 0: a [n] row, the same address in every lane (one broadcast transaction)
+        for (int g4 = 0; g4 < 8; ++g4)
+          *reinterpret_cast<float4*>(stage + lane * 32 + ((g4 ^ (lane & 7)) << 2)) =
+              make_float4(__uint_as_float(raw[4 * g4]), __uint_as_float(raw[4 * g4 + 1]),
+                          __uint_as_float(raw[4 * g4 + 2]), __uint_as_float(raw[4 * g4 + 3]));
+        __syncwarp();
+        // lane == (row group, column group): 8 lanes cover one 128-byte row segment
+        const int64_t col = col0 + c4 * 4;
+        const int64_t rem = p.N - col;
+        const int valid = rem >= 4 ? 4 : (rem > 0 ? (int)rem : 0);
+        float bias_row[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (p.bias != nullptr && p.bias_rs == 0 && valid > 0) load4(p.bias, col, p.bias_dtype, valid, bias_row);
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) v[i] += p.beta * ld_param(p.bias, row * p.bias_rs + col0 + i, p.bias_dtype);
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + rr;
+          const int64_t row = row0 + r;
+          const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
+          if (row < p.M && valid > 0) {
+            float v[4] = {a4.x * p.alpha, a4.y * p.alpha, a4.z * p.alpha, a4.w * p.alpha};
+            if (p.bias != nullptr) {
+              float bb[4];
+              if (p.bias_rs == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) bb[j] = bias_row[j];
+              } else {
+                load4(p.bias, row * p.bias_rs + col, p.bias_dtype, valid, bb);
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] = fmaf(p.beta, bb[j], v[j]);
+            }
+            if (p.epilogue != B200_EPILOGUE_NONE) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] = act(v[j], p.epilogue);
+            }
+            if (p.residual != nullptr) {
+              float res[4];
+              load4(p.residual, row * p.residual_rs + col, p.residual_dtype, valid, res);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] += res[j];
+            }
+            store4(cbase + row * p.c_rs + col, v, valid);
           }
-          if (p.epilogue != B200_EPILOGUE_NONE) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = act(v[i], p.epilogue);
-          }
-          if (p.residual != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) v[i] += ld_param(p.residual, row * p.residual_rs + col0 + i, p.residual_dtype);
-          }
-          store_chunk(crow + col0, v, valid);
         }
+        __syncwarp();  // staging buffer is rewritten by the next chunk
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(tmem_empty_bar(acc));
@@ -347,12 +408,14 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
 int pick_bn(const b200_gemm_args& g) {
   if (g.n <= 128) return 128;
   const int sms = sm_count();
-  auto cost = [&](int bn) {
+  // Per-tile cost: the main loop is proportional to BN but a 128-wide tile needs 1.33x the
+  // operand bytes per flop of a 256-wide one, which is what bounds it; plus a fixed share.
+  auto cost = [&](int bn, double per_col) {
     const int64_t tiles = ((g.m + BM - 1) / BM) * ((g.n + bn - 1) / bn) * g.batch;
     const int64_t waves = (tiles + sms - 1) / sms;
-    return (double)waves * (bn + 32);
+    return (double)waves * (bn * per_col + 32);
   };
-  return cost(256) <= cost(128) ? 256 : 128;
+  return cost(256, 1.0) <= cost(128, 1.33) ? 256 : 128;
 }
 
 }  // namespace

@@ -142,11 +142,11 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint32_t phase = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int32_t kv0 = j * BN;
-        if (!ptx::mbar_wait(k_empty(s), phase ^ 1, abort_flag)) break;
+        if (!ptx::mbar_wait_relaxed(k_empty(s), phase ^ 1, abort_flag)) break;
         ptx::mbar_arrive_expect_tx(k_full(s), KV_BYTES);
         if (p.k_heads_inner) ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, h, kv0, b);
         else ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, kv0, h, b);
-        if (!ptx::mbar_wait(v_empty(s), phase ^ 1, abort_flag)) break;
+        if (!ptx::mbar_wait_relaxed(v_empty(s), phase ^ 1, abort_flag)) break;
         ptx::mbar_arrive_expect_tx(v_full(s), KV_BYTES);
         if (p.v_heads_inner) ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, h, kv0, b);
         else ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, kv0, h, b);
@@ -231,18 +231,24 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
       const int64_t kv0 = (int64_t)j * BN;
       const bool need_mask = (p.causal && kv0 + BN - 1 > q0) || (kv0 + BN > p.kv_len);
-      float x[64];
-      float tile_max = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float v = __uint_as_float(raw[c >> 5][c & 31]) * p.scale_log2;
-        if (need_mask) {
+        for (int c = 0; c < 64; ++c) {
           const int64_t key = kv0 + c;
-          if (key >= p.kv_len || (p.causal && key > row)) v = -INFINITY;
+          if (key >= p.kv_len || (p.causal && key > row)) raw[c >> 5][c & 31] = 0xff800000u;  // -inf
         }
-        x[c] = v;
-        tile_max = fmaxf(tile_max, v);
       }
+      // row maximum of the raw scores, four independent chains (scale > 0, so the scaled maximum
+      // is the maximum scaled)
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(raw[c >> 5][(c & 31) + 2 * u]),
+                                     __uint_as_float(raw[c >> 5][(c & 31) + 2 * u + 1])));
+      }
+      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
       // lazy rescale: follow the true maximum only when it ran away by more than 2^8
       float alpha = 1.0f;
       if (tile_max > m_ref + 8.0f) {
@@ -250,17 +256,21 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         m_ref = tile_max;
         l *= alpha;
       }
-      const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+      const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 negm2 = make_float2(neg_m, neg_m);
       uint32_t packed[32];
-      float sum = 0.0f;
+      float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2(x[c] - m_use);
-        const float p1 = ex2(x[c + 1] - m_use);
-        sum += p0 + p1;
-        packed[c >> 1] = pack_bf16x2(p0, p1);
+        // p = exp2(s * scale * log2e - m): one packed FMA for two scores, then two MUFU ops
+        const float2 s2 = make_float2(__uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[c >> 5][(c & 31) + 1]));
+        const float2 e2 = __ffma2_rn(s2, scale2, negm2);
+        const float2 p2 = make_float2(ex2(e2.x), ex2(e2.y));
+        sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], p2);
+        packed[c >> 1] = pack_bf16x2(p2.x, p2.y);
       }
-      l += sum;
+      l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
 
       // P buffer and O accumulator are free once the previous P V has completed
       if (j > 0) {
@@ -388,6 +398,7 @@ const char* sdpa_tcgen05_ineligible(const b200_sdpa_args& a) {
   if (a.dtype != B200_BF16) return "tensors are not bf16";
   if (a.head_dim != D) return "head_dim is not 64";
   if (a.kv_len == 0) return "kv_len is zero";
+  if (!(a.scale > 0.0f)) return "scale is not positive";
   if (!aligned_to(a.q, 16) || !aligned_to(a.k, 16) || !aligned_to(a.v, 16) || !aligned_to(a.o, 16))
     return "pointer not 16-byte aligned";
   if (!strides_ok(a.q_strides, a.batch, a.heads, a.q_len) || !strides_ok(a.k_strides, a.batch, a.heads, a.kv_len) ||
