@@ -80,7 +80,7 @@ def time_case(make_inputs, run, bytes_per_copy, iters, use_graph):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="gemm,layer_norm,softmax,gelu,reduce,sdpa")
+    ap.add_argument("--ops", default="gemm,gemm_fused,layer_norm,softmax,gelu,reduce,sdpa")
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--only", default="", help="substring filter on the case name")
     ap.add_argument("--no-graph", action="store_true", help="plain launches (what an ncu capture wants)")
@@ -141,6 +141,35 @@ def main():
                         us, rot = time_case(make, lambda t: ops.gemm(t[0], t[1], t[2]), nbytes, args.iters, use_graph)
                         bound = "tensor" if m >= 512 else "hbm"
                         report(name, us, rot, 2.0 * m * n * k, nbytes, bound)
+
+    if "gemm_fused" in wanted:
+        # The GEMMs of one GPT-2 XL block (and the LM head) as the fused graph launches them.
+        m, d = 8192, 1600
+        bf, f32 = torch.bfloat16, torch.float32
+        cases = [
+            ("xl qkv  bias", d, 3 * d, False, 0, bf),
+            ("xl proj bias+residual f32", d, d, True, 0, f32),
+            ("xl fc   bias+gelu_tanh", d, 4 * d, False, 1, bf),
+            ("xl out  bias+residual f32", 4 * d, d, True, 0, f32),
+            ("xl lm_head f32 logits", d, 50257, False, 0, f32),
+        ]
+        for label, k, n, with_res, epi, out_dtype in cases:
+            name = f"gemm_fused {label} {m}x{k}x{n}"
+            if not keep(name):
+                continue
+            out_s = 4 if out_dtype == f32 else 2
+            nbytes = 2 * (m * k + k * n) + out_s * m * n + (4 * m * n if with_res else 0)
+
+            def make(i, k=k, n=n, with_res=with_res, label=label):
+                a = randn((m, k), bf)
+                w = randn((n, k), bf, 0.02).t()
+                bias = None if "lm_head" in label else randn((n,), bf, 0.02)
+                res = randn((m, n), f32) if with_res else None
+                return a, w, bias, res
+
+            us, rot = time_case(make, lambda t, epi=epi, out_dtype=out_dtype: ops.gemm(t[0], t[1], t[2], t[3], 1.0, 1.0, epi, out_dtype),
+                                nbytes, args.iters, use_graph)
+            report(name, us, rot, 2.0 * m * n * k, nbytes, "tensor")
 
     if "layer_norm" in wanted:
         for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):

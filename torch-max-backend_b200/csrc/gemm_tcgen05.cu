@@ -22,6 +22,9 @@
 #include "gemm_internal.cuh"
 #include "ptx.cuh"
 #include "tma.cuh"
+#ifdef B200_GEMM_PROBE
+#include <cstdlib>
+#endif
 
 namespace b200 {
 namespace {
@@ -61,13 +64,21 @@ struct Params {
   int32_t tiles_m, tiles_n;
   int64_t num_tiles;
   unsigned int* status;
+  int32_t fast_ok;  // pointers/pitches allow the branch-free vector epilogue on interior tiles
+#ifdef B200_GEMM_PROBE
+  int probe;  // timing probes of the epilogue stages (development builds only)
+#endif
 };
 
 __device__ __forceinline__ float act(float v, int32_t epilogue) {
   if (epilogue == B200_EPILOGUE_GELU_TANH) {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    // 0.5 v (1 + tanh u) == v / (1 + exp(-2u)) == v * rcp(1 + exp2(-2 log2(e) u)): two MUFU ops
     const float u = k0 * (v + k1 * v * v * v);
-    return v / (1.0f + __expf(-2.0f * u));
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-2.885390081777927f * u));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return v * r;
   }
   if (epilogue == B200_EPILOGUE_GELU_ERF) return gelu_erf_f32(v);
   return v;
@@ -108,6 +119,17 @@ __device__ __forceinline__ void load4(const void* p, int64_t idx, int32_t dtype,
       for (int j = 0; j < 4; ++j) out[j] = j < valid ? __bfloat162float(q[j]) : 0.0f;
     }
   }
+}
+
+__device__ __forceinline__ void store4_aligned(float* dst, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+__device__ __forceinline__ void store4_aligned(__nv_bfloat16* dst, const float (&v)[4]) {
+  uint2 t;
+  t.x = pack_bf16x2(v[0], v[1]);
+  t.y = pack_bf16x2(v[2], v[3]);
+  *reinterpret_cast<uint2*>(dst) = t;
 }
 
 __device__ __forceinline__ void store4(float* dst, const float (&v)[4], int valid) {
@@ -260,19 +282,94 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int32_t mt, nt;
       tile_coords(t, p, b, mt, nt);
       const int64_t m0 = (int64_t)mt * BM, n0 = (int64_t)nt * BN;
+      Tout* cbase = C + b * p.c_bs;
+      const int64_t row0 = m0 + q * 32;
+      // Interior tiles with vector-friendly pointers take a branch-free path in which all loads
+      // of a chunk are issued before they are needed.
+      const bool fast = p.fast_ok && m0 + BM <= p.M && n0 + BN <= p.N;
+      // The bias row of this warp's columns is fetched before the accumulator is waited for.
+      float bias_pref[kChunks][4];
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bias_pref[c][j] = 0.0f;
+        if (p.bias != nullptr && p.bias_rs == 0) {
+          const int64_t col = n0 + half * (BN / 2) + c * 32 + c4 * 4;
+          const int64_t rem = p.N - col;
+          const int valid = rem >= 4 ? 4 : (rem > 0 ? (int)rem : 0);
+          if (valid > 0) load4(p.bias, col, p.bias_dtype, valid, bias_pref[c]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) bias_pref[c][j] *= p.beta;
+        }
+      }
       // warp-uniform result: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag))) break;
       ptx::tc_fence_after_sync();
-      Tout* cbase = C + b * p.c_bs;
-      const int64_t row0 = m0 + q * 32;
-#pragma unroll 1
+      if (fast) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          const int col_in_tile = half * (BN / 2) + c * 32;
+          const int64_t col = n0 + col_in_tile + c4 * 4;
+          // residual rows of this chunk: in flight while the accumulator chunk is staged
+          float4 res[8];
+          if (p.residual != nullptr) {
+            const float* rbase = static_cast<const float*>(p.residual) + (row0 + rr) * p.residual_rs + col;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) res[i] = __ldg(reinterpret_cast<const float4*>(rbase + (int64_t)i * 4 * p.residual_rs));
+          }
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + col_in_tile) + ((uint32_t)(q * 32) << 16), raw);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int g4 = 0; g4 < 8; ++g4)
+            *reinterpret_cast<float4*>(stage + lane * 32 + ((g4 ^ (lane & 7)) << 2)) =
+                make_float4(__uint_as_float(raw[4 * g4]), __uint_as_float(raw[4 * g4 + 1]),
+                            __uint_as_float(raw[4 * g4 + 2]), __uint_as_float(raw[4 * g4 + 3]));
+          __syncwarp();
+          float4 a4[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + rr;
+            a4[i] = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
+          }
+          __syncwarp();  // staging buffer may be rewritten by the next chunk
+          Tout* crow = cbase + (row0 + rr) * p.c_rs + col;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float v[4] = {fmaf(a4[i].x, p.alpha, bias_pref[c][0]), fmaf(a4[i].y, p.alpha, bias_pref[c][1]),
+                          fmaf(a4[i].z, p.alpha, bias_pref[c][2]), fmaf(a4[i].w, p.alpha, bias_pref[c][3])};
+            if (p.epilogue != B200_EPILOGUE_NONE) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] = act(v[j], p.epilogue);
+            }
+            if (p.residual != nullptr) {
+              v[0] += res[i].x; v[1] += res[i].y; v[2] += res[i].z; v[3] += res[i].w;
+            }
+            store4_aligned(crow + (int64_t)i * 4 * p.c_rs, v);
+          }
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(tmem_empty_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
+#pragma unroll
       for (int c = 0; c < kChunks; ++c) {
         const int col_in_tile = half * (BN / 2) + c * 32;
         const int64_t col0 = n0 + col_in_tile;
         if (col0 >= p.N || row0 >= p.M) break;  // uniform across the warp
+#ifdef B200_GEMM_PROBE
+        if (p.probe == 1) break;
+#endif
         uint32_t raw[32];
         ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + col_in_tile) + ((uint32_t)(q * 32) << 16), raw);
         ptx::tmem_ld_wait();
+#ifdef B200_GEMM_PROBE
+        if (p.probe == 2) {
+          if (raw[0] == 0x7fc12345u && raw[31] == 0x7fc54321u) cbase[0] = Elem<Tout>::from_f32(1.0f);
+          continue;
+        }
+#endif
         // lane == row: row `lane`, 8 groups of 4 columns, group index XOR (row mod 8)
 #pragma unroll
         for (int g4 = 0; g4 < 8; ++g4)
@@ -284,25 +381,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int64_t col = col0 + c4 * 4;
         const int64_t rem = p.N - col;
         const int valid = rem >= 4 ? 4 : (rem > 0 ? (int)rem : 0);
-        float bias_row[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (p.bias != nullptr && p.bias_rs == 0 && valid > 0) load4(p.bias, col, p.bias_dtype, valid, bias_row);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int r = i * 4 + rr;
           const int64_t row = row0 + r;
           const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
+#ifdef B200_GEMM_PROBE
+          if (p.probe == 3) {
+            if (a4.x == 123456.789f) cbase[0] = Elem<Tout>::from_f32(a4.y);
+            continue;
+          }
+#endif
           if (row < p.M && valid > 0) {
             float v[4] = {a4.x * p.alpha, a4.y * p.alpha, a4.z * p.alpha, a4.w * p.alpha};
             if (p.bias != nullptr) {
-              float bb[4];
               if (p.bias_rs == 0) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) bb[j] = bias_row[j];
+                for (int j = 0; j < 4; ++j) v[j] += bias_pref[c][j];
               } else {
+                float bb[4];
                 load4(p.bias, row * p.bias_rs + col, p.bias_dtype, valid, bb);
-              }
 #pragma unroll
-              for (int j = 0; j < 4; ++j) v[j] = fmaf(p.beta, bb[j], v[j]);
+                for (int j = 0; j < 4; ++j) v[j] = fmaf(p.beta, bb[j], v[j]);
+              }
             }
             if (p.epilogue != B200_EPILOGUE_NONE) {
 #pragma unroll
@@ -314,6 +415,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
               for (int j = 0; j < 4; ++j) v[j] += res[j];
             }
+#ifdef B200_GEMM_PROBE
+            if (p.probe == 4) {
+              if (v[0] == 123456.789f) cbase[0] = Elem<Tout>::from_f32(v[1]);
+              continue;
+            }
+#endif
             store4(cbase + row * p.c_rs + col, v, valid);
           }
         }
@@ -385,6 +492,18 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
   p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * g.batch;
   p.status = device_status_ptr();
   B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "gemm(tcgen05): device status word unavailable");
+  {
+    const size_t out_vec = sizeof(Tout) * 4;  // bytes of one 4-column group
+    bool ok = aligned_to(g.c, out_vec) && g.c_row_stride % 4 == 0 && (g.batch == 1 || g.c_batch_stride % 4 == 0);
+    if (g.bias != nullptr)
+      ok = ok && g.bias_row_stride == 0 && aligned_to(g.bias, g.bias_dtype == B200_F32 ? 16 : 8);
+    if (g.residual != nullptr)
+      ok = ok && g.residual_dtype == B200_F32 && aligned_to(g.residual, 16) && g.residual_row_stride % 4 == 0;
+    p.fast_ok = ok ? 1 : 0;
+  }
+#ifdef B200_GEMM_PROBE
+  p.probe = getenv("B200_GEMM_PROBE") ? atoi(getenv("B200_GEMM_PROBE")) : 0;
+#endif
 
   auto kernel = gemm_tcgen05_kernel<BN, B_MN_MAJOR, Tout>;
   static thread_local bool attr_set[64] = {false};

@@ -453,7 +453,8 @@ def fused_gemm(a, b, bias, residual, *, alpha, beta, epilogue, out_dtype, out_sh
     n = b.shape[-1]
     res2d = residual.reshape(-1, n) if residual is not None else None
     y = ops.gemm(a, b, bias, res2d, alpha, beta, epilogue, out_dtype)
-    return y.view(out_shape)
+    # reshape, not view: a padded-pitch result splits its row dim as a view and copies otherwise
+    return y.reshape(out_shape)
 
 
 @_count_calls

@@ -250,10 +250,16 @@ def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, 
         raise RuntimeError(f"gemm: operand dtypes differ ({a.dtype} and {b.dtype})")
     out_shape = _gemm_out_shape(a, b)
     out_dtype = out_dtype or a.dtype
-    c = torch.empty(out_shape, dtype=out_dtype, device=device)
+    m, n = out_shape[-2], out_shape[-1]
+    if a.dim() == 2 and n % 8 != 0 and n >= 1024 and m > 1:
+        # Rows of a wide output whose pitch is not a multiple of 16 bytes (e.g. the 50257-column
+        # logits) would be misaligned for vector stores: allocate a padded pitch and return the
+        # [m, n] view of it (the same idea as a padded leading dimension in BLAS).
+        c = torch.empty((m, (n + 7) // 8 * 8), dtype=out_dtype, device=device)[:, :n]
+    else:
+        c = torch.empty(out_shape, dtype=out_dtype, device=device)
     if c.numel() == 0:
         return c
-    m, n = out_shape[-2], out_shape[-1]
     if a.dim() == 2:
         bias = _normalise_bias(bias, m, n)
         if residual is not None and (residual.shape != c.shape or residual.stride(-1) != 1):
