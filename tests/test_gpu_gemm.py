@@ -113,6 +113,31 @@ def test_tcgen05_ragged(ops, m, n, k):
     assert_parity(y, cpu_gemm(a, w.t(), out_dtype=torch.float32), bf16=False, scale=k**0.5 * 4)
 
 
+@pytest.mark.parametrize("tile_n", [128, 192, 256])
+@pytest.mark.parametrize("b_layout", ["nk", "kn"])
+def test_tcgen05_every_tile_width(ops, monkeypatch, tile_n, b_layout):
+    """Each tile width on a shape with ragged M, N and K tails, bias, gelu, fp32 residual."""
+    monkeypatch.setenv("B200_GEMM_TILE_N", str(tile_n))
+    m, n, k = 700, 1000, 328
+    a = gen((m, k), torch.bfloat16, 40, 0.5)
+    if b_layout == "nk":
+        w = gen((n, k), torch.bfloat16, 41, 0.1)
+        b_cpu, b_gpu = w.t(), w.cuda().t()
+    else:
+        b_cpu = gen((k, n), torch.bfloat16, 41, 0.1)
+        b_gpu = b_cpu.cuda()
+    bias = gen((n,), torch.bfloat16, 42)
+    res = gen((m, n), torch.float32, 43)
+    y = ops.gemm(a.cuda(), b_gpu, bias.cuda(), res.cuda(), 1.0, 1.0, 1, torch.float32, ROUTE_TC)
+    want = torch.nn.functional.gelu(a.float() @ b_cpu.float() + bias.float(), approximate="tanh") + res
+    assert_parity(y, want, bf16=False)
+    # interior (branch-free) epilogue path: aligned pitch, full tiles
+    m2, n2 = 512, 768
+    a2, w2 = gen((m2, k), torch.bfloat16, 44, 0.5), gen((n2, k), torch.bfloat16, 45, 0.1)
+    y2 = ops.gemm(a2.cuda(), w2.cuda().t(), bias[:n2].cuda(), None, 1.0, 1.0, 0, torch.bfloat16, ROUTE_TC)
+    assert_parity(y2, a2.float() @ w2.float().t() + bias[:n2].float(), bf16=True)
+
+
 def test_tcgen05_epilogues(ops):
     m, n, k = 512, 640, 256
     a, w = gen((m, k), torch.bfloat16, 15, 0.5), gen((n, k), torch.bfloat16, 16, 0.1)

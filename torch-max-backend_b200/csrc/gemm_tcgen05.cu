@@ -22,9 +22,8 @@
 #include "gemm_internal.cuh"
 #include "ptx.cuh"
 #include "tma.cuh"
-#ifdef B200_GEMM_PROBE
+
 #include <cstdlib>
-#endif
 
 namespace b200 {
 namespace {
@@ -41,9 +40,9 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;
 
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kStages = BN == 128 ? 6 : 4;
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int kTmemCols = 2 * BN;  // two accumulators; 256 or 512 (powers of two)
+  static constexpr int kTmemCols = BN == 128 ? 256 : 512;  // two accumulators, rounded up to a power of two
   static constexpr int kSmemA = 0;
   static constexpr int kSmemB = kStages * A_STAGE_BYTES;
   static constexpr int kSmemStaging = kSmemB + kStages * B_STAGE_BYTES;
@@ -525,16 +524,24 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
 // Wave-quantisation cost of a tile width: waves of CTAs times the per-tile cost (main loop
 // proportional to BN plus a fixed epilogue/prologue share).
 int pick_bn(const b200_gemm_args& g) {
+  // B200_GEMM_TILE_N=128|192|256 pins the tile width (tuning and tests).
+  if (const char* forced = getenv("B200_GEMM_TILE_N")) {
+    const int v = atoi(forced);
+    if (v == 128 || v == 192 || v == 256) return v;
+  }
   if (g.n <= 128) return 128;
   const int sms = sm_count();
-  // Per-tile cost: the main loop is proportional to BN but a 128-wide tile needs 1.33x the
-  // operand bytes per flop of a 256-wide one, which is what bounds it; plus a fixed share.
+  // Per-tile cost: the main loop is proportional to BN, but narrower tiles need more operand
+  // bytes per flop (1.33x at 128, 1.14x at 192 relative to 256), which is what bounds them; plus
+  // a fixed share. The number of waves carries the quantisation loss of the last partial wave.
   auto cost = [&](int bn, double per_col) {
     const int64_t tiles = ((g.m + BM - 1) / BM) * ((g.n + bn - 1) / bn) * g.batch;
     const int64_t waves = (tiles + sms - 1) / sms;
-    return (double)waves * (bn * per_col + 32);
+    return (double)waves * (bn * per_col + 24);
   };
-  return cost(256, 1.0) <= cost(128, 1.33) ? 256 : 128;
+  const double c256 = cost(256, 1.0), c192 = cost(192, 1.08), c128 = cost(128, 1.25);
+  if (c256 <= c192 && c256 <= c128) return 256;
+  return c192 <= c128 ? 192 : 128;
 }
 
 }  // namespace
@@ -567,6 +574,7 @@ int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream) {
 #define TC_LAUNCH(BN_, MN_)                                                   \
   (f32 ? launch_cfg<BN_, MN_, float>(g, stream) : launch_cfg<BN_, MN_, __nv_bfloat16>(g, stream))
   if (bn == 256) return mn ? TC_LAUNCH(256, true) : TC_LAUNCH(256, false);
+  if (bn == 192) return mn ? TC_LAUNCH(192, true) : TC_LAUNCH(192, false);
   return mn ? TC_LAUNCH(128, true) : TC_LAUNCH(128, false);
 #undef TC_LAUNCH
 }
