@@ -64,6 +64,7 @@ struct Params {
   int64_t num_tiles;
   unsigned int* status;
   int32_t fast_ok;  // pointers/pitches allow the branch-free vector epilogue on interior tiles
+  int32_t direct;   // interior tiles: store straight from the TMEM row layout (no smem staging)
 #ifdef B200_GEMM_PROBE
   int probe;  // timing probes of the epilogue stages (development builds only)
 #endif
@@ -285,7 +286,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int64_t row0 = m0 + q * 32;
       // Interior tiles with vector-friendly pointers take a branch-free path in which all loads
       // of a chunk are issued before they are needed.
-      const bool fast = p.fast_ok && m0 + BM <= p.M && n0 + BN <= p.N;
+      // (a column tile that ends on a 32-column boundary only has whole chunks inside or outside)
+      const bool fast = p.fast_ok && m0 + BM <= p.M && (n0 + BN <= p.N || (p.N - n0) % 32 == 0);
       // The bias row of this warp's columns is fetched before the accumulator is waited for.
       float bias_pref[kChunks][4];
 #pragma unroll
@@ -304,10 +306,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // warp-uniform result: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag))) break;
       ptx::tc_fence_after_sync();
+      if (fast && p.direct) {
+        // lane == row: each lane owns 32 consecutive columns of its row
+        const int64_t row = row0 + lane;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          const int col_in_tile = half * (BN / 2) + c * 32;
+          const int64_t col0 = n0 + col_in_tile;
+          if (col0 >= p.N) break;  // uniform: chunk entirely past the last column
+          float bv[32];
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) {
+              float t4[4];
+              load4(p.bias, col0 + g4 * 4, p.bias_dtype, 4, t4);  // same address in every lane
+#pragma unroll
+              for (int j = 0; j < 4; ++j) bv[4 * g4 + j] = t4[j] * p.beta;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) bv[i] = 0.0f;
+          }
+          float4 res[8];
+          if (p.residual != nullptr) {
+            const float4* rrow = reinterpret_cast<const float4*>(static_cast<const float*>(p.residual) + row * p.residual_rs + col0);
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) res[g4] = __ldg(rrow + g4);
+          }
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + col_in_tile) + ((uint32_t)(q * 32) << 16), raw);
+          ptx::tmem_ld_wait();
+          Tout* crow = cbase + row * p.c_rs + col0;
+#pragma unroll
+          for (int g4 = 0; g4 < 8; ++g4) {
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = fmaf(__uint_as_float(raw[4 * g4 + j]), p.alpha, bv[4 * g4 + j]);
+            if (p.epilogue != B200_EPILOGUE_NONE) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] = act(v[j], p.epilogue);
+            }
+            if (p.residual != nullptr) {
+              v[0] += res[g4].x; v[1] += res[g4].y; v[2] += res[g4].z; v[3] += res[g4].w;
+            }
+            store4_aligned(crow + g4 * 4, v);
+          }
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(tmem_empty_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
       if (fast) {
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           const int col_in_tile = half * (BN / 2) + c * 32;
+          if (n0 + col_in_tile >= p.N) break;  // uniform: chunk entirely past the last column
           const int64_t col = n0 + col_in_tile + c4 * 4;
           // residual rows of this chunk: in flight while the accumulator chunk is staged
           float4 res[8];
@@ -499,6 +553,8 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
     if (g.residual != nullptr)
       ok = ok && g.residual_dtype == B200_F32 && aligned_to(g.residual, 16) && g.residual_row_stride % 4 == 0;
     p.fast_ok = ok ? 1 : 0;
+    const char* mode = getenv("B200_GEMM_EPILOGUE");  // "direct" | "staged" (tuning knob)
+    p.direct = (mode != nullptr && mode[0] == 'd') ? 1 : 0;
   }
 #ifdef B200_GEMM_PROBE
   p.probe = getenv("B200_GEMM_PROBE") ? atoi(getenv("B200_GEMM_PROBE")) : 0;

@@ -1,19 +1,22 @@
 // Attention forward on the 5th-generation tensor cores for head_dim 64, bf16.
 //
-// One CTA owns 128 query rows of one (batch, head) and walks the 64-key tiles it may attend to.
-//   warp 0      TMA producer: Q once, then K_j / V_j into two 3-deep rings (128-byte swizzle).
-//   warp 1      MMA issuer: S_j = Q K_j^T into one of two TMEM score buffers, and, once the
-//               softmax warps have published P_j, O += P_j V_j into the TMEM output accumulator.
-//               S_{j+1} is issued before P_j is waited for, so the tensor core works on the next
-//               scores while the softmax of the current tile runs.
+// Persistent kernel: two CTAs per SM, each looping over work items (128 query rows of one
+// (batch, head)), heaviest items first. Inside a CTA:
+//   warp 0      TMA producer: Q of the item, then its K_j / V_j tiles (64 keys) into two 3-deep
+//               rings (128-byte swizzle). The rings keep streaming across item boundaries.
+//   warp 1      MMA issuer: S = Q K_j^T into one of two TMEM score buffers and O += P_j V_j into
+//               the TMEM output accumulator. The score MMA stream runs one tile ahead of the
+//               P V stream, also across item boundaries, so the next item's first scores are
+//               ready when the softmax warps finish writing the previous item's output.
 //   warps 2-5   softmax, one thread per query row: pull S_j out of TMEM, online softmax in the
-//               exp2 domain with fp32 statistics, write P_j (rounded to bf16) into shared memory
-//               as the K-major A operand of the second MMA, and rescale O in TMEM when the
-//               running maximum moved. The rescale is lazy: the reference maximum only follows
-//               the true maximum when it is more than 8 (a factor 256) behind, which keeps P
-//               inside bf16/fp32 range and skips most TMEM round trips.
-// Two CTAs fit on one SM (80 KB of shared memory and 256 TMEM columns each), so the softmax of
-// one overlaps the MMAs of the other. The heaviest (last) query tiles are scheduled first.
+//               exp2 domain with fp32 statistics, write P_j (rounded to bf16) into one of two
+//               shared-memory buffers as the K-major A operand of the second MMA, and rescale O
+//               in TMEM when the running maximum moved. The rescale is lazy: the reference
+//               maximum only follows the true maximum when it is more than 8 (a factor 256)
+//               behind, which keeps P inside bf16/fp32 range and skips most TMEM round trips.
+//               With two P buffers the softmax of tile j+1 does not wait for P_j V_j.
+// Two CTAs fit on one SM (96 KB of shared memory and 256 TMEM columns each), so the softmax of
+// one overlaps the MMAs of the other.
 //
 // Numerics: scores scaled by scale*log2(e), P = exp2(s - m), masked scores are -inf, P is rounded
 // to bf16 before the second MMA, O is divided by the fp32 row sum once at the end, and the
@@ -25,7 +28,7 @@
 namespace b200 {
 namespace {
 
-constexpr int BM = 128;   // query rows per CTA
+constexpr int BM = 128;   // query rows per work item
 constexpr int BN = 64;    // keys per tile
 constexpr int D = 64;     // head_dim
 constexpr int kStages = 3;
@@ -41,9 +44,10 @@ constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + Q_BYTES;
 constexpr int SMEM_V = SMEM_K + kStages * KV_BYTES;
 constexpr int SMEM_P = SMEM_V + kStages * KV_BYTES;
-constexpr int SMEM_BAR = SMEM_P + P_BYTES;
-// barriers: q_full, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], s_empty[2], p_full, pv_done
-constexpr int kNumBars = 1 + 4 * kStages + 4 + 2;
+constexpr int SMEM_BAR = SMEM_P + 2 * P_BYTES;
+// barriers: q_full, q_empty, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], s_empty[2],
+//           p_full[2], pv_done[2]
+constexpr int kNumBars = 2 + 4 * kStages + 8;
 constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
 constexpr int SMEM_BYTES = SMEM_MISC + 16 + 1024;
 
@@ -55,6 +59,8 @@ struct Params {
   float scale_log2;  // scale * log2(e)
   int causal;
   int q_tiles;
+  int64_t bh;          // batch * heads
+  int64_t num_items;   // q_tiles * bh
   int q_heads_inner, k_heads_inner, v_heads_inner;  // tensor map dim order is (d, head, pos, batch)
   unsigned int* status;
 };
@@ -65,13 +71,28 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__device__ __forceinline__ int kv_tiles_for(int64_t q0, int64_t q_len, int64_t kv_len, int causal) {
-  int64_t last_key = kv_len;  // exclusive
-  if (causal) {
-    const int64_t lim = q0 + BM;  // rows q0..q0+127 see keys <= row
+// Work item -> (query tile, batch, head). Items are ordered heaviest first: all (batch, head)
+// pairs of the last query tile, then of the one before, ...
+struct Item {
+  int64_t q0;
+  int32_t b, h;
+  int n_tiles;
+};
+
+__device__ __forceinline__ Item decode_item(int64_t w, const Params& p) {
+  Item it;
+  const int q_tile = p.q_tiles - 1 - (int)(w / p.bh);
+  const int64_t bh = w % p.bh;
+  it.b = (int32_t)(bh / p.heads);
+  it.h = (int32_t)(bh % p.heads);
+  it.q0 = (int64_t)q_tile * BM;
+  int64_t last_key = p.kv_len;  // exclusive
+  if (p.causal) {
+    const int64_t lim = it.q0 + BM;  // rows q0..q0+127 see keys <= row
     if (lim < last_key) last_key = lim;
   }
-  return (int)((last_key + BN - 1) / BN);
+  it.n_tiles = (int)((last_key + BN - 1) / BN);
+  return it;
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -82,29 +103,24 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t base = ptx::smem_u32(smem);
   const uint32_t q_smem = base + SMEM_Q, k_smem = base + SMEM_K, v_smem = base + SMEM_V, p_smem = base + SMEM_P;
   const uint32_t bar = base + SMEM_BAR;
-  const uint32_t q_full = bar;
-  auto k_full = [&](int s) { return bar + 8u * (1 + s); };
-  auto k_empty = [&](int s) { return bar + 8u * (1 + kStages + s); };
-  auto v_full = [&](int s) { return bar + 8u * (1 + 2 * kStages + s); };
-  auto v_empty = [&](int s) { return bar + 8u * (1 + 3 * kStages + s); };
-  auto s_full = [&](int b) { return bar + 8u * (1 + 4 * kStages + b); };
-  auto s_empty = [&](int b) { return bar + 8u * (1 + 4 * kStages + 2 + b); };
-  const uint32_t p_full = bar + 8u * (1 + 4 * kStages + 4);
-  const uint32_t pv_done = bar + 8u * (1 + 4 * kStages + 5);
+  const uint32_t q_full = bar, q_empty = bar + 8;
+  auto k_full = [&](int s) { return bar + 8u * (2 + s); };
+  auto k_empty = [&](int s) { return bar + 8u * (2 + kStages + s); };
+  auto v_full = [&](int s) { return bar + 8u * (2 + 2 * kStages + s); };
+  auto v_empty = [&](int s) { return bar + 8u * (2 + 3 * kStages + s); };
+  auto s_full = [&](int b) { return bar + 8u * (2 + 4 * kStages + b); };
+  auto s_empty = [&](int b) { return bar + 8u * (2 + 4 * kStages + 2 + b); };
+  auto p_full = [&](int b) { return bar + 8u * (2 + 4 * kStages + 4 + b); };
+  auto pv_done = [&](int b) { return bar + 8u * (2 + 4 * kStages + 6 + b); };
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + SMEM_MISC);
   volatile uint32_t* tmem_holder = misc;
   volatile uint32_t* abort_flag = misc + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heaviest query tiles first
-  const int q_tile = p.q_tiles - 1 - (int)blockIdx.x;
-  const int64_t bh = blockIdx.y;
-  const int32_t b = (int32_t)(bh / p.heads), h = (int32_t)(bh % p.heads);
-  const int64_t q0 = (int64_t)q_tile * BM;
-  const int n_tiles = kv_tiles_for(q0, p.q_len, p.kv_len, p.causal);
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
+    ptx::mbar_init(q_empty, 1);
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(k_full(s), 1);
       ptx::mbar_init(k_empty(s), 1);
@@ -114,9 +130,9 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(s_full(i), 1);
       ptx::mbar_init(s_empty(i), kSoftmaxThreads);
+      ptx::mbar_init(p_full(i), kSoftmaxThreads);
+      ptx::mbar_init(pv_done(i), 1);
     }
-    ptx::mbar_init(p_full, kSoftmaxThreads);
-    ptx::mbar_init(pv_done, 1);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_q);
@@ -135,22 +151,29 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      ptx::mbar_arrive_expect_tx(q_full, Q_BYTES);
-      if (p.q_heads_inner) ptx::tma_load_4d(q_smem, &tmap_q, q_full, 0, h, (int32_t)q0, b);
-      else ptx::tma_load_4d(q_smem, &tmap_q, q_full, 0, (int32_t)q0, h, b);
       int s = 0;
       uint32_t phase = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int32_t kv0 = j * BN;
-        if (!ptx::mbar_wait_relaxed(k_empty(s), phase ^ 1, abort_flag)) break;
-        ptx::mbar_arrive_expect_tx(k_full(s), KV_BYTES);
-        if (p.k_heads_inner) ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, h, kv0, b);
-        else ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, kv0, h, b);
-        if (!ptx::mbar_wait_relaxed(v_empty(s), phase ^ 1, abort_flag)) break;
-        ptx::mbar_arrive_expect_tx(v_full(s), KV_BYTES);
-        if (p.v_heads_inner) ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, h, kv0, b);
-        else ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, kv0, h, b);
-        if (++s == kStages) { s = 0; phase ^= 1; }
+      uint32_t item_count = 0;
+      bool ok = true;
+      for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++item_count) {
+        const Item it = decode_item(w, p);
+        // Q buffer is free once the previous item's last score MMA has read it
+        if (!ptx::mbar_wait_relaxed(q_empty, (item_count & 1) ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(q_full, Q_BYTES);
+        if (p.q_heads_inner) ptx::tma_load_4d(q_smem, &tmap_q, q_full, 0, it.h, (int32_t)it.q0, it.b);
+        else ptx::tma_load_4d(q_smem, &tmap_q, q_full, 0, (int32_t)it.q0, it.h, it.b);
+        for (int j = 0; j < it.n_tiles; ++j) {
+          const int32_t kv0 = j * BN;
+          if (!ptx::mbar_wait_relaxed(k_empty(s), phase ^ 1, abort_flag)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(k_full(s), KV_BYTES);
+          if (p.k_heads_inner) ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, it.h, kv0, it.b);
+          else ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, kv0, it.h, it.b);
+          if (!ptx::mbar_wait_relaxed(v_empty(s), phase ^ 1, abort_flag)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(v_full(s), KV_BYTES);
+          if (p.v_heads_inner) ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, it.h, kv0, it.b);
+          else ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, kv0, it.h, it.b);
+          if (++s == kStages) { s = 0; phase ^= 1; }
+        }
       }
     }
   } else if (warp == 1) {
@@ -158,125 +181,149 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::idesc_bf16_f32(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = ptx::idesc_bf16_f32(BM, D, 0, 1);
-      auto issue_qk = [&](int j, int stage, uint32_t stage_phase) -> bool {
-        const int buf = j & 1;
-        // the score buffer must have been drained by the softmax warps (tile j-2)
-        if (!ptx::mbar_wait(s_empty(buf), ((uint32_t)(j >> 1) & 1) ^ 1, abort_flag)) return false;
-        if (!ptx::mbar_wait(k_full(stage), stage_phase, abort_flag)) return false;
+      // Two cursors over the same sequence of (item, tile) pairs: the score stream (qk_*) runs
+      // one tile ahead of the P V stream (pv_*). g counts tiles over the CTA's whole life and
+      // selects the double-buffered S / P buffers and their barrier phases.
+      int64_t qk_w = blockIdx.x, pv_w = blockIdx.x;
+      int qk_j = 0, pv_j = 0;
+      int qk_n = qk_w < p.num_items ? decode_item(qk_w, p).n_tiles : 0;
+      int pv_n = qk_n;
+      uint32_t qk_g = 0, pv_g = 0, qk_items = 0;
+      int ks = 0, vs = 0;
+      uint32_t kphase = 0, vphase = 0;
+      bool ok = true;
+
+      auto issue_qk = [&]() -> bool {
+        if (qk_j == 0 && !ptx::mbar_wait(q_full, qk_items & 1, abort_flag)) return false;
+        const int buf = qk_g & 1;
+        // the score buffer must have been drained by the softmax warps (tile g-2)
+        if (!ptx::mbar_wait(s_empty(buf), ((qk_g >> 1) & 1) ^ 1, abort_flag)) return false;
+        if (!ptx::mbar_wait(k_full(ks), kphase, abort_flag)) return false;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem + (buf ? TMEM_S1 : TMEM_S0);
-        const uint32_t kb = k_smem + stage * KV_BYTES;
+        const uint32_t kb = k_smem + ks * KV_BYTES;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
           const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
           ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
         }
-        ptx::tc_commit(k_empty(stage));
+        ptx::tc_commit(k_empty(ks));
         ptx::tc_commit(s_full(buf));
+        if (++ks == kStages) { ks = 0; kphase ^= 1; }
+        ++qk_g;
+        if (++qk_j == qk_n) {
+          ptx::tc_commit(q_empty);  // last score MMA of the item: Q may be overwritten
+          ++qk_items;
+          qk_j = 0;
+          qk_w += gridDim.x;
+          qk_n = qk_w < p.num_items ? decode_item(qk_w, p).n_tiles : 0;
+        }
         return true;
       };
-      bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
-      int ks = 0;
-      uint32_t kphase = 0;  // ring position of the next K tile to multiply
-      int vs = 0;
-      uint32_t vphase = 0;  // ring position of the next V tile to multiply
-      if (ok && n_tiles > 0) {
-        ok = issue_qk(0, ks, kphase);
-        if (++ks == kStages) { ks = 0; kphase ^= 1; }
-      }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          ok = issue_qk(j + 1, ks, kphase);
-          if (++ks == kStages) { ks = 0; kphase ^= 1; }
+
+      if (qk_n > 0) ok = issue_qk();
+      while (ok && pv_w < p.num_items) {
+        if (qk_w < p.num_items) {
+          ok = issue_qk();
           if (!ok) break;
         }
-        if (!ptx::mbar_wait(p_full, (uint32_t)j & 1, abort_flag)) { ok = false; break; }
+        const int pbuf = pv_g & 1;
+        if (!ptx::mbar_wait(p_full(pbuf), (pv_g >> 1) & 1, abort_flag)) { ok = false; break; }
         if (!ptx::mbar_wait(v_full(vs), vphase, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t vb = v_smem + vs * KV_BYTES;
+        const uint32_t pb = p_smem + pbuf * P_BYTES;
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t a_desc = ptx::smem_desc_sw128(p_smem + k * 32, 0, 1024);
+          const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
           // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
           const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
-          ptx::mma_f16_ss(tmem + TMEM_O, a_desc, b_desc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          ptx::mma_f16_ss(tmem + TMEM_O, a_desc, b_desc, idesc_pv, (pv_j > 0 || k > 0) ? 1u : 0u);
         }
         ptx::tc_commit(v_empty(vs));
-        ptx::tc_commit(pv_done);
+        ptx::tc_commit(pv_done(pbuf));
         if (++vs == kStages) { vs = 0; vphase ^= 1; }
+        ++pv_g;
+        if (++pv_j == pv_n) {
+          pv_j = 0;
+          pv_w += gridDim.x;
+          pv_n = pv_w < p.num_items ? decode_item(pv_w, p).n_tiles : 0;
+        }
       }
     }
   } else {
     // ---------------- softmax + output (warps 2..5), one thread per query row ----------------
     const int quad = warp & 3;
     const int r = quad * 32 + lane;          // row inside the tile == TMEM lane
-    const int64_t row = q0 + r;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    float m_ref = -INFINITY;  // maximum the stored P / O are relative to (log2 domain)
-    float l = 0.0f;
+    uint32_t g = 0;  // tiles processed by this CTA so far
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int buf = j & 1;
-      // wait results are made warp-uniform: the TMEM loads and votes below need the whole warp
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(buf), (uint32_t)(j >> 1) & 1, abort_flag))) { ok = false; break; }
-      ptx::tc_fence_after_sync();
-      uint32_t raw[2][32];
-      const uint32_t s_addr = tmem + (buf ? TMEM_S1 : TMEM_S0) + lane_addr;
-      ptx::tmem_ld_32x32b_x32(s_addr, raw[0]);
-      ptx::tmem_ld_32x32b_x32(s_addr + 32, raw[1]);
-      ptx::tmem_ld_wait();
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(s_empty(buf));
-
-      const int64_t kv0 = (int64_t)j * BN;
-      const bool need_mask = (p.causal && kv0 + BN - 1 > q0) || (kv0 + BN > p.kv_len);
-      if (need_mask) {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const int64_t key = kv0 + c;
-          if (key >= p.kv_len || (p.causal && key > row)) raw[c >> 5][c & 31] = 0xff800000u;  // -inf
-        }
-      }
-      // row maximum of the raw scores, four independent chains (scale > 0, so the scaled maximum
-      // is the maximum scaled)
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(raw[c >> 5][(c & 31) + 2 * u]),
-                                     __uint_as_float(raw[c >> 5][(c & 31) + 2 * u + 1])));
-      }
-      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
-      // lazy rescale: follow the true maximum only when it ran away by more than 2^8
-      float alpha = 1.0f;
-      if (tile_max > m_ref + 8.0f) {
-        alpha = ex2(m_ref - tile_max);  // m_ref == -inf on the first tile: alpha = 0
-        m_ref = tile_max;
-        l *= alpha;
-      }
-      const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-      const float2 negm2 = make_float2(neg_m, neg_m);
-      uint32_t packed[32];
-      float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
-#pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        // p = exp2(s * scale * log2e - m): one packed FMA for two scores, then two MUFU ops
-        const float2 s2 = make_float2(__uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[c >> 5][(c & 31) + 1]));
-        const float2 e2 = __ffma2_rn(s2, scale2, negm2);
-        const float2 p2 = make_float2(ex2(e2.x), ex2(e2.y));
-        sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], p2);
-        packed[c >> 1] = pack_bf16x2(p2.x, p2.y);
-      }
-      l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
-
-      // P buffer and O accumulator are free once the previous P V has completed
-      if (j > 0) {
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done, (uint32_t)(j - 1) & 1, abort_flag))) { ok = false; break; }
+    for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
+      const Item it = decode_item(w, p);
+      const int64_t row = it.q0 + r;
+      float m_ref = -INFINITY;  // maximum the stored P / O are relative to (log2 domain)
+      float l = 0.0f;
+      for (int j = 0; j < it.n_tiles; ++j, ++g) {
+        const int buf = g & 1;
+        // wait results are made warp-uniform: the TMEM loads and votes below need the whole warp
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(buf), (g >> 1) & 1, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+        uint32_t raw[2][32];
+        const uint32_t s_addr = tmem + (buf ? TMEM_S1 : TMEM_S0) + lane_addr;
+        ptx::tmem_ld_32x32b_x32(s_addr, raw[0]);
+        ptx::tmem_ld_32x32b_x32(s_addr + 32, raw[1]);
+        ptx::tmem_ld_wait();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(s_empty(buf));
+
+        const int64_t kv0 = (int64_t)j * BN;
+        const bool need_mask = (p.causal && kv0 + BN - 1 > it.q0) || (kv0 + BN > p.kv_len);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const int64_t key = kv0 + c;
+            if (key >= p.kv_len || (p.causal && key > row)) raw[c >> 5][c & 31] = 0xff800000u;  // -inf
+          }
+        }
+        // row maximum of the raw scores, four independent chains (scale > 0, so the scaled
+        // maximum is the maximum scaled)
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(raw[c >> 5][(c & 31) + 2 * u]),
+                                       __uint_as_float(raw[c >> 5][(c & 31) + 2 * u + 1])));
+        }
+        const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        // lazy rescale: follow the true maximum only when it ran away by more than 2^8
+        float alpha = 1.0f;
+        if (tile_max > m_ref + 8.0f) {
+          alpha = ex2(m_ref - tile_max);  // m_ref == -inf on the first tile: alpha = 0
+          m_ref = tile_max;
+          l *= alpha;
+        }
+        const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 negm2 = make_float2(neg_m, neg_m);
+        uint32_t packed[32];
+        float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          // p = exp2(s * scale * log2e - m): one packed FMA for two scores, then two MUFU ops
+          const float2 s2 = make_float2(__uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[c >> 5][(c & 31) + 1]));
+          const float2 e2 = __ffma2_rn(s2, scale2, negm2);
+          const float2 p2 = make_float2(ex2(e2.x), ex2(e2.y));
+          sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], p2);
+          packed[c >> 1] = pack_bf16x2(p2.x, p2.y);
+        }
+        l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+
+        // O may only be rescaled once the previous P V of this item has landed in it
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done((g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
+          ptx::tc_fence_after_sync();
           uint32_t o[2][32];
           ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
           ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
@@ -290,51 +337,45 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           ptx::tmem_st_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
           ptx::tmem_st_wait();
         }
-      }
-      // P row r, 64 bf16 = 8 chunks of 16 bytes, 128-byte swizzle: chunk index XOR (row mod 8)
-      {
-        uint8_t* prow = smem + SMEM_P + r * 128;
+        // this P buffer was last read by the P V of tile g-2
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done(buf), ((g >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
+        // P row r, 64 bf16 = 8 chunks of 16 bytes, 128-byte swizzle: chunk index XOR (row mod 8)
+        {
+          uint8_t* prow = smem + SMEM_P + buf * P_BYTES + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v4;
+          for (int c = 0; c < 8; ++c) {
+            uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v4;
+          }
         }
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(p_full(buf));
       }
-      ptx::fence_proxy_async_smem();
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(p_full);
-    }
+      if (!ok) break;
 
-    if (ok && n_tiles > 0)
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1, abort_flag));
-    if (ok) {
+      // ---- item epilogue: O / l -> global ----
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done((g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      float ov[64];
-      if (n_tiles > 0) {
-        uint32_t o[2][32];
-        ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
-        ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 64; ++c) ov[c] = __uint_as_float(o[c >> 5][c & 31]);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) ov[c] = 0.0f;
-      }
+      uint32_t o[2][32];
+      ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
+      ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
       if (row < p.q_len) {
         const float inv = 1.0f / l;  // l == 0 (no visible key) gives NaN like torch
-        __nv_bfloat16* orow = p.o + b * p.os_b + h * p.os_h + row * p.os_t;
+        __nv_bfloat16* orow = p.o + it.b * p.os_b + it.h * p.os_h + row * p.os_t;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 t;
-          t.x = pack_bf16x2(ov[8 * c] * inv, ov[8 * c + 1] * inv);
-          t.y = pack_bf16x2(ov[8 * c + 2] * inv, ov[8 * c + 3] * inv);
-          t.z = pack_bf16x2(ov[8 * c + 4] * inv, ov[8 * c + 5] * inv);
-          t.w = pack_bf16x2(ov[8 * c + 6] * inv, ov[8 * c + 7] * inv);
+          t.x = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 1) & 31]) * inv);
+          t.y = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c + 2) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 3) & 31]) * inv);
+          t.z = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c + 4) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 5) & 31]) * inv);
+          t.w = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c + 6) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 7) & 31]) * inv);
           reinterpret_cast<uint4*>(orow)[c] = t;
         }
         if (p.lse != nullptr)
-          p.lse[((int64_t)b * p.heads + h) * p.q_len + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+          p.lse[((int64_t)it.b * p.heads + it.h) * p.q_len + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
       }
     }
   }
@@ -406,7 +447,6 @@ const char* sdpa_tcgen05_ineligible(const b200_sdpa_args& a) {
     return "stride not a multiple of 16 bytes";
   if (a.o_strides[2] % 8 != 0 || a.o_strides[1] % 8 != 0 || a.o_strides[0] % 8 != 0)
     return "output stride not a multiple of 16 bytes";
-  if (a.batch * a.heads > 65535) return "batch*heads above 65535";
   if (a.q_len > INT32_MAX - 256 || a.kv_len > INT32_MAX - 256) return "sequence too long";
   return nullptr;
 }
@@ -428,6 +468,8 @@ int32_t launch_sdpa_tcgen05(const b200_sdpa_args& a, cudaStream_t stream) {
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.causal = a.causal;
   p.q_tiles = (int)((a.q_len + BM - 1) / BM);
+  p.bh = a.batch * a.heads;
+  p.num_items = (int64_t)p.q_tiles * p.bh;
   p.status = device_status_ptr();
   B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "sdpa(tcgen05): device status word unavailable");
 
@@ -441,7 +483,8 @@ int32_t launch_sdpa_tcgen05(const b200_sdpa_args& a, cudaStream_t stream) {
                 cudaGetErrorString(e));
     attr_set[dev] = true;
   }
-  dim3 grid((unsigned)p.q_tiles, (unsigned)(a.batch * a.heads));
+  const int64_t slots = 2 * (int64_t)sm_count();  // two resident CTAs per SM
+  const unsigned grid = (unsigned)(p.num_items < slots ? p.num_items : slots);
   sdpa_tcgen05_kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(mq, mk, mv, p);
   B200_CHECK_LAUNCH("sdpa(tcgen05)");
   return B200_OK;
