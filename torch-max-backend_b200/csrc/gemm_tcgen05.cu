@@ -64,7 +64,6 @@ struct Params {
   int64_t num_tiles;
   unsigned int* status;
   int32_t fast_ok;  // pointers/pitches allow the branch-free vector epilogue on interior tiles
-  int32_t direct;   // interior tiles: store straight from the TMEM row layout (no smem staging)
 #ifdef B200_GEMM_PROBE
   int probe;  // timing probes of the epilogue stages (development builds only)
 #endif
@@ -186,7 +185,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tmem_full_bar(a), 1);
-      ptx::mbar_init(tmem_empty_bar(a), kEpilogueThreads);
+      ptx::mbar_init(tmem_empty_bar(a), kEpilogueWarps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -306,57 +305,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // warp-uniform result: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag))) break;
       ptx::tc_fence_after_sync();
-      if (fast && p.direct) {
-        // lane == row: each lane owns 32 consecutive columns of its row
-        const int64_t row = row0 + lane;
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const int col_in_tile = half * (BN / 2) + c * 32;
-          const int64_t col0 = n0 + col_in_tile;
-          if (col0 >= p.N) break;  // uniform: chunk entirely past the last column
-          float bv[32];
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int g4 = 0; g4 < 8; ++g4) {
-              float t4[4];
-              load4(p.bias, col0 + g4 * 4, p.bias_dtype, 4, t4);  // same address in every lane
-#pragma unroll
-              for (int j = 0; j < 4; ++j) bv[4 * g4 + j] = t4[j] * p.beta;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) bv[i] = 0.0f;
-          }
-          float4 res[8];
-          if (p.residual != nullptr) {
-            const float4* rrow = reinterpret_cast<const float4*>(static_cast<const float*>(p.residual) + row * p.residual_rs + col0);
-#pragma unroll
-            for (int g4 = 0; g4 < 8; ++g4) res[g4] = __ldg(rrow + g4);
-          }
-          uint32_t raw[32];
-          ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + col_in_tile) + ((uint32_t)(q * 32) << 16), raw);
-          ptx::tmem_ld_wait();
-          Tout* crow = cbase + row * p.c_rs + col0;
-#pragma unroll
-          for (int g4 = 0; g4 < 8; ++g4) {
-            float v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = fmaf(__uint_as_float(raw[4 * g4 + j]), p.alpha, bv[4 * g4 + j]);
-            if (p.epilogue != B200_EPILOGUE_NONE) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) v[j] = act(v[j], p.epilogue);
-            }
-            if (p.residual != nullptr) {
-              v[0] += res[g4].x; v[1] += res[g4].y; v[2] += res[g4].z; v[3] += res[g4].w;
-            }
-            store4_aligned(crow + g4 * 4, v);
-          }
-        }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(tmem_empty_bar(acc));
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        continue;
-      }
       if (fast) {
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
@@ -402,7 +350,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(tmem_empty_bar(acc));
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(tmem_empty_bar(acc));
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
@@ -480,7 +429,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();  // staging buffer is rewritten by the next chunk
       }
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(tmem_empty_bar(acc));
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tmem_empty_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }
@@ -553,8 +503,6 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
     if (g.residual != nullptr)
       ok = ok && g.residual_dtype == B200_F32 && aligned_to(g.residual, 16) && g.residual_row_stride % 4 == 0;
     p.fast_ok = ok ? 1 : 0;
-    const char* mode = getenv("B200_GEMM_EPILOGUE");  // "direct" | "staged" (tuning knob)
-    p.direct = (mode != nullptr && mode[0] == 'd') ? 1 : 0;
   }
 #ifdef B200_GEMM_PROBE
   p.probe = getenv("B200_GEMM_PROBE") ? atoi(getenv("B200_GEMM_PROBE")) : 0;

@@ -129,8 +129,10 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(s_full(i), 1);
-      ptx::mbar_init(s_empty(i), kSoftmaxThreads);
-      ptx::mbar_init(p_full(i), kSoftmaxThreads);
+      // one arrival per softmax warp (lane 0 after a warp sync): 128 single-thread arrivals on
+      // one barrier serialise in shared memory and were a large part of the per-tile latency
+      ptx::mbar_init(s_empty(i), kSoftmaxThreads / 32);
+      ptx::mbar_init(p_full(i), kSoftmaxThreads / 32);
       ptx::mbar_init(pv_done(i), 1);
     }
     *abort_flag = 0;
@@ -275,7 +277,8 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         ptx::tmem_ld_32x32b_x32(s_addr + 32, raw[1]);
         ptx::tmem_ld_wait();
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(s_empty(buf));
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(s_empty(buf));
 
         const int64_t kv0 = (int64_t)j * BN;
         const bool need_mask = (p.causal && kv0 + BN - 1 > it.q0) || (kv0 + BN > p.kv_len);
@@ -348,9 +351,10 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v4;
           }
         }
-        ptx::fence_proxy_async_smem();
+        ptx::fence_proxy_async_smem();  // every writer: its P stores become visible to the MMA
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(p_full(buf));
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(p_full(buf));
       }
       if (!ok) break;
 
