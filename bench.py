@@ -158,6 +158,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host thread it is allowed to
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
     model, cfg = build_model(args.model)
     model.set_precision("bf16")
     cores = torch.get_num_threads()
@@ -306,6 +308,7 @@ def main():
         "device_status": status,
     }
     if cpu_model is not None:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
         tps, per_step, sample = cpu_forward_tokens_per_s(cpu_model, cfg, args.cpu_sample_tokens, reps=2)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": sample}
