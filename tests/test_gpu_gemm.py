@@ -170,6 +170,47 @@ def test_tcgen05_bmm(ops, shape):
     assert_parity(y, torch.bmm(a.float(), b_cpu.float()), bf16=False, scale=sa[2] ** 0.5 * 4)
 
 
+ROUTE_SKINNY = 3
+
+
+@pytest.mark.parametrize("m", [1, 16, 64, 100])
+@pytest.mark.parametrize("k,n,b_layout", [(6400, 1600, "nk"), (3072, 768, "kn"), (1600, 1600, "nk")])
+def test_small_m_split_k_route(ops, m, k, n, b_layout):
+    """Decode shapes: K is split across CTAs into a scratch buffer and reduced in a fixed order.
+    Checked against the oracle, against the unsplit tensor-core route, and for run-to-run
+    bitwise determinism."""
+    import ctypes
+
+    from torch_mojo_backend import native
+
+    a = gen((m, k), torch.bfloat16, 50, 0.5)
+    if b_layout == "nk":
+        w = gen((n, k), torch.bfloat16, 51, 0.1)
+        b_cpu, b_gpu = w.t(), w.cuda().t()
+    else:
+        b_cpu = gen((k, n), torch.bfloat16, 51, 0.1)
+        b_gpu = b_cpu.cuda()
+    bias = gen((n,), torch.bfloat16, 52)
+    res = gen((m, n), torch.float32, 53)
+    ag = a.cuda()
+    c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    g = ops.fill_gemm_args(ag, b_gpu, bias.cuda(), res.cuda(), c, 1.0, 1.0, 1, 0)
+    auto = native.lib().b200_gemm_route(ctypes.byref(g))
+    need = native.lib().b200_gemm_workspace_bytes(ctypes.byref(g))
+    assert (auto == ROUTE_SKINNY) == (need > 0)
+    want = torch.nn.functional.gelu(a.float() @ b_cpu.float() + bias.float(), approximate="tanh") + res
+    y = ops.gemm(ag, b_gpu, bias.cuda(), res.cuda(), 1.0, 1.0, 1, torch.float32)
+    assert_parity(y, want, bf16=False)
+    if auto == ROUTE_SKINNY:
+        y_again = ops.gemm(ag, b_gpu, bias.cuda(), res.cuda(), 1.0, 1.0, 1, torch.float32)
+        assert torch.equal(y, y_again), "fixed-order reduction must be bitwise reproducible"
+        y_tc = ops.gemm(ag, b_gpu, bias.cuda(), res.cuda(), 1.0, 1.0, 1, torch.float32, ROUTE_TC)
+        assert_parity(y, y_tc, bf16=False)
+        # a missing workspace is an error, not a silent reroute
+        st = native.lib().b200_gemm(ctypes.byref(g), None, 0, None)
+        assert st == -4
+
+
 def test_auto_route_choices(ops):
     import ctypes
 

@@ -62,14 +62,14 @@ extern "C" B200_API int32_t b200_gemm_route(const b200_gemm_args* args) {
 }
 
 extern "C" B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_args* args) {
-  (void)args;
-  return 0;
+  if (validate(args) != B200_OK) return 0;
+  const b200_gemm_args& g = *args;
+  if (g.m == 0 || g.n == 0 || g.batch == 0) return 0;
+  return resolve_route(g) == B200_ROUTE_SKINNY ? gemm_skinny_scratch_bytes(g) : 0;
 }
 
 extern "C" B200_API int32_t b200_gemm(const b200_gemm_args* args, void* workspace, size_t workspace_bytes,
                              b200_stream_t stream_) {
-  (void)workspace;
-  (void)workspace_bytes;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   int32_t st = validate(args);
   if (st != B200_OK) return st;
@@ -79,7 +79,7 @@ extern "C" B200_API int32_t b200_gemm(const b200_gemm_args* args, void* workspac
   if (route < 0) return route;
   switch (route) {
     case B200_ROUTE_TCGEN05: return launch_gemm_tcgen05(g, stream);
-    case B200_ROUTE_SKINNY: return launch_gemm_skinny(g, stream);
+    case B200_ROUTE_SKINNY: return launch_gemm_skinny(g, workspace, workspace_bytes, stream);
     default: return launch_gemm_simt(g, stream);
   }
 }

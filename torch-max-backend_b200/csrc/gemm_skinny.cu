@@ -1,13 +1,127 @@
-// Small-M (decode) GEMM route. Placeholder until the weight-streaming kernel lands: reports
-// itself ineligible so that the router never selects it.
+// Small-M (decode-shaped) GEMM: the weights are read once and the problem is HBM-bound, but with
+// few rows there are too few output tiles to keep every SM streaming. The K range is therefore
+// split across CTAs: the tensor-core kernel runs in batched mode with one "batch" per K slice
+// and writes fp32 partial tiles into a scratch buffer [splits, m, n]; a second kernel adds the
+// slices in a fixed order (deterministic, no atomics) and applies the epilogue.
+//
+// The scratch buffer is the caller's workspace (b200_gemm_workspace_bytes says how large).
 #include "gemm_internal.cuh"
 
 namespace b200 {
+namespace {
 
-const char* gemm_skinny_ineligible(const b200_gemm_args&) { return "no small-M kernel in this build"; }
+constexpr int kReduceThreads = 256;
 
-int32_t launch_gemm_skinny(const b200_gemm_args&, cudaStream_t) {
-  B200_FAIL(B200_ERR_UNSUPPORTED, "gemm(skinny): not built");
+struct ReduceParams {
+  const float* partial;  // [splits, m, n]
+  const void* bias;
+  const void* residual;
+  int64_t m, n, splits;
+  int64_t c_rs, bias_rs, residual_rs;
+  float alpha, beta;
+  int32_t bias_dtype, residual_dtype, epilogue;
+};
+
+__device__ __forceinline__ float ld_any(const void* p, int64_t idx, int32_t dtype) {
+  return dtype == B200_F32 ? __ldg(static_cast<const float*>(p) + idx)
+                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+}
+
+// One thread per output element; consecutive threads walk a row, so partial reads and the
+// store are coalesced. Slices are added in index order.
+template <typename Tout>
+__global__ void __launch_bounds__(kReduceThreads)
+splitk_reduce_kernel(Tout* __restrict__ C, ReduceParams p) {
+  const int64_t idx = (int64_t)blockIdx.x * kReduceThreads + threadIdx.x;
+  const int64_t total = p.m * p.n;
+  if (idx >= total) return;
+  const int64_t row = idx / p.n, col = idx - row * p.n;
+  float acc = 0.0f;
+  for (int64_t s = 0; s < p.splits; ++s) acc += __ldg(p.partial + s * total + idx);
+  float v = p.alpha * acc;
+  if (p.bias != nullptr) v += p.beta * ld_any(p.bias, row * p.bias_rs + col, p.bias_dtype);
+  if (p.epilogue == B200_EPILOGUE_GELU_TANH) v = gelu_tanh_f32(v);
+  else if (p.epilogue == B200_EPILOGUE_GELU_ERF) v = gelu_erf_f32(v);
+  if (p.residual != nullptr) v += ld_any(p.residual, row * p.residual_rs + col, p.residual_dtype);
+  C[row * p.c_rs + col] = Elem<Tout>::from_f32(v);
+}
+
+}  // namespace
+
+// Number of K slices for these arguments; < 2 means the route does not apply.
+int gemm_skinny_splits(const b200_gemm_args& g) {
+  if (g.batch != 1 || g.m > 128 || g.m <= 0) return 0;
+  if (gemm_tcgen05_ineligible(g) != nullptr) return 0;
+  const int64_t tiles = (g.n + 127) / 128;
+  const int64_t by_sm = sm_count() / (tiles > 0 ? tiles : 1);
+  // scratch traffic (write + read of fp32 partials) must stay well below the weight bytes
+  const int64_t by_traffic = g.k / (8 * g.m);
+  int64_t limit = by_sm < by_traffic ? by_sm : by_traffic;
+  if (limit > 16) limit = 16;
+  for (int64_t s = limit; s >= 2; --s)
+    if (g.k % (s * 64) == 0) return (int)s;  // every slice a whole number of 64-wide k-blocks
+  return 0;
+}
+
+const char* gemm_skinny_ineligible(const b200_gemm_args& g) {
+  if (g.batch != 1) return "batched";
+  if (g.m > 128) return "more than 128 rows";
+  if (gemm_tcgen05_ineligible(g) != nullptr) return "operands not eligible for the tensor-core kernel";
+  if (gemm_skinny_splits(g) < 2) return "no useful K split (few SMs idle, shallow K, or K not divisible)";
+  return nullptr;
+}
+
+size_t gemm_skinny_scratch_bytes(const b200_gemm_args& g) {
+  const int s = gemm_skinny_splits(g);
+  return s < 2 ? 0 : (size_t)s * (size_t)g.m * (size_t)g.n * sizeof(float);
+}
+
+int32_t launch_gemm_skinny(const b200_gemm_args& g, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
+  const int splits = gemm_skinny_splits(g);
+  B200_REQUIRE(splits >= 2, B200_ERR_UNSUPPORTED, "gemm(skinny): no K split for these arguments");
+  const size_t need = (size_t)splits * (size_t)g.m * (size_t)g.n * sizeof(float);
+  B200_REQUIRE(scratch != nullptr && scratch_bytes >= need, B200_ERR_WORKSPACE,
+               "gemm(skinny): scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+  B200_REQUIRE(aligned_to(scratch, 16), B200_ERR_ALIGNMENT, "gemm(skinny): scratch not 16-byte aligned");
+
+  // Stage 1: batched tensor-core GEMM, one batch per K slice, fp32 partials into the scratch.
+  b200_gemm_args part = g;
+  const int64_t ks = g.k / splits;
+  part.k = ks;
+  part.batch = splits;
+  part.a_batch_stride = ks * g.a_col_stride;  // a_col_stride == 1 on this route
+  part.b_batch_stride = ks * g.b_row_stride;
+  part.c = scratch;
+  part.c_row_stride = g.n;
+  part.c_batch_stride = g.m * g.n;
+  part.bias = nullptr;
+  part.residual = nullptr;
+  part.alpha = 1.0f;
+  part.beta = 0.0f;
+  part.epilogue = B200_EPILOGUE_NONE;
+  part.out_dtype = B200_F32;
+  part.route = B200_ROUTE_TCGEN05;
+  const char* why = gemm_tcgen05_ineligible(part);
+  B200_REQUIRE(why == nullptr, B200_ERR_UNSUPPORTED, "gemm(skinny): K slices not eligible: %s", why);
+  int32_t st = launch_gemm_tcgen05(part, stream);
+  if (st != B200_OK) return st;
+
+  // Stage 2: add the slices and apply the epilogue.
+  ReduceParams rp;
+  rp.partial = static_cast<const float*>(scratch);
+  rp.bias = g.bias; rp.residual = g.residual;
+  rp.m = g.m; rp.n = g.n; rp.splits = splits;
+  rp.c_rs = g.c_row_stride; rp.bias_rs = g.bias_row_stride; rp.residual_rs = g.residual_row_stride;
+  rp.alpha = g.alpha; rp.beta = g.beta;
+  rp.bias_dtype = g.bias_dtype; rp.residual_dtype = g.residual_dtype; rp.epilogue = g.epilogue;
+  const int64_t total = g.m * g.n;
+  const unsigned grid = (unsigned)((total + kReduceThreads - 1) / kReduceThreads);
+  if (g.out_dtype == B200_F32)
+    splitk_reduce_kernel<float><<<grid, kReduceThreads, 0, stream>>>(static_cast<float*>(g.c), rp);
+  else
+    splitk_reduce_kernel<__nv_bfloat16><<<grid, kReduceThreads, 0, stream>>>(static_cast<__nv_bfloat16*>(g.c), rp);
+  B200_CHECK_LAUNCH("gemm(skinny reduce)");
+  return B200_OK;
 }
 
 }  // namespace b200

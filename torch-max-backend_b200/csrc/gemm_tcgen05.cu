@@ -287,30 +287,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // of a chunk are issued before they are needed.
       // (a column tile that ends on a 32-column boundary only has whole chunks inside or outside)
       const bool fast = p.fast_ok && m0 + BM <= p.M && (n0 + BN <= p.N || (p.N - n0) % 32 == 0);
-      // The bias row of this warp's columns is fetched before the accumulator is waited for.
-      float bias_pref[kChunks][4];
+      // beta * bias for the 4 columns this lane owns in chunk c (zeros without a row bias)
+      auto bias_of_chunk = [&](int c, float (&out)[4]) {
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) bias_pref[c][j] = 0.0f;
+        for (int j = 0; j < 4; ++j) out[j] = 0.0f;
         if (p.bias != nullptr && p.bias_rs == 0) {
           const int64_t col = n0 + half * (BN / 2) + c * 32 + c4 * 4;
           const int64_t rem = p.N - col;
           const int valid = rem >= 4 ? 4 : (rem > 0 ? (int)rem : 0);
-          if (valid > 0) load4(p.bias, col, p.bias_dtype, valid, bias_pref[c]);
+          if (valid > 0) load4(p.bias, col, p.bias_dtype, valid, out);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) bias_pref[c][j] *= p.beta;
+          for (int j = 0; j < 4; ++j) out[j] *= p.beta;
         }
-      }
+      };
+      // The first chunk's bias is fetched before the accumulator is waited for.
+      float bias_next[4];
+      bias_of_chunk(0, bias_next);
       // warp-uniform result: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag))) break;
       ptx::tc_fence_after_sync();
       if (fast) {
-#pragma unroll
+        // (kept rolled: the unrolled form of both epilogue paths overflowed the instruction cache)
+#pragma unroll 1
         for (int c = 0; c < kChunks; ++c) {
           const int col_in_tile = half * (BN / 2) + c * 32;
           if (n0 + col_in_tile >= p.N) break;  // uniform: chunk entirely past the last column
           const int64_t col = n0 + col_in_tile + c4 * 4;
+          float bias_cur[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) bias_cur[j] = bias_next[j];
+          if (c + 1 < kChunks) bias_of_chunk(c + 1, bias_next);  // in flight during this chunk
           // residual rows of this chunk: in flight while the accumulator chunk is staged
           float4 res[8];
           if (p.residual != nullptr) {
@@ -337,8 +343,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           Tout* crow = cbase + (row0 + rr) * p.c_rs + col;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            float v[4] = {fmaf(a4[i].x, p.alpha, bias_pref[c][0]), fmaf(a4[i].y, p.alpha, bias_pref[c][1]),
-                          fmaf(a4[i].z, p.alpha, bias_pref[c][2]), fmaf(a4[i].w, p.alpha, bias_pref[c][3])};
+            float v[4] = {fmaf(a4[i].x, p.alpha, bias_cur[0]), fmaf(a4[i].y, p.alpha, bias_cur[1]),
+                          fmaf(a4[i].z, p.alpha, bias_cur[2]), fmaf(a4[i].w, p.alpha, bias_cur[3])};
             if (p.epilogue != B200_EPILOGUE_NONE) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) v[j] = act(v[j], p.epilogue);
@@ -355,11 +361,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < kChunks; ++c) {
         const int col_in_tile = half * (BN / 2) + c * 32;
         const int64_t col0 = n0 + col_in_tile;
         if (col0 >= p.N || row0 >= p.M) break;  // uniform across the warp
+        float bias_cur[4];
+        if (c == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) bias_cur[j] = bias_next[j];
+        } else {
+          bias_of_chunk(c, bias_cur);
+        }
 #ifdef B200_GEMM_PROBE
         if (p.probe == 1) break;
 #endif
@@ -399,7 +412,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (p.bias != nullptr) {
               if (p.bias_rs == 0) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] += bias_pref[c][j];
+                for (int j = 0; j < 4; ++j) v[j] += bias_cur[j];
               } else {
                 float bb[4];
                 load4(p.bias, row * p.bias_rs + col, p.bias_dtype, valid, bb);

@@ -269,9 +269,15 @@ def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, 
             raise RuntimeError("gemm: batched gemm takes only a 1-D [n] bias")
         bias = bias.contiguous()
     g = fill_gemm_args(a, b, bias, residual, c, alpha, beta, epilogue, route)
+    workspace, workspace_bytes = None, 0
+    if m <= 128 and a.dim() == 2:
+        # only small-M problems can resolve to the split-K route, the one that needs scratch
+        workspace_bytes = native.lib().b200_gemm_workspace_bytes(ctypes.byref(g))
+        if workspace_bytes:
+            workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=device)
     start = _prof_begin(device)
     with torch.cuda.device(device):
-        status = native.lib().b200_gemm(ctypes.byref(g), None, 0, native.current_stream(device))
+        status = native.lib().b200_gemm(ctypes.byref(g), _ptr(workspace), workspace_bytes, native.current_stream(device))
     native.check("gemm", status)
     _launched(device, start, "gemm", 2.0 * g.m * g.n * g.k * g.batch, _nbytes(a, b, c, bias, residual))
     return c
