@@ -8,15 +8,19 @@
 //               the TMEM output accumulator. The score MMA stream runs one tile ahead of the
 //               P V stream, also across item boundaries, so the next item's first scores are
 //               ready when the softmax warps finish writing the previous item's output.
-//   warps 2-5   softmax, one thread per query row: pull S_j out of TMEM, online softmax in the
-//               exp2 domain with fp32 statistics, write P_j (rounded to bf16) into one of two
-//               shared-memory buffers as the K-major A operand of the second MMA, and rescale O
-//               in TMEM when the running maximum moved. The rescale is lazy: the reference
-//               maximum only follows the true maximum when it is more than 8 (a factor 256)
-//               behind, which keeps P inside bf16/fp32 range and skips most TMEM round trips.
-//               With two P buffers the softmax of tile j+1 does not wait for P_j V_j.
-// Two CTAs fit on one SM (96 KB of shared memory and 256 TMEM columns each), so the softmax of
-// one overlaps the MMAs of the other.
+//   warps 2-9   softmax, two threads per query row: the "a" thread (warps 2-5) owns keys 0-31 of
+//               every tile, the "b" thread (warps 6-9) keys 32-63. Each runs its own online
+//               softmax (exp2 domain, fp32 running maximum and sum) and owns its own output
+//               accumulator in TMEM (O_a += P[:, :32] V[:32], O_b += P[:, 32:] V[32:]), so the
+//               two never synchronise inside the key loop; the a thread merges the two partial
+//               results once per item: O = (O_a 2^(m_a-m) + O_b 2^(m_b-m)) / (l_a 2^(m_a-m) +
+//               l_b 2^(m_b-m)). P (rounded to bf16) goes into one of two shared-memory buffers as
+//               the K-major A operand of the second MMA, so the softmax of tile j+1 does not wait
+//               for P_j V_j. O is rescaled in TMEM lazily: the reference maximum only follows the
+//               true maximum when it is more than 8 (a factor 256) behind, which keeps P inside
+//               bf16/fp32 range and skips most TMEM round trips.
+// Two CTAs fit on one SM (97 KB of shared memory and 256 TMEM columns each): 16 softmax warps per
+// SM hide each other's dependency stalls, and one CTA's MMAs run under the other's softmax.
 //
 // Numerics: scores scaled by scale*log2(e), P = exp2(s - m), masked scores are -inf, P is rounded
 // to bf16 before the second MMA, O is divided by the fp32 row sum once at the end, and the
@@ -32,22 +36,23 @@ constexpr int BM = 128;   // query rows per work item
 constexpr int BN = 64;    // keys per tile
 constexpr int D = 64;     // head_dim
 constexpr int kStages = 3;
-constexpr int kThreads = 192;
-constexpr int kSoftmaxThreads = 128;
+constexpr int kSoftmaxWarps = 8;
+constexpr int kThreads = 64 + kSoftmaxWarps * 32;
 constexpr int Q_BYTES = BM * D * 2;     // 16 KiB
 constexpr int KV_BYTES = BN * D * 2;    // 8 KiB
 constexpr int P_BYTES = BM * BN * 2;    // 16 KiB
 constexpr int kTmemCols = 256;
-constexpr int TMEM_S0 = 0, TMEM_S1 = 64, TMEM_O = 128;
+constexpr int TMEM_S0 = 0, TMEM_S1 = 64, TMEM_OA = 128, TMEM_OB = 192;
 
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + Q_BYTES;
 constexpr int SMEM_V = SMEM_K + kStages * KV_BYTES;
 constexpr int SMEM_P = SMEM_V + kStages * KV_BYTES;
-constexpr int SMEM_BAR = SMEM_P + 2 * P_BYTES;
+constexpr int SMEM_STATS = SMEM_P + 2 * P_BYTES;  // (m_b, l_b) per row, handed from b to a threads
+constexpr int SMEM_BAR = SMEM_STATS + BM * 8;
 // barriers: q_full, q_empty, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], s_empty[2],
-//           p_full[2], pv_done[2]
-constexpr int kNumBars = 2 + 4 * kStages + 8;
+//           p_full[2], pv_done[2], stat_full, stat_empty
+constexpr int kNumBars = 2 + 4 * kStages + 8 + 2;
 constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
 constexpr int SMEM_BYTES = SMEM_MISC + 16 + 1024;
 
@@ -112,6 +117,7 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto s_empty = [&](int b) { return bar + 8u * (2 + 4 * kStages + 2 + b); };
   auto p_full = [&](int b) { return bar + 8u * (2 + 4 * kStages + 4 + b); };
   auto pv_done = [&](int b) { return bar + 8u * (2 + 4 * kStages + 6 + b); };
+  const uint32_t stat_full = bar + 8u * (2 + 4 * kStages + 8), stat_empty = bar + 8u * (2 + 4 * kStages + 9);
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + SMEM_MISC);
   volatile uint32_t* tmem_holder = misc;
   volatile uint32_t* abort_flag = misc + 1;
@@ -131,10 +137,12 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       ptx::mbar_init(s_full(i), 1);
       // one arrival per softmax warp (lane 0 after a warp sync): 128 single-thread arrivals on
       // one barrier serialise in shared memory and were a large part of the per-tile latency
-      ptx::mbar_init(s_empty(i), kSoftmaxThreads / 32);
-      ptx::mbar_init(p_full(i), kSoftmaxThreads / 32);
+      ptx::mbar_init(s_empty(i), kSoftmaxWarps);
+      ptx::mbar_init(p_full(i), kSoftmaxWarps);
       ptx::mbar_init(pv_done(i), 1);
     }
+    ptx::mbar_init(stat_full, kSoftmaxWarps / 2);
+    ptx::mbar_init(stat_empty, kSoftmaxWarps / 2);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_q);
@@ -241,7 +249,10 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
           // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
           const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
-          ptx::mma_f16_ss(tmem + TMEM_O, a_desc, b_desc, idesc_pv, (pv_j > 0 || k > 0) ? 1u : 0u);
+          // keys 0-31 accumulate into O_a, keys 32-63 into O_b (independent softmax streams)
+          const int first = (k == 0 || k == 2);
+          ptx::mma_f16_ss(tmem + (k < 2 ? TMEM_OA : TMEM_OB), a_desc, b_desc, idesc_pv,
+                          (pv_j > 0 || !first) ? 1u : 0u);
         }
         ptx::tc_commit(v_empty(vs));
         ptx::tc_commit(pv_done(pbuf));
@@ -255,67 +266,68 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
     }
   } else {
-    // ---------------- softmax + output (warps 2..5), one thread per query row ----------------
+    // ---------------- softmax + output (warps 2..9), two threads per query row ----------------
     const int quad = warp & 3;
+    const int hf = (warp - 2) >> 2;          // 0: keys 0-31 of every tile ("a"), 1: keys 32-63 ("b")
     const int r = quad * 32 + lane;          // row inside the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    uint32_t g = 0;  // tiles processed by this CTA so far
+    const uint32_t o_mine = tmem + (hf ? TMEM_OB : TMEM_OA) + lane_addr;
+    float* stats = reinterpret_cast<float*>(smem + SMEM_STATS);
+    uint32_t g = 0;      // tiles processed by this CTA so far
+    uint32_t items = 0;  // items processed by this CTA so far
     bool ok = true;
-    for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
+    for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
       const Item it = decode_item(w, p);
       const int64_t row = it.q0 + r;
-      float m_ref = -INFINITY;  // maximum the stored P / O are relative to (log2 domain)
+      float m_ref = -INFINITY;  // maximum this thread's P / O are relative to (log2 domain)
       float l = 0.0f;
       for (int j = 0; j < it.n_tiles; ++j, ++g) {
         const int buf = g & 1;
         // wait results are made warp-uniform: the TMEM loads and votes below need the whole warp
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(buf), (g >> 1) & 1, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
-        uint32_t raw[2][32];
-        const uint32_t s_addr = tmem + (buf ? TMEM_S1 : TMEM_S0) + lane_addr;
-        ptx::tmem_ld_32x32b_x32(s_addr, raw[0]);
-        ptx::tmem_ld_32x32b_x32(s_addr + 32, raw[1]);
+        uint32_t raw[32];
+        ptx::tmem_ld_32x32b_x32(tmem + (buf ? TMEM_S1 : TMEM_S0) + hf * 32 + lane_addr, raw);
         ptx::tmem_ld_wait();
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(s_empty(buf));
 
-        const int64_t kv0 = (int64_t)j * BN;
-        const bool need_mask = (p.causal && kv0 + BN - 1 > it.q0) || (kv0 + BN > p.kv_len);
+        const int64_t kv0 = (int64_t)j * BN + hf * 32;  // first key of this thread's half
+        const bool need_mask = (p.causal && kv0 + 31 > it.q0) || (kv0 + 32 > p.kv_len);
         if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
+          for (int c = 0; c < 32; ++c) {
             const int64_t key = kv0 + c;
-            if (key >= p.kv_len || (p.causal && key > row)) raw[c >> 5][c & 31] = 0xff800000u;  // -inf
+            if (key >= p.kv_len || (p.causal && key > row)) raw[c] = 0xff800000u;  // -inf
           }
         }
-        // row maximum of the raw scores, four independent chains (scale > 0, so the scaled
-        // maximum is the maximum scaled)
+        // maximum of the raw scores, four independent chains (scale > 0, so the scaled maximum
+        // is the maximum scaled)
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 64; c += 8) {
+        for (int c = 0; c < 32; c += 8) {
 #pragma unroll
           for (int u = 0; u < 4; ++u)
-            mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(raw[c >> 5][(c & 31) + 2 * u]),
-                                       __uint_as_float(raw[c >> 5][(c & 31) + 2 * u + 1])));
+            mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(raw[c + 2 * u]), __uint_as_float(raw[c + 2 * u + 1])));
         }
         const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
         // lazy rescale: follow the true maximum only when it ran away by more than 2^8
         float alpha = 1.0f;
         if (tile_max > m_ref + 8.0f) {
-          alpha = ex2(m_ref - tile_max);  // m_ref == -inf on the first tile: alpha = 0
+          alpha = ex2(m_ref - tile_max);  // m_ref == -inf so far: alpha = 0
           m_ref = tile_max;
           l *= alpha;
         }
         const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         const float2 negm2 = make_float2(neg_m, neg_m);
-        uint32_t packed[32];
+        uint32_t packed[16];
         float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
-        for (int c = 0; c < 64; c += 2) {
+        for (int c = 0; c < 32; c += 2) {
           // p = exp2(s * scale * log2e - m): one packed FMA for two scores, then two MUFU ops
-          const float2 s2 = make_float2(__uint_as_float(raw[c >> 5][c & 31]), __uint_as_float(raw[c >> 5][(c & 31) + 1]));
+          const float2 s2 = make_float2(__uint_as_float(raw[c]), __uint_as_float(raw[c + 1]));
           const float2 e2 = __ffma2_rn(s2, scale2, negm2);
           const float2 p2 = make_float2(ex2(e2.x), ex2(e2.y));
           sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], p2);
@@ -323,32 +335,31 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
 
-        // O may only be rescaled once the previous P V of this item has landed in it
+        // this thread's accumulator may only be rescaled once the previous P V has landed in it
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
           if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done((g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
           ptx::tc_fence_after_sync();
-          uint32_t o[2][32];
-          ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
-          ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
-          ptx::tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            o[0][c] = __float_as_uint(__uint_as_float(o[0][c]) * alpha);
-            o[1][c] = __float_as_uint(__uint_as_float(o[1][c]) * alpha);
+          for (int hcol = 0; hcol < 2; ++hcol) {
+            uint32_t o[32];
+            ptx::tmem_ld_32x32b_x32(o_mine + hcol * 32, o);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            ptx::tmem_st_32x32b_x32(o_mine + hcol * 32, o);
           }
-          ptx::tmem_st_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
-          ptx::tmem_st_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
           ptx::tmem_st_wait();
         }
         // this P buffer was last read by the P V of tile g-2
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done(buf), ((g >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
-        // P row r, 64 bf16 = 8 chunks of 16 bytes, 128-byte swizzle: chunk index XOR (row mod 8)
+        // P row r: this thread's 32 bf16 are 16-byte chunks 4*hf .. 4*hf+3 of the 128-byte row,
+        // 128-byte swizzle: chunk index XOR (row mod 8)
         {
           uint8_t* prow = smem + SMEM_P + buf * P_BYTES + r * 128;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < 4; ++c) {
             uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v4;
+            *reinterpret_cast<uint4*>(prow + (((hf * 4 + c) ^ (r & 7)) << 4)) = v4;
           }
         }
         ptx::fence_proxy_async_smem();  // every writer: its P stores become visible to the MMA
@@ -358,29 +369,55 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       if (!ok) break;
 
-      // ---- item epilogue: O / l -> global ----
+      // ---- item epilogue ----
+      if (hf == 1) {
+        // b threads hand (m_b, l_b) to the a thread of the same row and move on
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(stat_empty, (items & 1) ^ 1, abort_flag))) { ok = false; break; }
+        stats[2 * r] = m_ref;
+        stats[2 * r + 1] = l;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(stat_full);  // mbarrier arrive has release semantics
+        continue;
+      }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(stat_full, items & 1, abort_flag))) { ok = false; break; }
+      const float m_b = stats[2 * r], l_b = stats[2 * r + 1];
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(stat_empty);
+      // both accumulators are complete once the last P V of the item is
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done((g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      uint32_t o[2][32];
-      ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr, o[0]);
-      ptx::tmem_ld_32x32b_x32(tmem + TMEM_O + lane_addr + 32, o[1]);
-      ptx::tmem_ld_wait();
-      ptx::tc_fence_before_sync();
-      if (row < p.q_len) {
-        const float inv = 1.0f / l;  // l == 0 (no visible key) gives NaN like torch
-        __nv_bfloat16* orow = p.o + it.b * p.os_b + it.h * p.os_h + row * p.os_t;
+      const float m_all = fmaxf(m_ref, m_b);
+      const float wa = (m_ref == -INFINITY) ? 0.0f : ex2(m_ref - m_all);
+      const float wb = (m_b == -INFINITY) ? 0.0f : ex2(m_b - m_all);
+      const float l_all = l * wa + l_b * wb;
+      const float inv = 1.0f / l_all;  // l_all == 0 (no visible key) gives NaN like torch
+      const float fa = wa * inv, fb = wb * inv;
+      __nv_bfloat16* orow = p.o + it.b * p.os_b + it.h * p.os_h + row * p.os_t;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4 t;
-          t.x = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 1) & 31]) * inv);
-          t.y = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c + 2) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 3) & 31]) * inv);
-          t.z = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c + 4) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 5) & 31]) * inv);
-          t.w = pack_bf16x2(__uint_as_float(o[c >> 2][(8 * c + 6) & 31]) * inv, __uint_as_float(o[c >> 2][(8 * c + 7) & 31]) * inv);
-          reinterpret_cast<uint4*>(orow)[c] = t;
+      for (int hcol = 0; hcol < 2; ++hcol) {
+        uint32_t oa[32], ob[32];
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_OA + lane_addr + hcol * 32, oa);
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_OB + lane_addr + hcol * 32, ob);
+        ptx::tmem_ld_wait();
+        if (row < p.q_len) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              v[e] = __uint_as_float(oa[8 * c + e]) * fa + __uint_as_float(ob[8 * c + e]) * fb;
+            uint4 t;
+            t.x = pack_bf16x2(v[0], v[1]);
+            t.y = pack_bf16x2(v[2], v[3]);
+            t.z = pack_bf16x2(v[4], v[5]);
+            t.w = pack_bf16x2(v[6], v[7]);
+            reinterpret_cast<uint4*>(orow)[hcol * 4 + c] = t;
+          }
         }
-        if (p.lse != nullptr)
-          p.lse[((int64_t)it.b * p.heads + it.h) * p.q_len + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
       }
+      ptx::tc_fence_before_sync();
+      if (row < p.q_len && p.lse != nullptr)
+        p.lse[((int64_t)it.b * p.heads + it.h) * p.q_len + row] = (m_all + log2f(l_all)) * 0.6931471805599453f;
     }
   }
 
