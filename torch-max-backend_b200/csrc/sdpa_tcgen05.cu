@@ -4,10 +4,11 @@
 // (batch, head)), heaviest items first. Inside a CTA:
 //   warp 0      TMA producer: Q of the item, then its K_j / V_j tiles (64 keys) into two 3-deep
 //               rings (128-byte swizzle). The rings keep streaming across item boundaries.
-//   warp 1      MMA issuer: S = Q K_j^T into one of two TMEM score buffers and O += P_j V_j into
-//               the TMEM output accumulator. The score MMA stream runs one tile ahead of the
-//               P V stream, also across item boundaries, so the next item's first scores are
-//               ready when the softmax warps finish writing the previous item's output.
+//   warp 1      score MMA issuer: S = Q K_j^T into one of two TMEM score buffers, up to two tiles
+//               ahead of the softmax, also across item boundaries.
+//   warp 10     P V MMA issuer: O += P_j V_j into the TMEM output accumulators once the softmax
+//               warps have published P_j. (Two issuing threads: one thread feeding both MMA
+//               streams was the pacing resource of the CTA.)
 //   warps 2-9   softmax, two threads per query row: the "a" thread (warps 2-5) owns keys 0-31 of
 //               every tile, the "b" thread (warps 6-9) keys 32-63. Each runs its own online
 //               softmax (exp2 domain, fp32 running maximum and sum) and owns its own output
@@ -37,7 +38,8 @@ constexpr int BN = 64;    // keys per tile
 constexpr int D = 64;     // head_dim
 constexpr int kStages = 3;
 constexpr int kSoftmaxWarps = 8;
-constexpr int kThreads = 64 + kSoftmaxWarps * 32;
+constexpr int kPvWarp = 2 + kSoftmaxWarps;             // warp index of the P V MMA issuer
+constexpr int kThreads = (kPvWarp + 1) * 32;
 constexpr int Q_BYTES = BM * D * 2;     // 16 KiB
 constexpr int KV_BYTES = BN * D * 2;    // 8 KiB
 constexpr int P_BYTES = BM * BN * 2;    // 16 KiB
@@ -50,7 +52,7 @@ constexpr int SMEM_V = SMEM_K + kStages * KV_BYTES;
 constexpr int SMEM_P = SMEM_V + kStages * KV_BYTES;
 constexpr int SMEM_STATS = SMEM_P + 2 * P_BYTES;  // (m_b, l_b) per row, handed from b to a threads
 constexpr int SMEM_BAR = SMEM_STATS + BM * 8;
-// barriers: q_full, q_empty, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], s_empty[2],
+// barriers: q_full, q_empty, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], (2 unused),
 //           p_full[2], pv_done[2], stat_full, stat_empty
 constexpr int kNumBars = 2 + 4 * kStages + 8 + 2;
 constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
@@ -114,7 +116,6 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto v_full = [&](int s) { return bar + 8u * (2 + 2 * kStages + s); };
   auto v_empty = [&](int s) { return bar + 8u * (2 + 3 * kStages + s); };
   auto s_full = [&](int b) { return bar + 8u * (2 + 4 * kStages + b); };
-  auto s_empty = [&](int b) { return bar + 8u * (2 + 4 * kStages + 2 + b); };
   auto p_full = [&](int b) { return bar + 8u * (2 + 4 * kStages + 4 + b); };
   auto pv_done = [&](int b) { return bar + 8u * (2 + 4 * kStages + 6 + b); };
   const uint32_t stat_full = bar + 8u * (2 + 4 * kStages + 8), stat_empty = bar + 8u * (2 + 4 * kStages + 9);
@@ -137,7 +138,6 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       ptx::mbar_init(s_full(i), 1);
       // one arrival per softmax warp (lane 0 after a warp sync): 128 single-thread arrivals on
       // one barrier serialise in shared memory and were a large part of the per-tile latency
-      ptx::mbar_init(s_empty(i), kSoftmaxWarps);
       ptx::mbar_init(p_full(i), kSoftmaxWarps);
       ptx::mbar_init(pv_done(i), 1);
     }
@@ -187,81 +187,67 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+    // ---------------- score MMA issuer: S_g = Q K_g^T ----------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::idesc_bf16_f32(BM, BN, 0, 0);
-      constexpr uint32_t idesc_pv = ptx::idesc_bf16_f32(BM, D, 0, 1);
-      // Two cursors over the same sequence of (item, tile) pairs: the score stream (qk_*) runs
-      // one tile ahead of the P V stream (pv_*). g counts tiles over the CTA's whole life and
-      // selects the double-buffered S / P buffers and their barrier phases.
-      int64_t qk_w = blockIdx.x, pv_w = blockIdx.x;
-      int qk_j = 0, pv_j = 0;
-      int qk_n = qk_w < p.num_items ? decode_item(qk_w, p).n_tiles : 0;
-      int pv_n = qk_n;
-      uint32_t qk_g = 0, pv_g = 0, qk_items = 0;
-      int ks = 0, vs = 0;
-      uint32_t kphase = 0, vphase = 0;
+      int ks = 0;
+      uint32_t kphase = 0, g = 0, items = 0;
       bool ok = true;
-
-      auto issue_qk = [&]() -> bool {
-        if (qk_j == 0 && !ptx::mbar_wait(q_full, qk_items & 1, abort_flag)) return false;
-        const int buf = qk_g & 1;
-        // the score buffer must have been drained by the softmax warps (tile g-2)
-        if (!ptx::mbar_wait(s_empty(buf), ((qk_g >> 1) & 1) ^ 1, abort_flag)) return false;
-        if (!ptx::mbar_wait(k_full(ks), kphase, abort_flag)) return false;
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem + (buf ? TMEM_S1 : TMEM_S0);
-        const uint32_t kb = k_smem + ks * KV_BYTES;
+      for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
+        const int n_tiles = decode_item(w, p).n_tiles;
+        if (!ptx::mbar_wait(q_full, items & 1, abort_flag)) break;
+        for (int j = 0; j < n_tiles; ++j, ++g) {
+          const int buf = g & 1;
+          // Score buffer `buf` held tile g-2. The softmax warps publish P_{g-2} only after they
+          // have pulled S_{g-2} out of TMEM, so that barrier also says the buffer is free.
+          if (!ptx::mbar_wait(p_full(buf), ((g >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(k_full(ks), kphase, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t d_tmem = tmem + (buf ? TMEM_S1 : TMEM_S0);
+          const uint32_t kb = k_smem + ks * KV_BYTES;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
-          const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
-          ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
+            const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
+            ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(k_empty(ks));
+          ptx::tc_commit(s_full(buf));
+          if (++ks == kStages) { ks = 0; kphase ^= 1; }
         }
-        ptx::tc_commit(k_empty(ks));
-        ptx::tc_commit(s_full(buf));
-        if (++ks == kStages) { ks = 0; kphase ^= 1; }
-        ++qk_g;
-        if (++qk_j == qk_n) {
-          ptx::tc_commit(q_empty);  // last score MMA of the item: Q may be overwritten
-          ++qk_items;
-          qk_j = 0;
-          qk_w += gridDim.x;
-          qk_n = qk_w < p.num_items ? decode_item(qk_w, p).n_tiles : 0;
-        }
-        return true;
-      };
-
-      if (qk_n > 0) ok = issue_qk();
-      while (ok && pv_w < p.num_items) {
-        if (qk_w < p.num_items) {
-          ok = issue_qk();
-          if (!ok) break;
-        }
-        const int pbuf = pv_g & 1;
-        if (!ptx::mbar_wait(p_full(pbuf), (pv_g >> 1) & 1, abort_flag)) { ok = false; break; }
-        if (!ptx::mbar_wait(v_full(vs), vphase, abort_flag)) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        const uint32_t vb = v_smem + vs * KV_BYTES;
-        const uint32_t pb = p_smem + pbuf * P_BYTES;
+        if (ok) ptx::tc_commit(q_empty);  // last score MMA of the item: Q may be overwritten
+      }
+    }
+  } else if (warp == kPvWarp) {
+    // ---------------- P V MMA issuer: O_a += P[:, :32] V[:32], O_b += P[:, 32:] V[32:] ----------------
+    // A thread of its own: issuing four MMAs and two commits costs several hundred cycles, and
+    // one thread doing both MMA streams was what set the pace of the whole CTA.
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = ptx::idesc_bf16_f32(BM, D, 0, 1);
+      int vs = 0;
+      uint32_t vphase = 0, g = 0;
+      bool ok = true;
+      for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
+        const int n_tiles = decode_item(w, p).n_tiles;
+        for (int j = 0; j < n_tiles; ++j, ++g) {
+          const int pbuf = g & 1;
+          if (!ptx::mbar_wait(p_full(pbuf), (g >> 1) & 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(v_full(vs), vphase, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t vb = v_smem + vs * KV_BYTES;
+          const uint32_t pb = p_smem + pbuf * P_BYTES;
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
-          // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
-          const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
-          // keys 0-31 accumulate into O_a, keys 32-63 into O_b (independent softmax streams)
-          const int first = (k == 0 || k == 2);
-          ptx::mma_f16_ss(tmem + (k < 2 ? TMEM_OA : TMEM_OB), a_desc, b_desc, idesc_pv,
-                          (pv_j > 0 || !first) ? 1u : 0u);
-        }
-        ptx::tc_commit(v_empty(vs));
-        ptx::tc_commit(pv_done(pbuf));
-        if (++vs == kStages) { vs = 0; vphase ^= 1; }
-        ++pv_g;
-        if (++pv_j == pv_n) {
-          pv_j = 0;
-          pv_w += gridDim.x;
-          pv_n = pv_w < p.num_items ? decode_item(pv_w, p).n_tiles : 0;
+          for (int k = 0; k < BN / 16; ++k) {
+            const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
+            // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
+            const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
+            const int first = (k == 0 || k == 2);
+            ptx::mma_f16_ss(tmem + (k < 2 ? TMEM_OA : TMEM_OB), a_desc, b_desc, idesc_pv,
+                            (j > 0 || !first) ? 1u : 0u);
+          }
+          ptx::tc_commit(v_empty(vs));
+          ptx::tc_commit(pv_done(pbuf));
+          if (++vs == kStages) { vs = 0; vphase ^= 1; }
         }
       }
     }
@@ -289,9 +275,6 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         uint32_t raw[32];
         ptx::tmem_ld_32x32b_x32(tmem + (buf ? TMEM_S1 : TMEM_S0) + hf * 32 + lane_addr, raw);
         ptx::tmem_ld_wait();
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(s_empty(buf));
 
         const int64_t kv0 = (int64_t)j * BN + hf * 32;  // first key of this thread's half
         const bool need_mask = (p.causal && kv0 + 31 > it.q0) || (kv0 + 32 > p.kv_len);
