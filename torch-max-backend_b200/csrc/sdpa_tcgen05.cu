@@ -4,11 +4,12 @@
 // (batch, head)), heaviest items first. Inside a CTA:
 //   warp 0      TMA producer: Q of the item, then its K_j / V_j tiles (64 keys) into two 3-deep
 //               rings (128-byte swizzle). The rings keep streaming across item boundaries.
-//   warp 1      score MMA issuer: S = Q K_j^T into one of two TMEM score buffers, up to two tiles
-//               ahead of the softmax, also across item boundaries.
-//   warp 10     P V MMA issuer: O += P_j V_j into the TMEM output accumulators once the softmax
-//               warps have published P_j. (Two issuing threads: one thread feeding both MMA
-//               streams was the pacing resource of the CTA.)
+//   warp 1      MMA issuer: S = Q K_j^T into one of two TMEM score buffers and O += P_j V_j into
+//               the TMEM output accumulators. The score stream runs one tile ahead of the P V
+//               stream, also across item boundaries. Every barrier wait and every MMA/commit
+//               costs this one thread a few hundred cycles, so the protocol is kept minimal: one
+//               "K and V landed" barrier per ring slot, and buffer reuse is implied by program
+//               order (a commit covers every MMA issued before it) instead of extra barriers.
 //   warps 2-9   softmax, two threads per query row: the "a" thread (warps 2-5) owns keys 0-31 of
 //               every tile, the "b" thread (warps 6-9) keys 32-63. Each runs its own online
 //               softmax (exp2 domain, fp32 running maximum and sum) and owns its own output
@@ -38,8 +39,7 @@ constexpr int BN = 64;    // keys per tile
 constexpr int D = 64;     // head_dim
 constexpr int kStages = 3;
 constexpr int kSoftmaxWarps = 8;
-constexpr int kPvWarp = 2 + kSoftmaxWarps;             // warp index of the P V MMA issuer
-constexpr int kThreads = (kPvWarp + 1) * 32;
+constexpr int kThreads = 64 + kSoftmaxWarps * 32;
 constexpr int Q_BYTES = BM * D * 2;     // 16 KiB
 constexpr int KV_BYTES = BN * D * 2;    // 8 KiB
 constexpr int P_BYTES = BM * BN * 2;    // 16 KiB
@@ -52,7 +52,7 @@ constexpr int SMEM_V = SMEM_K + kStages * KV_BYTES;
 constexpr int SMEM_P = SMEM_V + kStages * KV_BYTES;
 constexpr int SMEM_STATS = SMEM_P + 2 * P_BYTES;  // (m_b, l_b) per row, handed from b to a threads
 constexpr int SMEM_BAR = SMEM_STATS + BM * 8;
-// barriers: q_full, q_empty, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], (2 unused),
+// barriers: q_full, q_empty, kv_full[3], kv_empty[3], (6 unused), s_full[2], (2 unused),
 //           p_full[2], pv_done[2], stat_full, stat_empty
 constexpr int kNumBars = 2 + 4 * kStages + 8 + 2;
 constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
@@ -111,10 +111,8 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t q_smem = base + SMEM_Q, k_smem = base + SMEM_K, v_smem = base + SMEM_V, p_smem = base + SMEM_P;
   const uint32_t bar = base + SMEM_BAR;
   const uint32_t q_full = bar, q_empty = bar + 8;
-  auto k_full = [&](int s) { return bar + 8u * (2 + s); };
-  auto k_empty = [&](int s) { return bar + 8u * (2 + kStages + s); };
-  auto v_full = [&](int s) { return bar + 8u * (2 + 2 * kStages + s); };
-  auto v_empty = [&](int s) { return bar + 8u * (2 + 3 * kStages + s); };
+  auto kv_full = [&](int s) { return bar + 8u * (2 + s); };
+  auto kv_empty = [&](int s) { return bar + 8u * (2 + kStages + s); };
   auto s_full = [&](int b) { return bar + 8u * (2 + 4 * kStages + b); };
   auto p_full = [&](int b) { return bar + 8u * (2 + 4 * kStages + 4 + b); };
   auto pv_done = [&](int b) { return bar + 8u * (2 + 4 * kStages + 6 + b); };
@@ -129,10 +127,8 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_empty, 1);
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(k_full(s), 1);
-      ptx::mbar_init(k_empty(s), 1);
-      ptx::mbar_init(v_full(s), 1);
-      ptx::mbar_init(v_empty(s), 1);
+      ptx::mbar_init(kv_full(s), 1);
+      ptx::mbar_init(kv_empty(s), 1);
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(s_full(i), 1);
@@ -174,80 +170,94 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         else ptx::tma_load_4d(q_smem, &tmap_q, q_full, 0, (int32_t)it.q0, it.h, it.b);
         for (int j = 0; j < it.n_tiles; ++j) {
           const int32_t kv0 = j * BN;
-          if (!ptx::mbar_wait_relaxed(k_empty(s), phase ^ 1, abort_flag)) { ok = false; break; }
-          ptx::mbar_arrive_expect_tx(k_full(s), KV_BYTES);
-          if (p.k_heads_inner) ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, it.h, kv0, it.b);
-          else ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, k_full(s), 0, kv0, it.h, it.b);
-          if (!ptx::mbar_wait_relaxed(v_empty(s), phase ^ 1, abort_flag)) { ok = false; break; }
-          ptx::mbar_arrive_expect_tx(v_full(s), KV_BYTES);
-          if (p.v_heads_inner) ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, it.h, kv0, it.b);
-          else ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, v_full(s), 0, kv0, it.h, it.b);
+          if (!ptx::mbar_wait_relaxed(kv_empty(s), phase ^ 1, abort_flag)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(kv_full(s), 2 * KV_BYTES);  // K and V of the tile on one barrier
+          if (p.k_heads_inner) ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, kv_full(s), 0, it.h, kv0, it.b);
+          else ptx::tma_load_4d(k_smem + s * KV_BYTES, &tmap_k, kv_full(s), 0, kv0, it.h, it.b);
+          if (p.v_heads_inner) ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, kv_full(s), 0, it.h, kv0, it.b);
+          else ptx::tma_load_4d(v_smem + s * KV_BYTES, &tmap_v, kv_full(s), 0, kv0, it.h, it.b);
           if (++s == kStages) { s = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ---------------- score MMA issuer: S_g = Q K_g^T ----------------
+    // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::idesc_bf16_f32(BM, BN, 0, 0);
-      int ks = 0;
-      uint32_t kphase = 0, g = 0, items = 0;
-      bool ok = true;
-      for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
-        const int n_tiles = decode_item(w, p).n_tiles;
-        if (!ptx::mbar_wait(q_full, items & 1, abort_flag)) break;
-        for (int j = 0; j < n_tiles; ++j, ++g) {
-          const int buf = g & 1;
-          // Score buffer `buf` held tile g-2. The softmax warps publish P_{g-2} only after they
-          // have pulled S_{g-2} out of TMEM, so that barrier also says the buffer is free.
-          if (!ptx::mbar_wait(p_full(buf), ((g >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          if (!ptx::mbar_wait(k_full(ks), kphase, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
-          const uint32_t d_tmem = tmem + (buf ? TMEM_S1 : TMEM_S0);
-          const uint32_t kb = k_smem + ks * KV_BYTES;
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
-            const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
-            ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
-          }
-          ptx::tc_commit(k_empty(ks));
-          ptx::tc_commit(s_full(buf));
-          if (++ks == kStages) { ks = 0; kphase ^= 1; }
-        }
-        if (ok) ptx::tc_commit(q_empty);  // last score MMA of the item: Q may be overwritten
-      }
-    }
-  } else if (warp == kPvWarp) {
-    // ---------------- P V MMA issuer: O_a += P[:, :32] V[:32], O_b += P[:, 32:] V[32:] ----------------
-    // A thread of its own: issuing four MMAs and two commits costs several hundred cycles, and
-    // one thread doing both MMA streams was what set the pace of the whole CTA.
-    if (lane == 0) {
       constexpr uint32_t idesc_pv = ptx::idesc_bf16_f32(BM, D, 0, 1);
-      int vs = 0;
-      uint32_t vphase = 0, g = 0;
+      // Two cursors over the same sequence of (item, tile) pairs: the score stream (qk_*) runs
+      // one tile ahead of the P V stream (pv_*). g counts tiles over the CTA's whole life; tile g
+      // uses score buffer g & 1, P buffer g & 1 and K/V ring slot g % kStages.
+      //
+      // Reuse without extra barriers, from this thread's program order
+      //   ... PV(g-2), QK(g), wait p_full(g-1), PV(g-1), QK(g+1), ...
+      //  * score buffer of QK(g+1) held S(g-1): p_full(g-1) was waited for just before, and the
+      //    softmax warps publish P only after pulling S out of TMEM;
+      //  * P buffer g & 1 is rewritten by the softmax of tile g after it has seen s_full(g); that
+      //    commit was issued after PV(g-2), and a commit covers every MMA issued before it.
+      int64_t qk_w = blockIdx.x, pv_w = blockIdx.x;
+      int qk_j = 0, pv_j = 0;
+      int qk_n = qk_w < p.num_items ? decode_item(qk_w, p).n_tiles : 0;
+      int pv_n = qk_n;
+      uint32_t qk_g = 0, pv_g = 0, qk_items = 0;
+      int qk_slot = 0, pv_slot = 0;
+      uint32_t qk_phase = 0;
       bool ok = true;
-      for (int64_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
-        const int n_tiles = decode_item(w, p).n_tiles;
-        for (int j = 0; j < n_tiles; ++j, ++g) {
-          const int pbuf = g & 1;
-          if (!ptx::mbar_wait(p_full(pbuf), (g >> 1) & 1, abort_flag)) { ok = false; break; }
-          if (!ptx::mbar_wait(v_full(vs), vphase, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
-          const uint32_t vb = v_smem + vs * KV_BYTES;
-          const uint32_t pb = p_smem + pbuf * P_BYTES;
+
+      auto issue_qk = [&]() -> bool {
+        if (qk_j == 0 && !ptx::mbar_wait(q_full, qk_items & 1, abort_flag)) return false;
+        if (!ptx::mbar_wait(kv_full(qk_slot), qk_phase, abort_flag)) return false;  // K and V landed
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem + ((qk_g & 1) ? TMEM_S1 : TMEM_S0);
+        const uint32_t kb = k_smem + qk_slot * KV_BYTES;
 #pragma unroll
-          for (int k = 0; k < BN / 16; ++k) {
-            const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
-            // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
-            const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
-            const int first = (k == 0 || k == 2);
-            ptx::mma_f16_ss(tmem + (k < 2 ? TMEM_OA : TMEM_OB), a_desc, b_desc, idesc_pv,
-                            (j > 0 || !first) ? 1u : 0u);
-          }
-          ptx::tc_commit(v_empty(vs));
-          ptx::tc_commit(pv_done(pbuf));
-          if (++vs == kStages) { vs = 0; vphase ^= 1; }
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
+          const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
+          ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
+        }
+        ptx::tc_commit(s_full(qk_g & 1));
+        if (++qk_slot == kStages) { qk_slot = 0; qk_phase ^= 1; }
+        ++qk_g;
+        if (++qk_j == qk_n) {
+          ptx::tc_commit(q_empty);  // last score MMA of the item: Q may be overwritten
+          ++qk_items;
+          qk_j = 0;
+          qk_w += gridDim.x;
+          qk_n = qk_w < p.num_items ? decode_item(qk_w, p).n_tiles : 0;
+        }
+        return true;
+      };
+
+      if (qk_n > 0) ok = issue_qk();
+      while (ok && pv_w < p.num_items) {
+        if (qk_w < p.num_items) {
+          ok = issue_qk();
+          if (!ok) break;
+        }
+        const int pbuf = pv_g & 1;
+        if (!ptx::mbar_wait(p_full(pbuf), (pv_g >> 1) & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t vb = v_smem + pv_slot * KV_BYTES;  // landed together with K (seen at QK time)
+        const uint32_t pb = p_smem + pbuf * P_BYTES;
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
+          // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
+          const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
+          // keys 0-31 accumulate into O_a, keys 32-63 into O_b (independent softmax streams)
+          const int first = (k == 0 || k == 2);
+          ptx::mma_f16_ss(tmem + (k < 2 ? TMEM_OA : TMEM_OB), a_desc, b_desc, idesc_pv,
+                          (pv_j > 0 || !first) ? 1u : 0u);
+        }
+        ptx::tc_commit(kv_empty(pv_slot));  // frees K and V of the tile
+        ptx::tc_commit(pv_done(pbuf));
+        if (++pv_slot == kStages) pv_slot = 0;
+        ++pv_g;
+        if (++pv_j == pv_n) {
+          pv_j = 0;
+          pv_w += gridDim.x;
+          pv_n = pv_w < p.num_items ? decode_item(pv_w, p).n_tiles : 0;
         }
       }
     }
@@ -333,8 +343,8 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           }
           ptx::tmem_st_wait();
         }
-        // this P buffer was last read by the P V of tile g-2
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(pv_done(buf), ((g >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
+        // P buffer `buf` was last read by the P V of tile g-2, which had completed before s_full(g)
+        // could arrive (see the MMA issuer), so it can be rewritten without another wait.
         // P row r: this thread's 32 bf16 are 16-byte chunks 4*hf .. 4*hf+3 of the 128-byte row,
         // 128-byte swizzle: chunk index XOR (row mod 8)
         {
