@@ -303,6 +303,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // The first chunk's bias is fetched before the accumulator is waited for.
       float bias_next[4];
       bias_of_chunk(0, bias_next);
+      // Interior tiles also prefetch the fp32 residual one chunk ahead (8 rows x 16 bytes per
+      // lane): under a saturated main loop a global load takes thousands of cycles, and exposing
+      // that once per chunk was what made residual epilogues slower than their main loops.
+      float4 res_next[8];
+      auto residual_of_chunk = [&](int c, float4 (&out)[8]) {
+        const int64_t col = n0 + half * (BN / 2) + c * 32 + c4 * 4;
+        if (col < p.N) {
+          const float* rbase = static_cast<const float*>(p.residual) + (row0 + rr) * p.residual_rs + col;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) out[i] = __ldg(reinterpret_cast<const float4*>(rbase + (int64_t)i * 4 * p.residual_rs));
+        }
+      };
+      if (fast && p.residual != nullptr) residual_of_chunk(0, res_next);
       // warp-uniform result: the TMEM loads below need the whole warp
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag))) break;
       ptx::tc_fence_after_sync();
@@ -317,12 +330,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int j = 0; j < 4; ++j) bias_cur[j] = bias_next[j];
           if (c + 1 < kChunks) bias_of_chunk(c + 1, bias_next);  // in flight during this chunk
-          // residual rows of this chunk: in flight while the accumulator chunk is staged
           float4 res[8];
           if (p.residual != nullptr) {
-            const float* rbase = static_cast<const float*>(p.residual) + (row0 + rr) * p.residual_rs + col;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) res[i] = __ldg(reinterpret_cast<const float4*>(rbase + (int64_t)i * 4 * p.residual_rs));
+            for (int i = 0; i < 8; ++i) res[i] = res_next[i];
+            if (c + 1 < kChunks) residual_of_chunk(c + 1, res_next);  // in flight during this chunk
           }
           uint32_t raw[32];
           ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + col_in_tile) + ((uint32_t)(q * 32) << 16), raw);
