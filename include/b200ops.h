@@ -150,6 +150,26 @@ B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_args* args);
 B200_API int32_t b200_gemm(const b200_gemm_args* args, void* workspace, size_t workspace_bytes,
                   b200_stream_t stream);
 
+/* Small-M GEMM (the split-K route of b200_gemm) for callers that must not allocate device
+ * memory and have no workspace to lend: a plugin running inside another engine's memory budget,
+ * a serving loop that froze its memory pool after start-up, a host language whose binding can
+ * only hand over the operand buffers it was given. The scratch for the partial sums is a static
+ * array of B200_STATIC_SCRATCH_BYTES inside the library (every GPU that loads the library keeps
+ * that much memory until the process exits). No cudaMalloc/cudaFree or other allocating call is
+ * made.
+ *  - Same arguments and result as b200_gemm; only problems that b200_gemm_route() resolves to
+ *    B200_ROUTE_SKINNY are accepted (others: B200_ERR_UNSUPPORTED), and those that need more
+ *    scratch than the array holds are refused with B200_ERR_WORKSPACE (use b200_gemm).
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    before any stream capture is begun on that device.
+ *  - All calls share the one array: two calls whose kernels may overlap on the GPU (different
+ *    streams, or the same arguments from two threads) race on it. Serialise them on one stream.
+ *    The array keeps the previous call's partial sums; every element a call reads it has first
+ *    written itself, so no clearing is needed or done.
+ * This entry point has no counterpart in the reference. */
+#define B200_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+B200_API int32_t b200_gemm_small_m_static(const b200_gemm_args* args, b200_stream_t stream);
+
 /* ---- attention ----------------------------------------------------------------------- */
 
 /* softmax(scale * Q K^T [+ causal mask]) V per (batch, head); fp32 online softmax; writes

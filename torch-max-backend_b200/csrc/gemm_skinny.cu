@@ -7,8 +7,37 @@
 // The scratch buffer is the caller's workspace (b200_gemm_workspace_bytes says how large).
 #include "gemm_internal.cuh"
 
+#include <mutex>
+
 namespace b200 {
 namespace {
+
+// Scratch for b200_gemm_small_m_static: lives in the library image, so every GPU that loads the
+// library holds these bytes until the process exits. In host code this name is only a stand-in
+// for the symbol (not a device address); static_scratch_ptr() asks the runtime for the real one.
+static __device__ __align__(256) unsigned char g_static_scratch[B200_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+void* static_scratch_ptr() {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("gemm_small_m_static: cannot identify the current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      set_error("gemm_small_m_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cached[dev] = ptr;
+  }
+  return cached[dev];
+}
 
 constexpr int kReduceThreads = 256;
 
@@ -125,3 +154,31 @@ int32_t launch_gemm_skinny(const b200_gemm_args& g, void* scratch, size_t scratc
 }
 
 }  // namespace b200
+
+// The split-K small-M GEMM with its scratch taken from the library's own static device array
+// instead of a caller-provided workspace. See include/b200ops.h for the contract.
+extern "C" B200_API int32_t b200_gemm_small_m_static(const b200_gemm_args* args, b200_stream_t stream_) {
+  using namespace b200;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(args != nullptr, B200_ERR_INVALID_ARG, "gemm_small_m_static: null args");
+  const b200_gemm_args& g = *args;
+  B200_REQUIRE(g.m > 0 && g.n > 0 && g.k > 0 && g.batch == 1 && g.a != nullptr && g.b != nullptr && g.c != nullptr,
+               B200_ERR_INVALID_ARG, "gemm_small_m_static: needs one non-empty problem with non-null a, b, c");
+  B200_REQUIRE(valid_dtype(g.in_dtype) && valid_dtype(g.out_dtype) && (g.bias == nullptr || valid_dtype(g.bias_dtype)) &&
+                   (g.residual == nullptr || valid_dtype(g.residual_dtype)),
+               B200_ERR_INVALID_ARG, "gemm_small_m_static: bad dtype enum");
+  B200_REQUIRE(g.epilogue >= B200_EPILOGUE_NONE && g.epilogue <= B200_EPILOGUE_GELU_ERF, B200_ERR_INVALID_ARG,
+               "gemm_small_m_static: bad epilogue enum");
+  const char* why = gemm_skinny_ineligible(g);
+  B200_REQUIRE(why == nullptr, B200_ERR_UNSUPPORTED,
+               "gemm_small_m_static: these arguments do not take the split-K route (%s); use b200_gemm", why);
+  const size_t need = gemm_skinny_scratch_bytes(g);
+  B200_REQUIRE(need <= (size_t)B200_STATIC_SCRATCH_BYTES, B200_ERR_WORKSPACE,
+               "gemm_small_m_static: needs %zu bytes of scratch, the static array holds %d; use b200_gemm with a "
+               "workspace", need, B200_STATIC_SCRATCH_BYTES);
+  void* scratch = static_scratch_ptr();
+  if (scratch == nullptr) return B200_ERR_CUDA;
+  // Every partial element is written by the first stage before the second reads it, so nothing
+  // left over from an earlier call is ever read and the array needs no clearing.
+  return launch_gemm_skinny(g, scratch, (size_t)B200_STATIC_SCRATCH_BYTES, stream);
+}

@@ -37,6 +37,8 @@ ROUTE_SKINNY = 3
 
 ERR_DEVICE_TIMEOUT = -6
 
+STATIC_SCRATCH_BYTES = 8 * 1024 * 1024  # B200_STATIC_SCRATCH_BYTES of include/b200ops.h
+
 PACKAGE_ROOT = Path(__file__).resolve().parent.parent
 LIBRARY_PATH = PACKAGE_ROOT / "libb200ops.so"
 
@@ -53,6 +55,7 @@ EXPORTED_SYMBOLS = (
     "b200_gemm_route",
     "b200_gemm_workspace_bytes",
     "b200_gemm",
+    "b200_gemm_small_m_static",
     "b200_sdpa_route",
     "b200_sdpa_fwd",
 )
@@ -191,6 +194,8 @@ def _declare(dll: ctypes.CDLL) -> None:
     dll.b200_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmArgs)]
     dll.b200_gemm.restype = i32
     dll.b200_gemm.argtypes = [ctypes.POINTER(GemmArgs), vp, ctypes.c_size_t, vp]
+    dll.b200_gemm_small_m_static.restype = i32
+    dll.b200_gemm_small_m_static.argtypes = [ctypes.POINTER(GemmArgs), vp]
     dll.b200_sdpa_route.restype = i32
     dll.b200_sdpa_route.argtypes = [ctypes.POINTER(SdpaArgs)]
     dll.b200_sdpa_fwd.restype = i32
