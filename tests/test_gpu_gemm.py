@@ -138,6 +138,44 @@ def test_tcgen05_every_tile_width(ops, monkeypatch, tile_n, b_layout):
     assert_parity(y2, a2.float() @ w2.float().t() + bias[:n2].float(), bf16=True)
 
 
+@pytest.mark.parametrize("tile_n", [128, 192, 256])
+def test_tcgen05_cta_pair_kernel(ops, monkeypatch, tile_n):
+    """The CTA-pair kernel (two CTAs share a 256-row tile), forced on shapes it would not pick by
+    itself: ragged tails in M (second CTA partly or wholly past the last row), N and K, bias +
+    gelu + fp32 residual, batches; and bit-for-bit agreement with the single-CTA kernel."""
+    monkeypatch.setenv("B200_GEMM_TILE_N", str(tile_n))
+    for m, n, k in ((700, 1000, 328), (100, 520, 64), (1024, 768, 1600)):
+        a = gen((m, k), torch.bfloat16, 50, 0.5)
+        w = gen((n, k), torch.bfloat16, 51, 0.1)
+        bias = gen((n,), torch.bfloat16, 52)
+        res = gen((m, n), torch.float32, 53)
+        outs = {}
+        for pair in ("0", "1"):
+            monkeypatch.setenv("B200_GEMM_PAIR", pair)
+            outs[pair] = ops.gemm(a.cuda(), w.cuda().t(), bias.cuda(), res.cuda(), 1.0, 1.0, 1, torch.float32, ROUTE_TC)
+        want = torch.nn.functional.gelu(a.float() @ w.float().t() + bias.float(), approximate="tanh") + res
+        assert_parity(outs["1"], want, bf16=False)
+        assert torch.equal(outs["0"], outs["1"])
+    # batched, bf16 out
+    monkeypatch.setenv("B200_GEMM_PAIR", "1")
+    a3, w3 = gen((3, 300, 136), torch.bfloat16, 54, 0.5), gen((3, 200, 136), torch.bfloat16, 55, 0.1)
+    y3 = ops.gemm(a3.cuda(), w3.cuda().transpose(1, 2), None, None, 1.0, 1.0, 0, torch.bfloat16, ROUTE_TC)
+    assert_parity(y3, torch.bmm(a3.float(), w3.float().transpose(1, 2)), bf16=True)
+
+
+def test_tcgen05_cta_pair_kernel_is_the_default_for_large_problems(ops, monkeypatch):
+    """Without any override a large K-major problem takes the pair kernel; its result must equal
+    the single-CTA kernel's."""
+    m, n, k = 2048, 1536, 512
+    a, w = gen((m, k), torch.bfloat16, 56, 0.5), gen((n, k), torch.bfloat16, 57, 0.1)
+    monkeypatch.delenv("B200_GEMM_PAIR", raising=False)
+    y_default = ops.gemm(a.cuda(), w.cuda().t(), None, None, 1.0, 1.0, 0, torch.bfloat16, ROUTE_TC)
+    monkeypatch.setenv("B200_GEMM_PAIR", "0")
+    y_single = ops.gemm(a.cuda(), w.cuda().t(), None, None, 1.0, 1.0, 0, torch.bfloat16, ROUTE_TC)
+    assert_parity(y_default, a.float() @ w.float().t(), bf16=True)
+    assert torch.equal(y_default, y_single)
+
+
 def test_tcgen05_epilogues(ops):
     m, n, k = 512, 640, 256
     a, w = gen((m, k), torch.bfloat16, 15, 0.5), gen((n, k), torch.bfloat16, 16, 0.1)

@@ -3,9 +3,9 @@
 //
 //   warp 0      TMA producer: one lane streams 128xBK A tiles and BNxBK B tiles into a
 //               STAGES-deep ring (128-byte swizzle), signalling `full[s]` by transaction bytes.
-//   warp 1      MMA issuer: one lane waits `full[s]`, issues BK/16 tcgen05.mma (128 x BN x 16)
-//               per stage into one of two TMEM accumulators, and commits to `empty[s]`; after
-//               the last k-block it commits to `tmem_full[acc]`.
+//   warp 1      MMA issuer: the warp waits `full[s]` converged, one elected lane issues BK/16
+//               tcgen05.mma (128 x BN x 16) per stage into one of two TMEM accumulators and
+//               commits to `empty[s]`; after the last k-block it commits to `tmem_full[acc]`.
 //   warps 2-9   epilogue: wait `tmem_full[acc]`; each warp owns 32 rows (its TMEM lane quadrant)
 //               and half of the tile's columns. 32x32 chunks leave TMEM one row per lane, pass
 //               through a per-warp swizzled shared-memory staging buffer and come back one
@@ -17,6 +17,13 @@
 // Tiles are walked in bands of kBandM row-tiles (column-tile outer, row-tile inner inside a band):
 // a band's slice of A is re-used from L2 across all its column tiles while the (smaller) B stays
 // L2-resident.
+// Large problems with K-major B run the CTA-pair form (PAIR): clusters of two CTAs, each pair
+// owning a 256 x BN tile through tcgen05.mma.cta_group::2. Each CTA stages its own 128 rows of A
+// and its own BN/2 rows of B^T (plain TMA loads whose completion bytes are counted on the even
+// CTA's barrier), the even CTA's elected lane issues the 256 x BN x 16 MMAs for both and commits
+// to the barriers of both, and each CTA's epilogue warps drain their own 128 accumulator rows and
+// report to the even CTA's `tmem_empty`. A stage is a third smaller than the single-CTA stage of
+// the same BN, so the ring is six stages deep instead of four.
 // Every wait is bounded (ptx::mbar_wait); a CTA that gives up raises the device status word and
 // leaves through the common teardown, which frees its TMEM.
 #include "gemm_internal.cuh"
@@ -38,10 +45,14 @@ constexpr int kStageChunkBytes = 32 * 32 * 4;  // one 32x32 fp32 chunk per epilo
 constexpr int kBandM = 16;                     // row-tiles per raster band
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 
-template <int BN>
+// PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2). Each CTA stages its
+// own 128 rows of A and its own BN/2 rows of B^T, so a stage is a third smaller than the
+// single-CTA stage of the same BN and the shared-memory fill traffic per flop drops with it.
+template <int BN, bool PAIR = false>
 struct Cfg {
-  static constexpr int kStages = BN == 128 ? 6 : 4;
-  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;  // rows of B^T this CTA stages
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
+  static constexpr int kStages = PAIR ? 6 : (BN == 128 ? 6 : 4);
   static constexpr int kTmemCols = BN == 128 ? 256 : 512;  // two accumulators, rounded up to a power of two
   static constexpr int kSmemA = 0;
   static constexpr int kSmemB = kStages * A_STAGE_BYTES;
@@ -51,6 +62,16 @@ struct Cfg {
   static constexpr int kSmemMisc = kSmemBar + kNumBars * 8;
   static constexpr int kSmemBytes = kSmemMisc + 16 + 1024;  // +1024: manual 1 KiB alignment
 };
+
+#ifdef B200_GEMM_PROBE
+// development builds only: cycle counters of the MMA-issuing thread of CTA 0
+__device__ unsigned long long g_gemm_dbg[8];
+#define PROBE_T(var) const long long var = clock64()
+#define PROBE_ADD(slot, a, b) do { if (blockIdx.x == 0) g_gemm_dbg[slot] += (unsigned long long)((b) - (a)); } while (0)
+#else
+#define PROBE_T(var)
+#define PROBE_ADD(slot, a, b)
+#endif
 
 struct Params {
   int64_t M, N, K, batch;
@@ -85,16 +106,17 @@ __device__ __forceinline__ float act(float v, int32_t epilogue) {
 
 // Tile index -> (batch, row-tile, column-tile): bands of kBandM row-tiles, column-tile outer,
 // row-tile inner inside a band.
+template <int BAND = kBandM>
 __device__ __forceinline__ void tile_coords(int64_t t, const Params& p, int64_t& b, int32_t& mt, int32_t& nt) {
   const int64_t per_batch = (int64_t)p.tiles_m * p.tiles_n;
   b = t / per_batch;
   const int64_t r = t - b * per_batch;
-  const int64_t band_tiles = (int64_t)kBandM * p.tiles_n;
+  const int64_t band_tiles = (int64_t)BAND * p.tiles_n;
   const int32_t band = (int32_t)(r / band_tiles);
   const int32_t in_band = (int32_t)(r - (int64_t)band * band_tiles);
-  const int32_t rows_in_band = min(kBandM, p.tiles_m - band * kBandM);
+  const int32_t rows_in_band = min(BAND, p.tiles_m - band * BAND);
   nt = in_band / rows_in_band;
-  mt = band * kBandM + in_band % rows_in_band;
+  mt = band * BAND + in_band % rows_in_band;
 }
 
 __device__ __forceinline__ void load4(const void* p, int64_t idx, int32_t dtype, int valid, float (&out)[4]) {
@@ -154,12 +176,19 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, const float (&v)[4], 
   }
 }
 
-template <int BN, bool B_MN_MAJOR, typename Tout>
+template <int BN, bool B_MN_MAJOR, typename Tout, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, Tout* __restrict__ C, Params p) {
-  using C_ = Cfg<BN>;
+  static_assert(!(PAIR && B_MN_MAJOR), "the pair kernel stages B^T rows (K-major B) only");
+  using C_ = Cfg<BN, PAIR>;
   constexpr int kStages = C_::kStages;
+  constexpr int kTileM = PAIR ? 2 * BM : BM;        // rows of C per tile (per CTA pair when PAIR)
+  constexpr int kBand = PAIR ? kBandM / 2 : kBandM;  // same rows per raster band either way
+  // Rank inside the pair (0 = the CTA that issues the MMAs and owns the shared barriers).
+  const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;
+  const int64_t tile_first = PAIR ? (int64_t)(blockIdx.x >> 1) : (int64_t)blockIdx.x;
+  const int64_t tile_step = PAIR ? (int64_t)(gridDim.x >> 1) : (int64_t)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled operand tiles need a 1 KiB aligned base.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -185,7 +214,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tmem_full_bar(a), 1);
-      ptx::mbar_init(tmem_empty_bar(a), kEpilogueWarps);  // one arrival per epilogue warp
+      // one arrival per epilogue warp (of both CTAs when PAIR: the even CTA's barrier counts them)
+      ptx::mbar_init(tmem_empty_bar(a), PAIR ? 2 * kEpilogueWarps : kEpilogueWarps);
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -193,11 +223,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::prefetch_tensormap(&tmap_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), C_::kTmemCols);
-    ptx::tmem_relinquish();
+    if (PAIR) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), C_::kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), C_::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  if (PAIR) {
+    __syncthreads();
+    ptx::cluster_sync();  // the peer's barriers are initialised before anything signals them
+  } else {
+    __syncthreads();
+  }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -205,19 +245,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
+#ifdef B200_GEMM_PROBE
+    if (p.probe & 8) goto producer_done;  // no copies at all: the MMA thread does not wait for them
+#endif
     if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int64_t t = tile_first; t < p.num_tiles && ok; t += tile_step) {
         int64_t b;
         int32_t mt, nt;
-        tile_coords(t, p, b, mt, nt);
-        const int32_t m0 = mt * BM, n0 = nt * BN;
+        tile_coords<kBand>(t, p, b, mt, nt);
+        const int32_t m0 = mt * kTileM + (int32_t)rank * BM, n0 = nt * BN + (int32_t)rank * C_::B_ROWS * (PAIR ? 1 : 0);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
+#ifdef B200_GEMM_PROBE
+          if (p.probe & 64) {
+            if (!ptx::mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
+          } else
+#endif
           if (!ptx::mbar_wait_relaxed(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
-          ptx::mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + C_::B_STAGE_BYTES);
           const int32_t k0 = (int32_t)(kb * BK);
+          if (PAIR) {
+            // Both CTAs' copies are counted on the even CTA's barrier, which expects the bytes of
+            // both. (The peer's bytes may land before the expectation is posted; the phase cannot
+            // complete until the pending arrival below has happened.)
+            const uint32_t bar = ptx::mapa(full_bar(s), 0);
+            if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + C_::B_STAGE_BYTES));
+            ptx::tma_load_3d_pair(a_base + s * A_STAGE_BYTES, &tmap_a, bar, k0, m0, (int32_t)b);
+            ptx::tma_load_3d_pair(b_base + s * C_::B_STAGE_BYTES, &tmap_b, bar, k0, n0, (int32_t)b);
+            if (++s == kStages) { s = 0; phase ^= 1; }
+            continue;
+          }
+          ptx::mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + C_::B_STAGE_BYTES);
           ptx::tma_load_3d(a_base + s * A_STAGE_BYTES, &tmap_a, full_bar(s), k0, m0, (int32_t)b);
           if (!B_MN_MAJOR) {
             ptx::tma_load_3d(b_base + s * C_::B_STAGE_BYTES, &tmap_b, full_bar(s), k0, n0, (int32_t)b);
@@ -232,37 +291,83 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+#ifdef B200_GEMM_PROBE
+  producer_done:;
+#endif
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(BM, BN, 0, B_MN_MAJOR ? 1 : 0);
+    // The whole warp walks the loop converged (so that addresses and descriptors are warp-uniform
+    // values) and one elected lane issues the MMAs and commits; tcgen05.commit tracks the MMAs of
+    // the thread that executes it, and the election returns the same lane every time.
+    if (rank == 0) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(kTileM, BN, 0, B_MN_MAJOR ? 1 : 0);
       int s = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag)) break;
+      for (int64_t t = tile_first; t < p.num_tiles && ok; t += tile_step) {
+        PROBE_T(t0);
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag))) break;
         ptx::tc_fence_after_sync();
+        PROBE_T(t1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(full_bar(s), phase, abort_flag)) { ok = false; break; }
+#ifdef B200_GEMM_PROBE
+          if (p.probe & 32) __nanosleep(600);  // data surely landed: the wait below costs its floor
+#endif
+          PROBE_T(t2);
+#ifdef B200_GEMM_PROBE
+          if (!(p.probe & 8))
+#endif
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(s), phase, abort_flag))) { ok = false; break; }
           ptx::tc_fence_after_sync();
+          PROBE_T(t3);
           const uint32_t a_addr = a_base + s * A_STAGE_BYTES;
           const uint32_t b_addr = b_base + s * C_::B_STAGE_BYTES;
+          if (ptx::elect_one()) {
+#ifdef B200_GEMM_PROBE
+            if (!(p.probe & 16)) {
+#endif
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t a_desc = ptx::smem_desc_sw128(a_addr + k * (UMMA_K * 2), 0, 1024);
-            const uint64_t b_desc =
-                B_MN_MAJOR ? ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                           : ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 2), 0, 1024);
-            ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t a_desc = ptx::smem_desc_sw128(a_addr + k * (UMMA_K * 2), 0, 1024);
+              const uint64_t b_desc =
+                  B_MN_MAJOR ? ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                             : ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 2), 0, 1024);
+              if (PAIR) ptx::mma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              else ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+#ifdef B200_GEMM_PROBE
+            }
+#endif
+            PROBE_T(t4);
+            // frees the smem slot (in both CTAs when PAIR) when these MMAs have read it
+            if (PAIR) {
+              ptx::tc_commit_pair(ptx::mapa(empty_bar(s), 0));
+              ptx::tc_commit_pair(ptx::mapa(empty_bar(s), 1));
+            } else {
+              ptx::tc_commit(empty_bar(s));
+            }
+            // after the last k-block: the accumulator is complete when these MMAs are
+            if (kb == num_kb - 1) {
+              if (PAIR) {
+                ptx::tc_commit_pair(ptx::mapa(tmem_full_bar(acc), 0));
+                ptx::tc_commit_pair(ptx::mapa(tmem_full_bar(acc), 1));
+              } else {
+                ptx::tc_commit(tmem_full_bar(acc));
+              }
+            }
+            PROBE_T(t5);
+            PROBE_ADD(1, t2, t3);
+            PROBE_ADD(2, t3, t4);
+            PROBE_ADD(3, t4, t5);
+            PROBE_ADD(4, 0, 1);
+            if (kb == 0) { PROBE_ADD(0, t0, t1); PROBE_ADD(5, 0, 1); }
           }
-          ptx::tc_commit(empty_bar(s));  // frees the smem slot when these MMAs have read it
+          __syncwarp();
           if (++s == kStages) { s = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        ptx::tc_commit(tmem_full_bar(acc));
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -276,11 +381,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int c4 = lane & 7;             // 16-byte column group inside the chunk
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int64_t t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+    // where this warp reports a drained accumulator (the even CTA's barrier when PAIR)
+    const uint32_t tmem_empty_remote0 = PAIR ? ptx::mapa(tmem_empty_bar(0), 0) : 0u;
+    const uint32_t tmem_empty_remote1 = PAIR ? ptx::mapa(tmem_empty_bar(1), 0) : 0u;
+    for (int64_t t = tile_first; t < p.num_tiles; t += tile_step) {
       int64_t b;
       int32_t mt, nt;
-      tile_coords(t, p, b, mt, nt);
-      const int64_t m0 = (int64_t)mt * BM, n0 = (int64_t)nt * BN;
+      tile_coords<kBand>(t, p, b, mt, nt);
+      const int64_t m0 = (int64_t)mt * kTileM + (int64_t)rank * BM, n0 = (int64_t)nt * BN;
       Tout* cbase = C + b * p.c_bs;
       const int64_t row0 = m0 + q * 32;
       // Interior tiles with vector-friendly pointers take a branch-free path in which all loads
@@ -325,6 +433,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int c = 0; c < kChunks; ++c) {
           const int col_in_tile = half * (BN / 2) + c * 32;
           if (n0 + col_in_tile >= p.N) break;  // uniform: chunk entirely past the last column
+#ifdef B200_GEMM_PROBE
+          if (p.probe & 1) break;
+#endif
           const int64_t col = n0 + col_in_tile + c4 * 4;
           float bias_cur[4];
 #pragma unroll
@@ -369,7 +480,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(tmem_empty_bar(acc));
+        if (lane == 0) {
+          if (PAIR) ptx::mbar_arrive_cluster(acc ? tmem_empty_remote1 : tmem_empty_remote0);
+          else ptx::mbar_arrive(tmem_empty_bar(acc));
+        }
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
@@ -385,18 +499,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else {
           bias_of_chunk(c, bias_cur);
         }
-#ifdef B200_GEMM_PROBE
-        if (p.probe == 1) break;
-#endif
         uint32_t raw[32];
         ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t)(acc * BN + col_in_tile) + ((uint32_t)(q * 32) << 16), raw);
         ptx::tmem_ld_wait();
-#ifdef B200_GEMM_PROBE
-        if (p.probe == 2) {
-          if (raw[0] == 0x7fc12345u && raw[31] == 0x7fc54321u) cbase[0] = Elem<Tout>::from_f32(1.0f);
-          continue;
-        }
-#endif
         // lane == row: row `lane`, 8 groups of 4 columns, group index XOR (row mod 8)
 #pragma unroll
         for (int g4 = 0; g4 < 8; ++g4)
@@ -413,12 +518,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int r = i * 4 + rr;
           const int64_t row = row0 + r;
           const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
-#ifdef B200_GEMM_PROBE
-          if (p.probe == 3) {
-            if (a4.x == 123456.789f) cbase[0] = Elem<Tout>::from_f32(a4.y);
-            continue;
-          }
-#endif
           if (row < p.M && valid > 0) {
             float v[4] = {a4.x * p.alpha, a4.y * p.alpha, a4.z * p.alpha, a4.w * p.alpha};
             if (p.bias != nullptr) {
@@ -442,12 +541,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
               for (int j = 0; j < 4; ++j) v[j] += res[j];
             }
-#ifdef B200_GEMM_PROBE
-            if (p.probe == 4) {
-              if (v[0] == 123456.789f) cbase[0] = Elem<Tout>::from_f32(v[1]);
-              continue;
-            }
-#endif
             store4(cbase + row * p.c_rs + col, v, valid);
           }
         }
@@ -455,7 +548,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(tmem_empty_bar(acc));
+      if (lane == 0) {
+        if (PAIR) ptx::mbar_arrive_cluster(acc ? tmem_empty_remote1 : tmem_empty_remote0);
+        else ptx::mbar_arrive(tmem_empty_bar(acc));
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }
@@ -468,9 +564,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
     __syncthreads();
   }
+  if (PAIR) {
+    // Neither CTA may free its tensor memory or leave (its shared memory is read by the pair's
+    // MMAs and its barriers are signalled by the peer) before both are done.
+    ptx::tc_fence_before_sync();
+    ptx::cluster_sync();
+  }
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, C_::kTmemCols);
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, C_::kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, C_::kTmemCols);
   }
 }
 
@@ -478,6 +581,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 bool b_is_k_major(const b200_gemm_args& g) { return g.b_row_stride == 1 && (g.b_col_stride != 1 || g.n == 1); }
 bool b_is_n_major(const b200_gemm_args& g) { return g.b_col_stride == 1; }
+
+// Kernel parameters common to both launchers; tile_m x tile_n is the tile one CTA (or pair) owns.
+int32_t fill_params(const b200_gemm_args& g, Params& p, int tile_m, int tile_n, size_t out_elem_bytes) {
+  p.M = g.m; p.N = g.n; p.K = g.k; p.batch = g.batch;
+  p.c_rs = g.c_row_stride; p.c_bs = g.c_batch_stride;
+  p.bias = g.bias; p.residual = g.residual;
+  p.bias_rs = g.bias_row_stride; p.residual_rs = g.residual_row_stride;
+  p.alpha = g.alpha; p.beta = g.beta;
+  p.bias_dtype = g.bias_dtype; p.residual_dtype = g.residual_dtype; p.epilogue = g.epilogue;
+  p.tiles_m = (int32_t)((g.m + tile_m - 1) / tile_m);
+  p.tiles_n = (int32_t)((g.n + tile_n - 1) / tile_n);
+  p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * g.batch;
+  p.status = device_status_ptr();
+  B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "gemm(tcgen05): device status word unavailable");
+  {
+    const size_t out_vec = out_elem_bytes * 4;  // bytes of one 4-column group
+    bool ok = aligned_to(g.c, out_vec) && g.c_row_stride % 4 == 0 && (g.batch == 1 || g.c_batch_stride % 4 == 0);
+    if (g.bias != nullptr)
+      ok = ok && g.bias_row_stride == 0 && aligned_to(g.bias, g.bias_dtype == B200_F32 ? 16 : 8);
+    if (g.residual != nullptr)
+      ok = ok && g.residual_dtype == B200_F32 && aligned_to(g.residual, 16) && g.residual_row_stride % 4 == 0;
+    p.fast_ok = ok ? 1 : 0;
+  }
+#ifdef B200_GEMM_PROBE
+  p.probe = getenv("B200_GEMM_PROBE") ? atoi(getenv("B200_GEMM_PROBE")) : 0;
+#endif
+  return B200_OK;
+}
 
 template <int BN, bool B_MN_MAJOR, typename Tout>
 int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
@@ -509,25 +640,9 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
     if (st != B200_OK) return st;
   }
   Params p;
-  p.M = g.m; p.N = g.n; p.K = g.k; p.batch = g.batch;
-  p.c_rs = g.c_row_stride; p.c_bs = g.c_batch_stride;
-  p.bias = g.bias; p.residual = g.residual;
-  p.bias_rs = g.bias_row_stride; p.residual_rs = g.residual_row_stride;
-  p.alpha = g.alpha; p.beta = g.beta;
-  p.bias_dtype = g.bias_dtype; p.residual_dtype = g.residual_dtype; p.epilogue = g.epilogue;
-  p.tiles_m = (int32_t)((g.m + BM - 1) / BM);
-  p.tiles_n = (int32_t)((g.n + BN - 1) / BN);
-  p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * g.batch;
-  p.status = device_status_ptr();
-  B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "gemm(tcgen05): device status word unavailable");
   {
-    const size_t out_vec = sizeof(Tout) * 4;  // bytes of one 4-column group
-    bool ok = aligned_to(g.c, out_vec) && g.c_row_stride % 4 == 0 && (g.batch == 1 || g.c_batch_stride % 4 == 0);
-    if (g.bias != nullptr)
-      ok = ok && g.bias_row_stride == 0 && aligned_to(g.bias, g.bias_dtype == B200_F32 ? 16 : 8);
-    if (g.residual != nullptr)
-      ok = ok && g.residual_dtype == B200_F32 && aligned_to(g.residual, 16) && g.residual_row_stride % 4 == 0;
-    p.fast_ok = ok ? 1 : 0;
+    int32_t st = fill_params(g, p, BM, BN, sizeof(Tout));
+    if (st != B200_OK) return st;
   }
 #ifdef B200_GEMM_PROBE
   p.probe = getenv("B200_GEMM_PROBE") ? atoi(getenv("B200_GEMM_PROBE")) : 0;
@@ -548,6 +663,87 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
   kernel<<<(unsigned)grid, kThreads, C_::kSmemBytes, stream>>>(tmap_a, tmap_b, static_cast<Tout*>(g.c), p);
   B200_CHECK_LAUNCH("gemm(tcgen05)");
   return B200_OK;
+}
+
+// The CTA-pair form: clusters of two CTAs, each pair walking 256 x BN tiles.
+template <int BN, typename Tout>
+int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream) {
+  using C_ = Cfg<BN, true>;
+  static_assert(C_::kSmemBytes <= 227 * 1024, "pair configuration exceeds the shared memory of an SM");
+  CUtensorMap tmap_a, tmap_b;
+  {
+    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch};
+    const uint64_t strides[2] = {(uint64_t)g.a_row_stride * 2,
+                                 (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_row_stride * g.m) * 2};
+    const uint32_t box[3] = {BK, BM, 1};
+    int32_t st = encode_tensor_map(&tmap_a, B200_BF16, 3, g.a, dims, strides, box, true);
+    if (st != B200_OK) return st;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.batch};
+    const uint64_t strides[2] = {(uint64_t)g.b_col_stride * 2,
+                                 (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_col_stride * g.n) * 2};
+    const uint32_t box[3] = {BK, (uint32_t)C_::B_ROWS, 1};
+    int32_t st = encode_tensor_map(&tmap_b, B200_BF16, 3, g.b, dims, strides, box, true);
+    if (st != B200_OK) return st;
+  }
+  Params p;
+  int32_t st = fill_params(g, p, 2 * BM, BN, sizeof(Tout));
+  if (st != B200_OK) return st;
+
+  auto kernel = gemm_tcgen05_kernel<BN, false, Tout, true>;
+  static thread_local bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes);
+    if (e != cudaSuccess)
+      B200_FAIL(B200_ERR_CUDA, "gemm(tcgen05 pair): cannot opt in to %d bytes of shared memory: %s",
+                C_::kSmemBytes, cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  const int64_t pairs_avail = sm_count() / 2;
+  const int64_t pairs = p.num_tiles < pairs_avail ? p.num_tiles : pairs_avail;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C_::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmap_a, tmap_b, static_cast<Tout*>(g.c), p);
+  if (e != cudaSuccess)
+    B200_FAIL(B200_ERR_CUDA, "gemm(tcgen05 pair): launch failed: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+// Whether the CTA-pair kernel is used, and with which tile width (0 = not used).
+// B200_GEMM_PAIR=0 turns it off, =1 forces it wherever it is eligible (tuning and tests).
+int pick_pair_bn(const b200_gemm_args& g) {
+  if (!b_is_k_major(g)) return 0;
+  int mode = -1;
+  if (const char* v = getenv("B200_GEMM_PAIR")) mode = atoi(v);
+  if (mode == 0) return 0;
+  // Small problems have too few 256-row tiles to fill 74 pairs; they keep the single-CTA kernel.
+  if (mode != 1 && (g.m < 1024 || g.n < 512)) return 0;
+  if (const char* forced = getenv("B200_GEMM_TILE_N")) {
+    const int v = atoi(forced);
+    if (v == 128 || v == 192 || v == 256) return v;
+  }
+  const int64_t pairs = sm_count() / 2;
+  auto cost = [&](int bn, double per_col) {
+    const int64_t tiles = ((g.m + 2 * BM - 1) / (2 * BM)) * ((g.n + bn - 1) / bn) * g.batch;
+    const int64_t waves = (tiles + pairs - 1) / pairs;
+    return (double)waves * (bn * per_col + 24);
+  };
+  const double c256 = cost(256, 1.0), c192 = cost(192, 1.04), c128 = cost(128, 1.12);
+  if (c256 <= c192 && c256 <= c128) return 256;
+  return c192 <= c128 ? 192 : 128;
 }
 
 // Wave-quantisation cost of a tile width: waves of CTAs times the per-tile cost (main loop
@@ -598,8 +794,15 @@ const char* gemm_tcgen05_ineligible(const b200_gemm_args& g) {
 
 int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream) {
   const bool mn = !b_is_k_major(g);
-  const int bn = pick_bn(g);
   const bool f32 = g.out_dtype == B200_F32;
+  if (const int pbn = pick_pair_bn(g)) {
+#define PAIR_LAUNCH(BN_) (f32 ? launch_pair_cfg<BN_, float>(g, stream) : launch_pair_cfg<BN_, __nv_bfloat16>(g, stream))
+    if (pbn == 256) return PAIR_LAUNCH(256);
+    if (pbn == 192) return PAIR_LAUNCH(192);
+    return PAIR_LAUNCH(128);
+#undef PAIR_LAUNCH
+  }
+  const int bn = pick_bn(g);
 #define TC_LAUNCH(BN_, MN_)                                                   \
   (f32 ? launch_cfg<BN_, MN_, float>(g, stream) : launch_cfg<BN_, MN_, __nv_bfloat16>(g, stream))
   if (bn == 256) return mn ? TC_LAUNCH(256, true) : TC_LAUNCH(256, false);
@@ -609,3 +812,13 @@ int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream) {
 }
 
 }  // namespace b200
+
+#ifdef B200_GEMM_PROBE
+// development builds only: read and clear the MMA-thread cycle counters
+extern "C" B200_API int b200_probe_read(unsigned long long* host) {
+  int rc = (int)cudaMemcpyFromSymbol(host, b200::g_gemm_dbg, sizeof(unsigned long long) * 8);
+  unsigned long long zero[8] = {0};
+  cudaMemcpyToSymbol(b200::g_gemm_dbg, zero, sizeof(zero));
+  return rc;
+}
+#endif
