@@ -182,14 +182,17 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop converged (addresses and descriptors are then warp-uniform
+    // values) and one elected lane, the same on every election, issues the MMAs and the commits
+    // that track them.
+    {
       constexpr uint32_t idesc_qk = ptx::idesc_bf16_f32(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = ptx::idesc_bf16_f32(BM, D, 0, 1);
       // Two cursors over the same sequence of (item, tile) pairs: the score stream (qk_*) runs
       // one tile ahead of the P V stream (pv_*). g counts tiles over the CTA's whole life; tile g
       // uses score buffer g & 1, P buffer g & 1 and K/V ring slot g % kStages.
       //
-      // Reuse without extra barriers, from this thread's program order
+      // Reuse without extra barriers, from the issuing lane's program order
       //   ... PV(g-2), QK(g), wait p_full(g-1), PV(g-1), QK(g+1), ...
       //  * score buffer of QK(g+1) held S(g-1): p_full(g-1) was waited for just before, and the
       //    softmax warps publish P only after pulling S out of TMEM;
@@ -205,26 +208,34 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       bool ok = true;
 
       auto issue_qk = [&]() -> bool {
-        if (qk_j == 0 && !ptx::mbar_wait(q_full, qk_items & 1, abort_flag)) return false;
-        if (!ptx::mbar_wait(kv_full(qk_slot), qk_phase, abort_flag)) return false;  // K and V landed
+        bool landed = true;
+        if (qk_j == 0) landed = ptx::mbar_wait(q_full, qk_items & 1, abort_flag);
+        landed = landed && ptx::mbar_wait(kv_full(qk_slot), qk_phase, abort_flag);  // K and V of the tile
+        if (!__all_sync(0xffffffffu, landed)) return false;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem + ((qk_g & 1) ? TMEM_S1 : TMEM_S0);
         const uint32_t kb = k_smem + qk_slot * KV_BYTES;
+        const bool last_of_item = qk_j + 1 == qk_n;
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
-          const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
-          ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint64_t a_desc = ptx::smem_desc_sw128(q_smem + k * 32, 0, 1024);
+            const uint64_t b_desc = ptx::smem_desc_sw128(kb + k * 32, 0, 1024);
+            ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(s_full(qk_g & 1));
+          if (last_of_item) ptx::tc_commit(q_empty);  // last score MMA of the item: Q may be overwritten
         }
-        ptx::tc_commit(s_full(qk_g & 1));
+        __syncwarp();
         if (++qk_slot == kStages) { qk_slot = 0; qk_phase ^= 1; }
         ++qk_g;
-        if (++qk_j == qk_n) {
-          ptx::tc_commit(q_empty);  // last score MMA of the item: Q may be overwritten
+        if (last_of_item) {
           ++qk_items;
           qk_j = 0;
           qk_w += gridDim.x;
           qk_n = qk_w < p.num_items ? decode_item(qk_w, p).n_tiles : 0;
+        } else {
+          ++qk_j;
         }
         return true;
       };
@@ -236,22 +247,25 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (!ok) break;
         }
         const int pbuf = pv_g & 1;
-        if (!ptx::mbar_wait(p_full(pbuf), (pv_g >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(p_full(pbuf), (pv_g >> 1) & 1, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t vb = v_smem + pv_slot * KV_BYTES;  // landed together with K (seen at QK time)
         const uint32_t pb = p_smem + pbuf * P_BYTES;
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
-          // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
-          const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
-          // keys 0-31 accumulate into O_a, keys 32-63 into O_b (independent softmax streams)
-          const int first = (k == 0 || k == 2);
-          ptx::mma_f16_ss(tmem + (k < 2 ? TMEM_OA : TMEM_OB), a_desc, b_desc, idesc_pv,
-                          (pv_j > 0 || !first) ? 1u : 0u);
+          for (int k = 0; k < BN / 16; ++k) {
+            const uint64_t a_desc = ptx::smem_desc_sw128(pb + k * 32, 0, 1024);
+            // V tile is [keys][d] with d contiguous: MN-major B, 16 keys = two 8-row groups of 1 KiB
+            const uint64_t b_desc = ptx::smem_desc_sw128(vb + k * 2048, 0, 1024);
+            // keys 0-31 accumulate into O_a, keys 32-63 into O_b (independent softmax streams)
+            const int first = (k == 0 || k == 2);
+            ptx::mma_f16_ss(tmem + (k < 2 ? TMEM_OA : TMEM_OB), a_desc, b_desc, idesc_pv,
+                            (pv_j > 0 || !first) ? 1u : 0u);
+          }
+          ptx::tc_commit(kv_empty(pv_slot));  // frees K and V of the tile
+          ptx::tc_commit(pv_done(pbuf));
         }
-        ptx::tc_commit(kv_empty(pv_slot));  // frees K and V of the tile
-        ptx::tc_commit(pv_done(pbuf));
+        __syncwarp();
         if (++pv_slot == kStages) pv_slot = 0;
         ++pv_g;
         if (++pv_j == pv_n) {
