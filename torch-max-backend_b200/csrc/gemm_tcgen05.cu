@@ -63,16 +63,6 @@ struct Cfg {
   static constexpr int kSmemBytes = kSmemMisc + 16 + 1024;  // +1024: manual 1 KiB alignment
 };
 
-#ifdef B200_GEMM_PROBE
-// development builds only: cycle counters of the MMA-issuing thread of CTA 0
-__device__ unsigned long long g_gemm_dbg[8];
-#define PROBE_T(var) const long long var = clock64()
-#define PROBE_ADD(slot, a, b) do { if (blockIdx.x == 0) g_gemm_dbg[slot] += (unsigned long long)((b) - (a)); } while (0)
-#else
-#define PROBE_T(var)
-#define PROBE_ADD(slot, a, b)
-#endif
-
 struct Params {
   int64_t M, N, K, batch;
   int64_t c_rs, c_bs;
@@ -85,9 +75,6 @@ struct Params {
   int64_t num_tiles;
   unsigned int* status;
   int32_t fast_ok;  // pointers/pitches allow the branch-free vector epilogue on interior tiles
-#ifdef B200_GEMM_PROBE
-  int probe;  // timing probes of the epilogue stages (development builds only)
-#endif
 };
 
 __device__ __forceinline__ float act(float v, int32_t epilogue) {
@@ -245,9 +232,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-#ifdef B200_GEMM_PROBE
-    if (p.probe & 8) goto producer_done;  // no copies at all: the MMA thread does not wait for them
-#endif
     if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
@@ -258,11 +242,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tile_coords<kBand>(t, p, b, mt, nt);
         const int32_t m0 = mt * kTileM + (int32_t)rank * BM, n0 = nt * BN + (int32_t)rank * C_::B_ROWS * (PAIR ? 1 : 0);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
-#ifdef B200_GEMM_PROBE
-          if (p.probe & 64) {
-            if (!ptx::mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
-          } else
-#endif
           if (!ptx::mbar_wait_relaxed(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
           const int32_t k0 = (int32_t)(kb * BK);
           if (PAIR) {
@@ -291,9 +270,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-#ifdef B200_GEMM_PROBE
-  producer_done:;
-#endif
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     // The whole warp walks the loop converged (so that addresses and descriptors are warp-uniform
@@ -307,28 +283,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int64_t t = tile_first; t < p.num_tiles && ok; t += tile_step) {
-        PROBE_T(t0);
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, abort_flag))) break;
         ptx::tc_fence_after_sync();
-        PROBE_T(t1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
-#ifdef B200_GEMM_PROBE
-          if (p.probe & 32) __nanosleep(600);  // data surely landed: the wait below costs its floor
-#endif
-          PROBE_T(t2);
-#ifdef B200_GEMM_PROBE
-          if (!(p.probe & 8))
-#endif
           if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(s), phase, abort_flag))) { ok = false; break; }
           ptx::tc_fence_after_sync();
-          PROBE_T(t3);
           const uint32_t a_addr = a_base + s * A_STAGE_BYTES;
           const uint32_t b_addr = b_base + s * C_::B_STAGE_BYTES;
           if (ptx::elect_one()) {
-#ifdef B200_GEMM_PROBE
-            if (!(p.probe & 16)) {
-#endif
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t a_desc = ptx::smem_desc_sw128(a_addr + k * (UMMA_K * 2), 0, 1024);
@@ -338,10 +301,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               if (PAIR) ptx::mma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
               else ptx::mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
-#ifdef B200_GEMM_PROBE
-            }
-#endif
-            PROBE_T(t4);
             // frees the smem slot (in both CTAs when PAIR) when these MMAs have read it
             if (PAIR) {
               ptx::tc_commit_pair(ptx::mapa(empty_bar(s), 0));
@@ -358,12 +317,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 ptx::tc_commit(tmem_full_bar(acc));
               }
             }
-            PROBE_T(t5);
-            PROBE_ADD(1, t2, t3);
-            PROBE_ADD(2, t3, t4);
-            PROBE_ADD(3, t4, t5);
-            PROBE_ADD(4, 0, 1);
-            if (kb == 0) { PROBE_ADD(0, t0, t1); PROBE_ADD(5, 0, 1); }
           }
           __syncwarp();
           if (++s == kStages) { s = 0; phase ^= 1; }
@@ -433,9 +386,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int c = 0; c < kChunks; ++c) {
           const int col_in_tile = half * (BN / 2) + c * 32;
           if (n0 + col_in_tile >= p.N) break;  // uniform: chunk entirely past the last column
-#ifdef B200_GEMM_PROBE
-          if (p.probe & 1) break;
-#endif
           const int64_t col = n0 + col_in_tile + c4 * 4;
           float bias_cur[4];
 #pragma unroll
@@ -604,9 +554,6 @@ int32_t fill_params(const b200_gemm_args& g, Params& p, int tile_m, int tile_n, 
       ok = ok && g.residual_dtype == B200_F32 && aligned_to(g.residual, 16) && g.residual_row_stride % 4 == 0;
     p.fast_ok = ok ? 1 : 0;
   }
-#ifdef B200_GEMM_PROBE
-  p.probe = getenv("B200_GEMM_PROBE") ? atoi(getenv("B200_GEMM_PROBE")) : 0;
-#endif
   return B200_OK;
 }
 
@@ -644,9 +591,6 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
     int32_t st = fill_params(g, p, BM, BN, sizeof(Tout));
     if (st != B200_OK) return st;
   }
-#ifdef B200_GEMM_PROBE
-  p.probe = getenv("B200_GEMM_PROBE") ? atoi(getenv("B200_GEMM_PROBE")) : 0;
-#endif
 
   auto kernel = gemm_tcgen05_kernel<BN, B_MN_MAJOR, Tout>;
   static thread_local bool attr_set[64] = {false};
@@ -813,12 +757,3 @@ int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream) {
 
 }  // namespace b200
 
-#ifdef B200_GEMM_PROBE
-// development builds only: read and clear the MMA-thread cycle counters
-extern "C" B200_API int b200_probe_read(unsigned long long* host) {
-  int rc = (int)cudaMemcpyFromSymbol(host, b200::g_gemm_dbg, sizeof(unsigned long long) * 8);
-  unsigned long long zero[8] = {0};
-  cudaMemcpyToSymbol(b200::g_gemm_dbg, zero, sizeof(zero));
-  return rc;
-}
-#endif
