@@ -59,7 +59,7 @@ extern "C" {
 #define B200_ROUTE_AUTO 0
 #define B200_ROUTE_SIMT 1     /* generic strided CUDA-core kernel, any layout */
 #define B200_ROUTE_TCGEN05 2  /* TMA-fed tcgen05/TMEM tensor-core kernel */
-#define B200_ROUTE_SKINNY 3   /* small-M (decode) GEMM: weight-streaming, HBM bound */
+#define B200_ROUTE_SKINNY 3   /* decode shapes, HBM bound: split-K small-M GEMM; split-KV attention for <= 16 query rows */
 
 typedef void* b200_stream_t; /* cudaStream_t */
 
@@ -176,9 +176,14 @@ B200_API int32_t b200_gemm_small_m_static(const b200_gemm_args* args, b200_strea
  * O (same dtype as Q) and, when lse != NULL, the natural-log LSE as fp32 [batch, heads, q_len].
  * Strides are in elements for the (batch, head, position) dims; head_dim is contiguous.
  * The causal mask is top-left aligned.
+ * Routes: bf16 with head_dim 64 takes the tensor-core kernel; up to 16 query rows with
+ * head_dim 32/64/128 and at most 32768 keys take the split-KV decode kernel (a cluster of eight
+ * CTAs per row, merged through distributed shared memory); everything else the CUDA-core kernel.
  * Replaces: aten__scaled_dot_product_flash_attention
- * (torch_mojo_backend/aten_functions.py:539-677) and the FA4 bridge
- * (torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:20-61,480-498). */
+ * (torch_mojo_backend/aten_functions.py:539-677), the FA4 bridge
+ * (torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:20-61,480-498) and the single-query
+ * decode kernel (torch_mojo_backend/mojo_kernels/attention.mojo:27-191, gated at
+ * torch_mojo_backend/aten_functions.py:3053-3074). */
 typedef struct b200_sdpa_args {
   const void* q;
   const void* k;
@@ -193,7 +198,7 @@ typedef struct b200_sdpa_args {
   float scale;
   int32_t causal;
   int32_t dtype;
-  int32_t route; /* B200_ROUTE_AUTO / SIMT / TCGEN05 */
+  int32_t route; /* B200_ROUTE_AUTO / SIMT / TCGEN05 / SKINNY */
 } b200_sdpa_args;
 
 B200_API int32_t b200_sdpa_route(const b200_sdpa_args* args);

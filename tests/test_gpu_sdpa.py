@@ -93,6 +93,47 @@ def test_sdpa_route_selection(ops):
     assert route((2, 2, 128, 128), torch.bfloat16) == 1   # head_dim other than 64
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("head_dim", [32, 64, 128])
+@pytest.mark.parametrize("q_len,kv_len,causal", [(1, 1, False), (1, 7, False), (1, 1024, False), (1, 5000, False),
+                                                 (3, 333, False), (3, 333, True), (16, 9, True), (2, 32768, False)])
+def test_sdpa_decode_route(ops, dtype, head_dim, q_len, kv_len, causal):
+    """Few query rows against a KV cache: the split-KV cluster kernel, forced (route 3) so that a
+    silent reroute fails. Keys fewer than the eight CTAs of a cluster, a ragged last chunk, the
+    largest supported cache, and the top-left aligned causal mask."""
+    b, h = (1, 2) if kv_len > 8192 else (2, 3)
+    q = gen((b, h, q_len, head_dim), dtype, 60)
+    k = gen((b, h, kv_len, head_dim), dtype, 61)
+    v = gen((b, h, kv_len, head_dim), dtype, 62)
+    out, lse = ops.sdpa(q.cuda(), k.cuda(), v.cuda(), causal, None, 3)
+    want, want_lse = ref_ops.sdpa(q, k, v, causal)
+    assert out.dtype == dtype and out.shape == q.shape
+    assert_parity(out, want, bf16=dtype == torch.bfloat16)
+    assert_parity(lse, want_lse, bf16=False, scale=max(want_lse.abs().max().item(), 1.0) * (10 if dtype == torch.bfloat16 else 1))
+
+
+def test_sdpa_decode_route_strided_cache_view(ops):
+    """K and V as the first T positions of a longer preallocated cache [B, H, T_max, D] (strides
+    that are not the dense ones) and Q as a slice of a fused projection; AUTO picks the decode
+    kernel for one query row."""
+    import ctypes
+
+    from torch_mojo_backend import native
+
+    B, H, T, T_max, D = 2, 5, 300, 512, 64
+    cache_k, cache_v = gen((B, H, T_max, D), torch.bfloat16, 63), gen((B, H, T_max, D), torch.bfloat16, 64)
+    qkv = gen((B, 1, 3 * H * D), torch.bfloat16, 65)
+    q = qkv[..., : H * D].view(B, 1, H, D).transpose(1, 2)
+    kg, vg = cache_k.cuda()[:, :, :T], cache_v.cuda()[:, :, :T]
+    qg = qkv.cuda()[..., : H * D].view(B, 1, H, D).transpose(1, 2)
+    o = torch.empty((B, H, 1, D), dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty((B, H, 1), device="cuda")
+    args = ops.fill_sdpa_args(qg, kg, vg, o, lse, False, D**-0.5, 0)
+    assert native.lib().b200_sdpa_route(ctypes.byref(args)) == 3
+    out, _ = ops.sdpa(qg, kg, vg, False)
+    assert_parity(out, ref_ops.sdpa(q, cache_k[:, :, :T], cache_v[:, :, :T], False)[0], bf16=True)
+
+
 @pytest.mark.parametrize("shape", [(8, 12, 1024, 64), (4, 25, 2048, 64)])
 def test_sdpa_benchmark_shapes_bf16(ops, shape):
     """The two causal bf16 configurations; oracle = PyTorch CPU SDPA in fp32 on the bf16 values."""

@@ -80,7 +80,7 @@ def time_case(make_inputs, run, bytes_per_copy, iters, use_graph):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="gemm,gemm_fused,layer_norm,softmax,gelu,reduce,sdpa")
+    ap.add_argument("--ops", default="gemm,gemm_fused,layer_norm,softmax,gelu,reduce,sdpa,sdpa_decode")
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--only", default="", help="substring filter on the case name")
     ap.add_argument("--no-graph", action="store_true", help="plain launches (what an ncu capture wants)")
@@ -239,6 +239,20 @@ def main():
 
             us, rot = time_case(make, lambda t: ops.sdpa(t[0], t[1], t[2], True), nbytes, args.iters, use_graph)
             report(name, us, rot, flops, nbytes, "tensor")
+
+    if "sdpa_decode" in wanted:
+        # One new token against a KV cache: K and V are read once, so the bound is HBM.
+        for B, H, T, D in ((8, 25, 1024, 64), (64, 25, 1024, 64), (8, 25, 8192, 64), (32, 32, 4096, 128)):
+            name = f"sdpa_decode bf16 {B}x{H}x1x{T}x{D}"
+            if not keep(name):
+                continue
+            nbytes = 2 * B * H * T * D * 2 + 2 * B * H * D * 2
+
+            def make(i, B=B, H=H, T=T, D=D):
+                return (randn((B, H, 1, D), torch.bfloat16), randn((B, H, T, D), torch.bfloat16), randn((B, H, T, D), torch.bfloat16))
+
+            us, rot = time_case(make, lambda t: ops.sdpa(t[0], t[1], t[2], False), nbytes, args.iters, use_graph)
+            report(name, us, rot, nbytes=nbytes)
 
     status = native.device_status()
     if status != 0:

@@ -12,4 +12,8 @@ int32_t launch_sdpa_simt(const b200_sdpa_args& a, cudaStream_t stream);
 const char* sdpa_tcgen05_ineligible(const b200_sdpa_args& a);
 int32_t launch_sdpa_tcgen05(const b200_sdpa_args& a, cudaStream_t stream);
 
+// Few query rows against many keys (decode): split-KV over a thread-block cluster.
+const char* sdpa_decode_ineligible(const b200_sdpa_args& a);
+int32_t launch_sdpa_decode(const b200_sdpa_args& a, cudaStream_t stream);
+
 }  // namespace b200
