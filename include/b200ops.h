@@ -96,6 +96,20 @@ B200_API int32_t b200_softmax_lastdim(const void* x, void* y, int64_t rows, int6
                              int64_t x_row_stride, float scale, int32_t causal, int64_t q_len,
                              int32_t in_dtype, int32_t out_dtype, b200_stream_t stream);
 
+/* Row softmax of where(masked, fill, x * scale): the chain mul(scale) -> masked_fill(mask, fill)
+ * -> _softmax of a decomposed attention in one pass over the scores. mask is bytes (torch.bool)
+ * [mask_rows, cols] with row stride mask_row_stride; row r of x uses mask row r % mask_rows (a
+ * [T, S] mask broadcast over batch and heads), and an element is masked where
+ * (mask byte != 0) != (mask_invert != 0), so both masked_fill(mask, fill) and
+ * where(keep, x, fill) map onto it. A row whose elements are all masked to -inf gives NaN, as torch.
+ * Replaces: aten_masked_fill + aten__softmax (torch_mojo_backend/aten_functions.py:3965, 680-714)
+ * with the fused contract of SoftmaxRows (torch_mojo_backend/eager_kernels/nn_ops.mojo:392-409),
+ * generalised from its causal flag to an explicit mask. */
+B200_API int32_t b200_softmax_masked(const void* x, const uint8_t* mask, void* y, int64_t rows,
+                            int64_t cols, int64_t x_row_stride, int64_t mask_rows,
+                            int64_t mask_row_stride, int32_t mask_invert, float fill, float scale,
+                            int32_t in_dtype, int32_t out_dtype, b200_stream_t stream);
+
 /* Elementwise GELU over numel contiguous elements; approximate_tanh selects the tanh form.
  * Replaces: aten_gelu (torch_mojo_backend/aten_functions.py:2062-2067) and
  * _gelu_forward_bf16_{exact,tanh}

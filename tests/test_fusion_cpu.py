@@ -48,6 +48,18 @@ class _StandIns:
         return torch.softmax(x.float() * scale, -1).to(out_dtype or x.dtype)
 
     @staticmethod
+    def mask_rows_of(x, mask):
+        from torch_mojo_backend import ops
+
+        return ops.mask_rows_of(x, mask)
+
+    @staticmethod
+    def softmax_masked(x, mask, fill, scale=1.0, invert=False, out_dtype=None):
+        _StandIns._record(x, ("softmax_masked", fill, scale, invert))
+        masked = mask != invert
+        return torch.softmax(torch.where(masked, torch.tensor(fill), x.float() * scale), -1).to(out_dtype or x.dtype)
+
+    @staticmethod
     def gelu(x, approximate="none"):
         return F.gelu(x, approximate=approximate)
 
@@ -160,3 +172,48 @@ def test_attention_output_copy_is_dropped_only_for_fresh_outputs():
     assert af.contiguous_or_alias(x).is_contiguous()
     xc = x.contiguous()
     assert af.contiguous_or_alias(xc) is xc
+
+
+def test_masked_softmax_chain_is_folded(stand_ins):
+    """scale -> masked_fill -> softmax (GPT-2 demo form) and div -> where -> softmax (HF form)
+    each become one masked softmax; the fused node gets the unscaled scores, the mask as it is
+    and the scale / fill / polarity of the chain."""
+    T = 12
+    tril = torch.tril(torch.ones(T, T)).view(1, 1, T, T)
+
+    def demo_form(att, bias):
+        att = att * 0.25
+        att = att.masked_fill(bias[:, :, :T, :T] == 0, float("-inf"))
+        return torch.softmax(att, dim=-1)
+
+    def hf_form(att, keep):
+        att = att / 4.0
+        att = torch.where(keep, att, torch.full([], -1e9))
+        return torch.nn.functional.softmax(att, dim=-1)
+
+    g = torch.Generator().manual_seed(0)
+    att = torch.randn(2, 3, T, T, generator=g)
+    for fn, second, entry in ((demo_form, tril, ("softmax_masked", float("-inf"), 0.25, False)),
+                              (hf_form, tril.bool(), ("softmax_masked", -1e9, 0.25, True))):
+        torch._dynamo.reset()
+        stand_ins.calls.clear()
+        with torch.no_grad():
+            got = torch.compile(fn, backend=mojo_backend)(att, second)
+        torch.testing.assert_close(got, fn(att, second))
+        assert stand_ins.calls == [entry]
+
+
+def test_masked_softmax_is_left_alone_when_the_mask_varies_over_heads(stand_ins):
+    """A mask with a real head dimension is not one [T, S] matrix: the chain stays unfused."""
+    g = torch.Generator().manual_seed(1)
+    att = torch.randn(2, 3, 8, 8, generator=g)
+    mask = torch.rand(1, 3, 8, 8, generator=g) > 0.5
+    mask[..., 0] = False
+
+    def fn(att, mask):
+        return torch.softmax(att.masked_fill(mask, float("-inf")), dim=-1)
+
+    with torch.no_grad():
+        got = torch.compile(fn, backend=mojo_backend)(att, mask)
+    torch.testing.assert_close(got, fn(att, mask))
+    assert not [c for c in stand_ins.calls if c[0] == "softmax_masked"]

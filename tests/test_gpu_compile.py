@@ -72,6 +72,28 @@ def test_sdpa_is_causal_reaches_the_kernel(tmb, dtype):
     assert_parity(got, want, bf16=dtype == torch.bfloat16)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_step_with_kv_cache(tmb, dtype):
+    """One decode step as a serving loop runs it: the new token's K/V are appended to the cache
+    (aten.cat), one query row attends to the whole cache, then the output projection (a small-M
+    GEMM). The attention has one query row, so the lowering must reach the split-KV kernel."""
+    B, H, T, D = 2, 4, 300, 64
+
+    def fn(q, k_new, v_new, k_cache, v_cache, w):
+        k = torch.cat([k_cache, k_new], dim=2)
+        v = torch.cat([v_cache, v_new], dim=2)
+        y = F.scaled_dot_product_attention(q, k, v)
+        return y.transpose(1, 2).reshape(B, 1, H * D) @ w
+
+    g = torch.Generator().manual_seed(3)
+    rnd = lambda *s: torch.randn(s, generator=g).to(dtype)
+    q, k_new, v_new = rnd(B, H, 1, D), rnd(B, H, 1, D), rnd(B, H, 1, D)
+    k_cache, v_cache, w = rnd(B, H, T, D), rnd(B, H, T, D), rnd(H * D, H * D) * 0.05
+    got = run_compiled(tmb, fn, q, k_new, v_new, k_cache, v_cache, w)
+    want = fn(*(t.float() for t in (q, k_new, v_new, k_cache, v_cache, w)))
+    assert_parity(got, want, bf16=dtype == torch.bfloat16)
+
+
 @pytest.mark.parametrize("attention", ["sdpa", "masked_softmax"])
 def test_gpt2_tiny_golden(tmb, golden, attention):
     from demo_scripts.gpt2 import GPT2, GPTConfig

@@ -119,6 +119,39 @@ def test_softmax_fused_scale_causal(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cols,offset", [(64, 0), (200, 0), (77, 0), (128, 3)])
+def test_softmax_masked(ops, dtype, cols, offset):
+    """scale -> masked_fill -> softmax in one kernel: a [T, S] mask shared by batch and heads, read
+    as a strided slice of a larger buffer (with an odd byte offset it takes the scalar kernel),
+    both polarities, -inf and finite fills; oracle = the unfused chain in fp64."""
+    B, H, T = 2, 3, 40
+    x = gen((B, H, T, cols), dtype, 17, std=2.0)
+    g = torch.Generator().manual_seed(18)
+    buf = torch.rand(1, 1, 64, 256, generator=g) > 0.4
+    buf[..., offset] = False  # at least one visible key per row
+    mask = buf[:, :, :T, offset : offset + cols]
+    for fill in (float("-inf"), -3.0):
+        want = torch.softmax((x.double() * 0.3).masked_fill(mask, fill), -1).to(dtype)
+        y = ops.softmax_masked(x.cuda(), buf.cuda()[:, :, :T, offset : offset + cols], fill, 0.3, False)
+        assert y.dtype == dtype
+        assert_parity(y, want, bf16=dtype == torch.bfloat16, scale=1.0)
+        if fill == float("-inf"):
+            assert (y.cpu().float().masked_select(mask.expand_as(x)) == 0).all()
+        keep = ~mask
+        y2 = ops.softmax_masked(x.cuda(), keep.contiguous().cuda(), fill, 0.3, True)
+        # (the dense `keep` may take the vector kernel where the offset slice took the scalar one)
+        assert_parity(y2, want, bf16=dtype == torch.bfloat16, scale=1.0)
+        if offset == 0:
+            assert torch.equal(y2, y), "where(keep, x, fill) form must agree with masked_fill(mask, fill)"
+    # row-broadcast mask [S] and the rejection of a mask that varies over heads
+    m1 = buf[0, 0, 0, :cols]
+    y3 = ops.softmax_masked(x.cuda(), m1.cuda(), float("-inf"), 1.0, False)
+    assert_parity(y3, torch.softmax(x.double().masked_fill(m1, float("-inf")), -1).to(dtype), bf16=dtype == torch.bfloat16, scale=1.0)
+    with pytest.raises(ValueError, match="not one"):
+        ops.softmax_masked(x.cuda(), mask.expand(1, H, T, cols).contiguous().cuda(), 0.0, 1.0, False)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_softmax_full_size_properties(ops, dtype):
     """Scores of 8 batch x 12 heads x 1024 x 1024 with the strict upper triangle at -inf: rows sum
     to one, masked entries are exact zeros, and a slice matches the oracle."""

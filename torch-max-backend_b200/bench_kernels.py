@@ -201,6 +201,15 @@ def main():
                 # masked columns are never read: algorithmic bytes = half the reads + all the writes
                 report(name, us, rot, nbytes=0.75 * nbytes)
 
+            name = f"softmax {dname} 96x1024x1024 fused scale+explicit mask"
+            if keep(name):
+                make = lambda i, dtype=dtype: (randn(shape, dtype),)
+                blocked = ~mask
+                us, rot = time_case(make, lambda t: ops.softmax_masked(t[0], blocked, float("-inf"), 0.125, False),
+                                    nbytes + 1024 * 1024, args.iters, use_graph)
+                # every score is read (the mask's values are not known to be triangular) + the 1 MB mask
+                report(name, us, rot, nbytes=nbytes + 1024 * 1024)
+
     if "gelu" in wanted:
         for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
             for approx in ("tanh", "none"):

@@ -242,6 +242,16 @@ int32_t launch_layer_norm(const void* x, const void* gamma, const void* beta, vo
 // Softmax over the last dim
 // =========================================================================================
 
+// Optional element mask of the fused scale + masked_fill + softmax form: row r of x uses mask row
+// r % rows (a [T, S] mask broadcast over batch and heads); an element is replaced by `fill`
+// where (mask byte != 0) != invert. ptr == nullptr: no mask.
+struct RowMask {
+  const uint8_t* ptr;
+  int64_t rows, stride;
+  int invert;
+  float fill;
+};
+
 template <bool kAccurate>
 __device__ __forceinline__ float exp_sel(float x) {
   return kAccurate ? expf(x) : __expf(x);
@@ -250,7 +260,7 @@ __device__ __forceinline__ float exp_sel(float x) {
 template <typename Tin, typename Tout, int N, int MAXC>
 __global__ void __launch_bounds__(kRowThreads)
 softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t rows, int cols,
-                    int64_t x_row_stride, float scale, int causal, int64_t q_len) {
+                    int64_t x_row_stride, float scale, int causal, int64_t q_len, RowMask mask) {
   constexpr bool kAccurate = sizeof(Tout) == 4;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
@@ -262,6 +272,7 @@ softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t row
     allowed = a < cols ? (int)a : cols;
   }
   const Tin* xr = x + row * x_row_stride;
+  const uint8_t* mr = mask.ptr != nullptr ? mask.ptr + (row % mask.rows) * mask.stride : nullptr;
 
   float v[MAXC][N];
   float m = -INFINITY;
@@ -271,9 +282,15 @@ softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t row
     // Chunks entirely past the causal limit are never read.
     if (c < nchunks && c * N < allowed) {
       Chunk<Tin, N>::load(xr + c * N, v[i]);
+      // N mask bytes of this chunk (the launcher guarantees N-byte alignment of every chunk)
+      uint64_t mbits = 0;
+      if (mr != nullptr)
+        mbits = N == 8 ? *reinterpret_cast<const uint64_t*>(mr + c * N)
+                       : (uint64_t) * reinterpret_cast<const uint32_t*>(mr + c * N);
 #pragma unroll
       for (int j = 0; j < N; ++j) {
         v[i][j] = (c * N + j < allowed) ? v[i][j] * scale : -INFINITY;
+        if (mr != nullptr && (((mbits >> (8 * j)) & 0xffu) != 0) != (mask.invert != 0)) v[i][j] = mask.fill;
         m = nan_max(m, v[i][j]);
       }
     } else {
@@ -310,7 +327,7 @@ softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t row
 template <typename Tin, typename Tout>
 __global__ void softmax_block_kernel(const Tin* __restrict__ x, Tout* __restrict__ y,
                                      int64_t cols, int64_t x_row_stride, float scale, int causal,
-                                     int64_t q_len) {
+                                     int64_t q_len, RowMask mask) {
   __shared__ float red[32];
   const int64_t row = blockIdx.x;
   int64_t allowed = cols;
@@ -319,38 +336,42 @@ __global__ void softmax_block_kernel(const Tin* __restrict__ x, Tout* __restrict
     allowed = a < cols ? a : cols;
   }
   const Tin* xr = x + row * x_row_stride;
+  const uint8_t* mr = mask.ptr != nullptr ? mask.ptr + (row % mask.rows) * mask.stride : nullptr;
+  auto value = [&](int64_t j) {
+    if (mr != nullptr && (mr[j] != 0) != (mask.invert != 0)) return mask.fill;
+    return Elem<Tin>::to_f32(xr[j]) * scale;
+  };
   float m = -INFINITY;
-  for (int64_t j = threadIdx.x; j < allowed; j += blockDim.x)
-    m = nan_max(m, Elem<Tin>::to_f32(xr[j]) * scale);
+  for (int64_t j = threadIdx.x; j < allowed; j += blockDim.x) m = nan_max(m, value(j));
   m = block_max(m, red);
   float s = 0.0f;
-  for (int64_t j = threadIdx.x; j < allowed; j += blockDim.x)
-    s += expf(Elem<Tin>::to_f32(xr[j]) * scale - m);
+  for (int64_t j = threadIdx.x; j < allowed; j += blockDim.x) s += expf(value(j) - m);
   s = block_sum(s, red);
   const float inv = 1.0f / s;
   Tout* yr = y + row * cols;
   for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
-    const float o = j < allowed ? expf(Elem<Tin>::to_f32(xr[j]) * scale - m) * inv : 0.0f;
+    const float o = j < allowed ? expf(value(j) - m) * inv : 0.0f;
     yr[j] = Elem<Tout>::from_f32(o);
   }
 }
 
 template <typename Tin, typename Tout>
 int32_t launch_softmax(const void* x, void* y, int64_t rows, int64_t cols, int64_t x_row_stride,
-                       float scale, int causal, int64_t q_len, cudaStream_t stream) {
+                       float scale, int causal, int64_t q_len, RowMask mask, cudaStream_t stream) {
   constexpr int N = Elem<Tin>::kVec;
   const Tin* xp = static_cast<const Tin*>(x);
   Tout* yp = static_cast<Tout*>(y);
   const size_t out_align = N * sizeof(Tout) > 16 ? 16 : N * sizeof(Tout);
   const bool vec_ok = cols % N == 0 && x_row_stride % N == 0 && aligned_to(x, 16) &&
                       aligned_to(y, out_align) && cols <= 32 * N * 8 &&
-                      rows <= (int64_t)INT32_MAX * kWarpsPerCta;
+                      rows <= (int64_t)INT32_MAX * kWarpsPerCta &&
+                      (mask.ptr == nullptr || (aligned_to(mask.ptr, N) && mask.stride % N == 0));
   if (vec_ok) {
     const int per_lane = (int)((cols / N + 31) / 32);
     const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
 #define SM_LAUNCH(MAXC)                                                              \
   softmax_warp_kernel<Tin, Tout, N, MAXC><<<grid, kRowThreads, 0, stream>>>(           \
-      xp, yp, rows, (int)cols, x_row_stride, scale, causal, q_len)
+      xp, yp, rows, (int)cols, x_row_stride, scale, causal, q_len, mask)
     if (per_lane <= 1) SM_LAUNCH(1);
     else if (per_lane <= 2) SM_LAUNCH(2);
     else if (per_lane <= 4) SM_LAUNCH(4);
@@ -360,7 +381,7 @@ int32_t launch_softmax(const void* x, void* y, int64_t rows, int64_t cols, int64
     B200_REQUIRE(rows <= INT32_MAX, B200_ERR_UNSUPPORTED, "softmax: too many rows");
     const int threads = cols >= 2048 ? 1024 : (cols >= 512 ? 256 : 128);
     softmax_block_kernel<Tin, Tout><<<(unsigned)rows, threads, 0, stream>>>(
-        xp, yp, cols, x_row_stride, scale, causal, q_len);
+        xp, yp, cols, x_row_stride, scale, causal, q_len, mask);
   }
   B200_CHECK_LAUNCH("softmax_lastdim");
   return B200_OK;
@@ -572,11 +593,11 @@ extern "C" B200_API int32_t b200_layer_norm(const void* x, const void* gamma, co
 #undef LN_CASE
 }
 
-extern "C" B200_API int32_t b200_softmax_lastdim(const void* x, void* y, int64_t rows, int64_t cols,
-                                        int64_t x_row_stride, float scale, int32_t causal,
-                                        int64_t q_len, int32_t in_dtype, int32_t out_dtype,
-                                        b200_stream_t stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+namespace {
+int32_t softmax_entry(const void* x, void* y, int64_t rows, int64_t cols, int64_t x_row_stride, float scale,
+                      int32_t causal, int64_t q_len, b200::RowMask mask, int32_t in_dtype, int32_t out_dtype,
+                      cudaStream_t stream) {
+  using namespace b200;
   B200_REQUIRE(rows >= 0 && cols >= 0, B200_ERR_INVALID_ARG, "softmax: negative size");
   B200_REQUIRE(valid_dtype(in_dtype) && valid_dtype(out_dtype), B200_ERR_INVALID_ARG,
                "softmax: bad dtype enum");
@@ -588,10 +609,36 @@ extern "C" B200_API int32_t b200_softmax_lastdim(const void* x, void* y, int64_t
   B200_REQUIRE(x_row_stride >= cols || rows == 1, B200_ERR_INVALID_ARG,
                "softmax: row stride smaller than cols");
   if (in_dtype == B200_F32)
-    return launch_softmax<float, float>(x, y, rows, cols, x_row_stride, scale, causal, q_len, stream);
+    return launch_softmax<float, float>(x, y, rows, cols, x_row_stride, scale, causal, q_len, mask, stream);
   if (out_dtype == B200_F32)
-    return launch_softmax<bf16, float>(x, y, rows, cols, x_row_stride, scale, causal, q_len, stream);
-  return launch_softmax<bf16, bf16>(x, y, rows, cols, x_row_stride, scale, causal, q_len, stream);
+    return launch_softmax<bf16, float>(x, y, rows, cols, x_row_stride, scale, causal, q_len, mask, stream);
+  return launch_softmax<bf16, bf16>(x, y, rows, cols, x_row_stride, scale, causal, q_len, mask, stream);
+}
+}  // namespace
+
+extern "C" B200_API int32_t b200_softmax_lastdim(const void* x, void* y, int64_t rows, int64_t cols,
+                                        int64_t x_row_stride, float scale, int32_t causal,
+                                        int64_t q_len, int32_t in_dtype, int32_t out_dtype,
+                                        b200_stream_t stream_) {
+  const b200::RowMask none = {nullptr, 1, 0, 0, 0.0f};
+  return softmax_entry(x, y, rows, cols, x_row_stride, scale, causal, q_len, none, in_dtype, out_dtype,
+                       static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" B200_API int32_t b200_softmax_masked(const void* x, const uint8_t* mask, void* y, int64_t rows,
+                                       int64_t cols, int64_t x_row_stride, int64_t mask_rows,
+                                       int64_t mask_row_stride, int32_t mask_invert, float fill,
+                                       float scale, int32_t in_dtype, int32_t out_dtype,
+                                       b200_stream_t stream_) {
+  B200_REQUIRE(rows == 0 || cols == 0 || mask != nullptr, B200_ERR_INVALID_ARG, "softmax_masked: null mask");
+  B200_REQUIRE(mask_rows > 0 && (mask_row_stride >= cols || mask_rows == 1), B200_ERR_INVALID_ARG,
+               "softmax_masked: mask needs at least one row and a row stride of at least cols");
+  B200_REQUIRE(rows % mask_rows == 0, B200_ERR_INVALID_ARG,
+               "softmax_masked: rows (%lld) is not a multiple of mask_rows (%lld)", (long long)rows,
+               (long long)mask_rows);
+  const b200::RowMask m = {mask, mask_rows, mask_row_stride, mask_invert != 0 ? 1 : 0, fill};
+  return softmax_entry(x, y, rows, cols, x_row_stride, scale, 0, 0, m, in_dtype, out_dtype,
+                       static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" B200_API int32_t b200_gelu(const void* x, void* y, int64_t numel, int32_t approximate_tanh,

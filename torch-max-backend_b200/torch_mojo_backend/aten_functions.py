@@ -464,7 +464,19 @@ def contiguous_or_alias(x):
     return x if x.is_contiguous() else x.contiguous()
 
 
-for _fused in (fused_layer_norm, fused_gemm, contiguous_or_alias):
+@_count_calls
+def fused_masked_softmax(x, mask, *, fill, scale, invert):
+    """`_softmax(masked_fill(x * scale, mask, fill), -1)` (invert=False) or
+    `_softmax(where(mask, x * scale, fill), -1)` (invert=True) in one pass over the scores. A mask
+    whose run-time layout is not one [T, S] matrix shared by all leading indices is applied with
+    torch glue first and only the softmax runs in the kernel."""
+    if ops.mask_rows_of(x, mask) is not None:
+        return ops.softmax_masked(x, mask, fill, scale, invert)
+    masked = torch.where(mask if invert else ~mask, x * scale, fill)
+    return ops.softmax(masked)
+
+
+for _fused in (fused_layer_norm, fused_gemm, contiguous_or_alias, fused_masked_softmax):
     MAPPING_TORCH_ATEN_TO_MOJO[_fused] = _fused
 
 

@@ -50,6 +50,7 @@ EXPORTED_SYMBOLS = (
     "b200_device_status",
     "b200_layer_norm",
     "b200_softmax_lastdim",
+    "b200_softmax_masked",
     "b200_gelu",
     "b200_reduce_lastdim",
     "b200_gemm_route",
@@ -184,6 +185,8 @@ def _declare(dll: ctypes.CDLL) -> None:
     dll.b200_layer_norm.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, f32, i32, i32, i32, vp]
     dll.b200_softmax_lastdim.restype = i32
     dll.b200_softmax_lastdim.argtypes = [vp, vp, i64, i64, i64, f32, i32, i64, i32, i32, vp]
+    dll.b200_softmax_masked.restype = i32
+    dll.b200_softmax_masked.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i32, f32, f32, i32, i32, vp]
     dll.b200_gelu.restype = i32
     dll.b200_gelu.argtypes = [vp, vp, i64, i32, i32, vp]
     dll.b200_reduce_lastdim.restype = i32

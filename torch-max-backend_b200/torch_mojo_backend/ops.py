@@ -29,6 +29,10 @@ _lib.define(
 _lib.define(
     "softmax(Tensor x, float scale=1.0, bool causal=False, int q_len=0, ScalarType? out_dtype=None) -> Tensor"
 )
+_lib.define(
+    "softmax_masked(Tensor x, Tensor mask, float fill, float scale=1.0, bool invert=False,"
+    " ScalarType? out_dtype=None) -> Tensor"
+)
 _lib.define("gelu(Tensor x, str approximate='none') -> Tensor")
 _lib.define("reduce(Tensor x, int op, ScalarType? out_dtype=None) -> Tensor")
 _lib.define(
@@ -130,6 +134,52 @@ def _softmax_cuda(x, scale=1.0, causal=False, q_len=0, out_dtype=None):
 
 
 def _softmax_meta(x, scale=1.0, causal=False, q_len=0, out_dtype=None):
+    return torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+
+
+def mask_rows_of(x: torch.Tensor, mask: torch.Tensor):
+    """(mask_rows, mask_row_stride) when `mask` (bool) broadcasts against `x` as one [T, S] matrix
+    shared by every leading index of x — the layout the fused kernel reads — else None."""
+    if mask.dtype != torch.bool or mask.dim() < 1 or mask.dim() > x.dim() or x.dim() < 1:
+        return None
+    shape = (1,) * (x.dim() - mask.dim()) + tuple(mask.shape)
+    strides = (0,) * (x.dim() - mask.dim()) + tuple(mask.stride())
+    if shape[-1] != x.shape[-1] or (shape[-1] > 1 and strides[-1] != 1):
+        return None
+    if any(d != 1 for d in shape[:-2]):
+        return None
+    if x.dim() == 1 or shape[-2] == 1:
+        return 1, max(int(x.shape[-1]), 1)
+    if shape[-2] != x.shape[-2]:
+        return None
+    return int(shape[-2]), int(strides[-2])
+
+
+def _softmax_masked_cuda(x, mask, fill, scale=1.0, invert=False, out_dtype=None):
+    device = native.require_cuda("softmax_masked", x, mask)
+    out_dtype = out_dtype or x.dtype
+    layout = mask_rows_of(x, mask)
+    if layout is None:
+        raise ValueError(
+            f"softmax_masked: mask of shape {tuple(mask.shape)} and strides {mask.stride()} is not one [T, S] "
+            f"matrix broadcast over the leading dims of x {tuple(x.shape)}"
+        )
+    mask_rows, mask_stride = layout
+    xr, rows, cols, row_stride = _as_rows(x)
+    y = torch.empty(x.shape, dtype=out_dtype, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_softmax_masked(
+            xr.data_ptr(), mask.data_ptr(), y.data_ptr(), rows, cols, row_stride, mask_rows, mask_stride,
+            int(invert), fill, scale, native.dtype_enum(x.dtype), native.dtype_enum(out_dtype),
+            native.current_stream(device),
+        )
+    native.check("softmax_masked", status)
+    _launched(device, start, "softmax", 0.0, _nbytes(xr, y))
+    return y
+
+
+def _softmax_masked_meta(x, mask, fill, scale=1.0, invert=False, out_dtype=None):
     return torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
 
 
@@ -359,6 +409,7 @@ def _refuse_cpu(name):
 for _name, _cuda, _meta in (
     ("layer_norm", _layer_norm_cuda, _layer_norm_meta),
     ("softmax", _softmax_cuda, _softmax_meta),
+    ("softmax_masked", _softmax_masked_cuda, _softmax_masked_meta),
     ("gelu", _gelu_cuda, _gelu_meta),
     ("reduce", _reduce_cuda, _reduce_meta),
     ("gemm", _gemm_cuda, _gemm_meta),
@@ -370,6 +421,7 @@ for _name, _cuda, _meta in (
 
 layer_norm = torch.ops.b200.layer_norm
 softmax = torch.ops.b200.softmax
+softmax_masked = torch.ops.b200.softmax_masked
 gelu = torch.ops.b200.gelu
 reduce = torch.ops.b200.reduce
 gemm = torch.ops.b200.gemm

@@ -12,6 +12,10 @@ epilogues:
            bf16 rounding the unfused graph would do)
   * `sdpa -> getitem[0] -> transpose -> clone(contiguous)`        => no copy: the attention kernel
         already writes its output in the [B, T, H, D] order that `clone` would produce
+  * `[mul | div (scalar)] -> masked_fill(mask, value) | where(keep, ., value) -> _softmax(-1)`
+        => one masked softmax over the scores of a decomposed attention (the reference's fused
+           contract is SoftmaxRows(scale, causal, q_len), eager_kernels/nn_ops.mojo:392-409; the
+           mask here is explicit, so nothing is assumed about its values)
 
 Every intermediate node of a chain must have exactly one user; chains with symbolic shapes are
 left alone. Fused nodes call functions registered in MAPPING_TORCH_ATEN_TO_MOJO under themselves,
@@ -198,6 +202,65 @@ def _drop_attention_output_copies(graph) -> int:
     return count
 
 
+def _constant_fill(node):
+    """Python float of a `where` fill operand built in the graph as a constant, else None."""
+    if isinstance(node, (int, float)):
+        return float(node)
+    if _is_call(node, aten.scalar_tensor.default) and isinstance(node.args[0], (int, float)):
+        return float(node.args[0])
+    if _is_call(node, aten.full.default) and list(node.args[0]) == [] and isinstance(node.args[1], (int, float)):
+        return float(node.args[1])
+    return None
+
+
+def _fuse_masked_softmax(graph) -> int:
+    from torch_mojo_backend import ops
+
+    count = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten._softmax.default) or not _static_tensor(node):
+            continue
+        src, dim, half_to_float = node.args[:3]
+        v = _val(node)
+        if half_to_float or dim not in (-1, v.dim() - 1) or not native.supported_dtype(v.dtype):
+            continue
+        if not isinstance(src, torch.fx.Node) or len(src.users) != 1:
+            continue
+        if _is_call(src, aten.masked_fill.Scalar):
+            x, mask, fill = src.args
+            invert = False
+        elif _is_call(src, aten.where.self):
+            mask, x, fill = src.args
+            fill = _constant_fill(fill)
+            invert = True
+        else:
+            continue
+        if not isinstance(fill, (int, float)) or not isinstance(x, torch.fx.Node):
+            continue
+        vx, vm = _val(x), _val(mask)
+        if not (isinstance(vx, torch.Tensor) and isinstance(vm, torch.Tensor) and vx.dtype == v.dtype):
+            continue
+        if tuple(vx.shape) != tuple(v.shape) or ops.mask_rows_of(vx, vm) is None:
+            continue
+        scale = 1.0
+        if len(x.users) == 1 and _is_call(x, aten.mul.Tensor, aten.div.Tensor) and _static_tensor(x):
+            inner, factor = x.args
+            vi = _val(inner)
+            if (
+                isinstance(factor, (int, float))
+                and isinstance(vi, torch.Tensor)
+                and vi.dtype == vx.dtype
+                and tuple(vi.shape) == tuple(vx.shape)
+                and (x.target is aten.mul.Tensor or factor != 0)
+            ):
+                scale = float(factor) if x.target is aten.mul.Tensor else 1.0 / float(factor)
+                x = inner
+        _replace(graph, node, af.fused_masked_softmax, (x, mask),
+                 {"fill": float(fill), "scale": scale, "invert": invert})
+        count += 1
+    return count
+
+
 def fuse_graph(gm: torch.fx.GraphModule) -> dict[str, int]:
     """Rewrites gm.graph in place and returns how many chains of each kind were folded."""
     graph = gm.graph
@@ -205,6 +268,7 @@ def fuse_graph(gm: torch.fx.GraphModule) -> dict[str, int]:
         "layer_norm_cast": _fuse_layer_norm(graph),
         "gemm_epilogue": _fuse_gemm_epilogues(graph),
         "attention_output_copy": _drop_attention_output_copies(graph),
+        "masked_softmax": _fuse_masked_softmax(graph),
     }
     if any(stats.values()):
         graph.eliminate_dead_code()
