@@ -144,7 +144,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // max that propagates NaN like torch.amax / softmax do.
 __device__ __forceinline__ float nan_max(float a, float b) {
-  return (a != a) ? a : ((b != b) ? b : fmaxf(a, b));
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));  // one instruction; NaN if either is
+  return r;
 }
 
 __device__ __forceinline__ float warp_max(float v) {

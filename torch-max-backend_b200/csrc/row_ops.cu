@@ -252,16 +252,16 @@ struct RowMask {
   float fill;
 };
 
-template <bool kAccurate>
-__device__ __forceinline__ float exp_sel(float x) {
-  return kAccurate ? expf(x) : __expf(x);
-}
-
+// One warp per row, the row in registers. Values are moved to the base-2 exponent domain when
+// they are loaded (x * scale * log2(e)), so each element costs one subtract and one ex2 between
+// the two reductions; masking is decided per 16-byte chunk and only chunks that straddle the
+// causal limit (or rows that carry an explicit mask) look at single elements. A masked element is
+// -inf, which the exponential turns into an exact 0; a row with nothing visible gives NaN like
+// torch.
 template <typename Tin, typename Tout, int N, int MAXC>
 __global__ void __launch_bounds__(kRowThreads)
 softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t rows, int cols,
                     int64_t x_row_stride, float scale, int causal, int64_t q_len, RowMask mask) {
-  constexpr bool kAccurate = sizeof(Tout) == 4;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -273,6 +273,9 @@ softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t row
   }
   const Tin* xr = x + row * x_row_stride;
   const uint8_t* mr = mask.ptr != nullptr ? mask.ptr + (row % mask.rows) * mask.stride : nullptr;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float sl = scale * kLog2e;
+  const float fill2 = mask.fill * kLog2e;
 
   float v[MAXC][N];
   float m = -INFINITY;
@@ -282,17 +285,23 @@ softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t row
     // Chunks entirely past the causal limit are never read.
     if (c < nchunks && c * N < allowed) {
       Chunk<Tin, N>::load(xr + c * N, v[i]);
-      // N mask bytes of this chunk (the launcher guarantees N-byte alignment of every chunk)
-      uint64_t mbits = 0;
-      if (mr != nullptr)
-        mbits = N == 8 ? *reinterpret_cast<const uint64_t*>(mr + c * N)
-                       : (uint64_t) * reinterpret_cast<const uint32_t*>(mr + c * N);
 #pragma unroll
-      for (int j = 0; j < N; ++j) {
-        v[i][j] = (c * N + j < allowed) ? v[i][j] * scale : -INFINITY;
-        if (mr != nullptr && (((mbits >> (8 * j)) & 0xffu) != 0) != (mask.invert != 0)) v[i][j] = mask.fill;
-        m = nan_max(m, v[i][j]);
+      for (int j = 0; j < N; ++j) v[i][j] *= sl;
+      if (c * N + N > allowed) {  // the chunk that straddles the limit
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          if (c * N + j >= allowed) v[i][j] = -INFINITY;
       }
+      if (mr != nullptr) {
+        // N mask bytes of this chunk (the launcher guarantees N-byte alignment of every chunk)
+        const uint64_t mbits = N == 8 ? *reinterpret_cast<const uint64_t*>(mr + c * N)
+                                      : (uint64_t) * reinterpret_cast<const uint32_t*>(mr + c * N);
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          if ((((mbits >> (8 * j)) & 0xffu) != 0) != (mask.invert != 0)) v[i][j] = fill2;
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) m = nan_max(m, v[i][j]);
     } else {
 #pragma unroll
       for (int j = 0; j < N; ++j) v[i][j] = -INFINITY;
@@ -304,9 +313,10 @@ softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t row
   for (int i = 0; i < MAXC; ++i) {
 #pragma unroll
     for (int j = 0; j < N; ++j) {
-      // masked lanes hold -inf: exp gives exactly 0 unless the whole row is -inf (NaN, as torch)
-      v[i][j] = exp_sel<kAccurate>(v[i][j] - m);
-      s += v[i][j];
+      float e;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v[i][j] - m));
+      v[i][j] = e;
+      s += e;
     }
   }
   s = warp_sum(s);
@@ -318,7 +328,7 @@ softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t row
     if (c < nchunks) {
       float o[N];
 #pragma unroll
-      for (int j = 0; j < N; ++j) o[j] = (c * N + j < allowed) ? v[i][j] * inv : 0.0f;
+      for (int j = 0; j < N; ++j) o[j] = v[i][j] * inv;
       Chunk<Tout, N>::store(yr + c * N, o);
     }
   }
