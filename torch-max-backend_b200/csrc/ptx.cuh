@@ -154,8 +154,11 @@ __device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
 }
 
 // Arrive (count 1) on an mbarrier that may live in the peer CTA; `bar` is a shared::cluster address.
+// Default ordering (release at CTA scope): a cluster-scope release would first wait for every
+// global store of the thread to become visible cluster-wide, and what the arrival publishes here
+// is tensor-memory traffic, which the tcgen05 fence before it orders.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // Hardware barrier over all threads of the cluster (every warp must reach it converged).
