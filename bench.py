@@ -39,6 +39,7 @@ import torch.distributed as dist  # noqa: E402
 
 GLOBAL_BATCH = 64
 SEQ_LEN = 1024
+NCU_DRAM_BYTES_MLP_DOWN = 251.75e6 + 37.19e6
 MICRO_BATCH = 8
 VOCAB = 50257
 
@@ -285,7 +286,13 @@ def main():
     peak = peaks["bf16_tflops_sustained"]
     roofline = {
         "bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak, "traffic": None, "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
+        "frac": achieved / peak,
+        # DRAM bytes of one launch of the GEMM with the largest time share (MLP down-projection,
+        # 8192x6400x1600 + fp32 residual; algorithmic 229 MB) from its ncu capture, summarised in
+        # profiles/gemm_tcgen05_xl_out_8192x6400x1600.md: dram__bytes_read.sum + dram__bytes_write.sum
+        "traffic": NCU_DRAM_BYTES_MLP_DOWN if args.model == "xl" else None,
+        "traffic_unit": "bytes per launch (ncu capture, MLP down-projection GEMM)",
+        "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
         "launches_timed": gemm["launches"],
         "per_op_ms": {k: round(v["ms"], 3) for k, v in prof.items()},
     }
