@@ -217,3 +217,42 @@ def test_masked_softmax_is_left_alone_when_the_mask_varies_over_heads(stand_ins)
         got = torch.compile(fn, backend=mojo_backend)(att, mask)
     torch.testing.assert_close(got, fn(att, mask))
     assert not [c for c in stand_ins.calls if c[0] == "softmax_masked"]
+
+
+def test_export_with_frozen_weights_matches_eager(stand_ins):
+    """export_to_max_graph: parameters and buffers become plan constants, only the user inputs
+    are passed at run time, a [K, N]-contiguous weight used directly by mm is repacked K-major,
+    and the result equals eager."""
+    from torch_mojo_backend.torch_compile_backend.exporter import export_to_max_graph
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = torch.nn.Linear(16, 32)
+            self.ln = torch.nn.LayerNorm(32)
+            self.conv1d_weight = torch.nn.Parameter(torch.randn(32, 24) * 0.1)  # [K, N] like HF Conv1D
+            self.register_buffer("shift", torch.arange(24, dtype=torch.float32) * 0.01)
+
+        def forward(self, x):
+            h = self.ln(F.gelu(self.fc(x), approximate="tanh"))
+            return h @ self.conv1d_weight + self.shift, h.sum(-1)
+
+    torch.manual_seed(0)
+    net = Net().eval()
+    x = torch.randn(5, 16)
+    exported = export_to_max_graph(net, (x,))
+    assert exported.num_user_inputs == 1
+    frozen = [c for _, c in exported.plan.constants]
+    assert len(frozen) == 6  # fc.weight, fc.bias, ln.weight, ln.bias, conv1d_weight, shift
+    repacked = [c for c in frozen if c.shape == (32, 24)]
+    assert repacked and repacked[0].stride() == (1, 32), "the [K, N] weight is stored K-major"
+    with torch.no_grad():
+        want = net(x)
+    got = exported.execute(x)
+    for g, w in zip(got, want):
+        torch.testing.assert_close(g, w, rtol=1e-5, atol=1e-5)
+    x2 = torch.randn(5, 16)
+    with torch.no_grad():
+        torch.testing.assert_close(exported(x2)[0], net(x2)[0], rtol=1e-5, atol=1e-5)
+    with pytest.raises(TypeError, match="expected 1 inputs"):
+        exported.execute(x, x)

@@ -105,6 +105,23 @@ def test_gpt2_tiny_golden(tmb, golden, attention):
     assert_parity(logits, torch.from_numpy(golden[f"gpt_logits_{attention}"]), bf16=False)
 
 
+@pytest.mark.parametrize("cuda_graph", [False, True])
+def test_export_with_frozen_weights_gpt2_tiny(tmb, golden, cuda_graph):
+    """export_to_max_graph (torch.export, weights frozen into the plan, optional CUDA-graph
+    replay): same logits as the golden CPU-eager run, from token ids alone, on two calls."""
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+    from torch_mojo_backend.torch_compile_backend.exporter import export_to_max_graph
+
+    cfg = GPTConfig(vocab_size=211, block_size=32, n_layer=2, n_head=4, n_embd=64)
+    model = GPT2(cfg, "sdpa").init_weights(0).eval().cuda()
+    ids = torch.from_numpy(golden["gpt_ids"]).cuda()
+    exported = export_to_max_graph(model, (ids,), cuda_graph=cuda_graph)
+    assert exported.num_user_inputs == 1
+    for _ in range(2):
+        (logits,) = exported.execute(ids)
+        assert_parity(logits, torch.from_numpy(golden["gpt_logits_sdpa"]), bf16=False)
+
+
 def test_gpt2_small_fp32_config(tmb):
     """GPT-2 small, fp32, batch 1 x 128 tokens, seed-0 weights: logits within 1e-4 of CPU eager."""
     from demo_scripts.gpt2 import GPT2, GPTConfig

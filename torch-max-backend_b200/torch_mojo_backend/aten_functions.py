@@ -480,6 +480,21 @@ for _fused in (fused_layer_norm, fused_gemm, contiguous_or_alias, fused_masked_s
     MAPPING_TORCH_ATEN_TO_MOJO[_fused] = _fused
 
 
+# _assert_tensor_metadata(Tensor a, SymInt[]? size=None, SymInt[]? stride=None, ScalarType? dtype=None,
+#                         *, Device? device=None, Layout? layout=None) -> ()
+@map_to(aten._assert_tensor_metadata)
+def aten__assert_tensor_metadata(a, size=None, stride=None, dtype=None, *, device=None, layout=None):
+    """torch.export leaves this check behind dtype / device casts. Shape and dtype are verified
+    where the lowering runs (once on the trace's FakeTensors at plan-building time, then per
+    call on metadata only: no kernel is launched). The device is not compared: a plan exported
+    with `force_device` runs its frozen weights somewhere else than the module had them."""
+    if dtype is not None and a.dtype != dtype:
+        raise AssertionError(f"tensor dtype mismatch: expected {dtype}, got {a.dtype}")
+    if size is not None and list(a.shape) != list(size):
+        raise AssertionError(f"tensor size mismatch: expected {list(size)}, got {list(a.shape)}")
+    return None
+
+
 # ==============================================================================================
 # Glue: ops kept whole and executed by stock torch on CUDA views
 # ==============================================================================================
