@@ -256,3 +256,21 @@ def test_export_with_frozen_weights_matches_eager(stand_ins):
         torch.testing.assert_close(exported(x2)[0], net(x2)[0], rtol=1e-5, atol=1e-5)
     with pytest.raises(TypeError, match="expected 1 inputs"):
         exported.execute(x, x)
+
+
+def test_fp32_split_gemm_wiring(stand_ins):
+    """The "high" fp32 matmul precision level: three bf16 GEMMs chained through the fp32 residual
+    input reproduce the fp32 product to ~1e-5; "highest" leaves a single fp32 GEMM."""
+    g = torch.Generator().manual_seed(0)
+    a, b, bias = torch.randn(256, 512, generator=g), torch.randn(512, 192, generator=g) * 0.05, torch.randn(192, generator=g)
+    want = torch.addmm(bias.double(), a.double(), b.double()).float()
+    old = torch.get_float32_matmul_precision()
+    try:
+        for level, calls, tol in (("highest", 1, 1e-5), ("high", 3, 1e-4), ("medium", 1, 2e-2)):
+            torch.set_float32_matmul_precision(level)
+            stand_ins.calls.clear()
+            got = af.aten_addmm(bias, a, b)
+            assert len(stand_ins.calls) == calls
+            assert (got - want).abs().max().item() <= tol * want.abs().max().item()
+    finally:
+        torch.set_float32_matmul_precision(old)

@@ -277,3 +277,30 @@ def test_no_device_timeout_recorded():
     from torch_mojo_backend import native
 
     assert native.device_status() == 0
+
+
+@pytest.mark.parametrize("level,rtol", [("high", 1e-4), ("medium", 2e-2)])
+def test_fp32_matmul_precision_levels_use_the_tensor_cores(level, rtol):
+    """torch.set_float32_matmul_precision("high") runs an fp32 mm / addmm as three bf16
+    tensor-core GEMMs (two-term bf16 split of each operand), "medium" as one; "high" must still
+    meet the fp32 tolerance of the default exact route."""
+    from torch_mojo_backend import aten_functions as af
+    from torch_mojo_backend import native
+
+    m, k, n = 1024, 768, 1536
+    a, w, bias = gen((m, k), torch.float32, 70), gen((n, k), torch.float32, 71, 0.05), gen((n,), torch.float32, 72)
+    want = torch.addmm(bias.double(), a.double(), w.double().t()).float()
+    old = torch.get_float32_matmul_precision()
+    try:
+        torch.set_float32_matmul_precision(level)
+        before = native.launch_count
+        got = af.aten_addmm(bias.cuda(), a.cuda(), w.cuda().t())
+        launches = native.launch_count - before
+        got_mm = af.aten_mm(a.cuda(), w.cuda().t())
+    finally:
+        torch.set_float32_matmul_precision(old)
+    assert launches == (3 if level == "high" else 1)
+    assert got.dtype == torch.float32
+    scale = want.abs().max().item()
+    assert (got.cpu() - want).abs().max().item() <= rtol * scale
+    assert (got_mm.cpu() - (want - bias)).abs().max().item() <= rtol * scale

@@ -80,7 +80,7 @@ def time_case(make_inputs, run, bytes_per_copy, iters, use_graph):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="gemm,gemm_fused,layer_norm,softmax,gelu,reduce,sdpa,sdpa_decode")
+    ap.add_argument("--ops", default="gemm,gemm_fused,gemm_fp32_split,layer_norm,softmax,gelu,reduce,sdpa,sdpa_decode")
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--only", default="", help="substring filter on the case name")
     ap.add_argument("--no-graph", action="store_true", help="plain launches (what an ncu capture wants)")
@@ -141,6 +141,30 @@ def main():
                         us, rot = time_case(make, lambda t: ops.gemm(t[0], t[1], t[2]), nbytes, args.iters, use_graph)
                         bound = "tensor" if m >= 512 else "hbm"
                         report(name, us, rot, 2.0 * m * n * k, nbytes, bound)
+
+    if "gemm_fp32_split" in wanted:
+        # fp32 operands on the bf16 tensor cores: torch.set_float32_matmul_precision("high") makes the
+        # lowering split each operand into two bf16 terms and run three tensor-core GEMMs.
+        from torch_mojo_backend import aten_functions as af
+
+        for m, k, n in ((8192, 768, 2304), (8192, 1600, 6400)):
+            for level in ("highest", "high"):
+                name = f"gemm_fp32_split {level} {m}x{k}x{n} B=nk +bias"
+                if not keep(name):
+                    continue
+                nbytes = 4 * (m * k + k * n + m * n + n)
+
+                def make(i, m=m, k=k, n=n):
+                    return randn((m, k), torch.float32), randn((n, k), torch.float32, 0.05).t(), randn((n,), torch.float32, 0.02)
+
+                old_level = torch.get_float32_matmul_precision()
+                torch.set_float32_matmul_precision(level)
+                try:
+                    us, rot = time_case(make, lambda t: af.aten_addmm(t[2], t[0], t[1]), nbytes,
+                                        max(4, args.iters // 4), use_graph)
+                finally:
+                    torch.set_float32_matmul_precision(old_level)
+                report(name, us, rot, 2.0 * m * n * k, nbytes, "tensor")
 
     if "gemm_fused" in wanted:
         # The GEMMs of one GPT-2 XL block (and the LM head) as the fused graph launches them.

@@ -102,11 +102,42 @@ def _kernel_dtype(*tensors) -> bool:
 # ==============================================================================================
 
 
+def _fp32_on_tensor_cores(a, b) -> str | None:
+    """"high" / "medium" when a 2-D fp32 product should run on the bf16 tensor cores, as
+    torch.set_float32_matmul_precision defines those levels ("high": each fp32 number treated as
+    the sum of two bfloat16 numbers; "medium": bfloat16 operands), else None. The default
+    ("highest") keeps the exact-fp32 CUDA-core kernel. Small products stay there too."""
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.dim() != 2 or b.dim() != 2:
+        return None
+    level = torch.get_float32_matmul_precision()
+    if level == "highest" or a.shape[0] * a.shape[1] * b.shape[1] < (1 << 24):
+        return None
+    return level
+
+
+def _fp32_split_gemm(level, a, b, bias, alpha, beta):
+    """alpha * a @ b + beta * bias for fp32 a, b on the bf16 tensor cores. With x = x_hi + x_lo
+    (x_hi = bf16(x), x_lo = bf16(x - x_hi)), a @ b ~= a_hi b_lo + a_lo b_hi + a_hi b_hi (the
+    dropped a_lo b_lo term is ~2^-16 of the product): three GEMMs that accumulate in fp32 through
+    the residual input of the epilogue, smallest terms first."""
+    a_hi, b_hi = a.bfloat16(), b.bfloat16()
+    if level == "medium":
+        return ops.gemm(a_hi, b_hi, bias, None, alpha, beta, 0, torch.float32)
+    a_lo = (a - a_hi.float()).bfloat16()
+    b_lo = (b - b_hi.float()).bfloat16()
+    c = ops.gemm(a_hi, b_lo, None, None, alpha, 1.0, 0, torch.float32)
+    c = ops.gemm(a_lo, b_hi, None, c, alpha, 1.0, 0, torch.float32)
+    return ops.gemm(a_hi, b_hi, bias, c, alpha, beta, 0, torch.float32)
+
+
 # mm(Tensor self, Tensor mat2) -> Tensor
 @map_to(aten.mm)
 def aten_mm(x, y):
     if not _kernel_dtype(x, y):
         return aten.mm.default(x, y)
+    level = _fp32_on_tensor_cores(x, y)
+    if level is not None:
+        return _fp32_split_gemm(level, x, y, None, 1.0, 1.0)
     return ops.gemm(x, y)
 
 
@@ -117,6 +148,9 @@ def aten_addmm(input, mat1, mat2, *, beta=1.0, alpha=1.0):
     # happen in the GEMM epilogue on the fp32 accumulator.
     if not _kernel_dtype(input, mat1, mat2):
         return aten.addmm.default(input, mat1, mat2, beta=beta, alpha=alpha)
+    level = _fp32_on_tensor_cores(mat1, mat2)
+    if level is not None and input.dtype == torch.float32:
+        return _fp32_split_gemm(level, mat1, mat2, input, float(alpha), float(beta))
     return ops.gemm(mat1, mat2, input, None, float(alpha), float(beta))
 
 
