@@ -330,6 +330,23 @@ def _sdpa_kernel(query, key, value, is_causal, scale):
     return out, lse
 
 
+_PLACEHOLDERS: dict = {}
+
+
+def _placeholder(shape, dtype, device):
+    """A zero tensor for the attention outputs that only a backward pass or dropout replay would
+    read (philox seed / offset, debug mask). One per (shape, dtype, device), made once: filling a
+    fresh one per call costs a kernel launch per attention layer for values nobody reads."""
+    capturing = torch.device(device).type == "cuda" and torch.cuda.is_current_stream_capturing()
+    if torch._guards.detect_fake_mode() is not None or capturing:
+        return torch.zeros(shape, dtype=dtype, device=device)  # tracing / capture: nothing is cached
+    key = (tuple(shape), dtype, device)
+    t = _PLACEHOLDERS.get(key)
+    if t is None:
+        t = _PLACEHOLDERS[key] = torch.zeros(shape, dtype=dtype, device=device)
+    return t
+
+
 # _scaled_dot_product_flash_attention(Tensor query, Tensor key, Tensor value, float dropout_p=0.0,
 #   bool is_causal=False, bool return_debug_mask=False, *, float? scale=None)
 #   -> (Tensor, Tensor, Tensor, Tensor, SymInt, SymInt, Tensor, Tensor, Tensor)
@@ -344,9 +361,9 @@ def aten__scaled_dot_product_flash_attention(
     # placeholders for them too (torch_mojo_backend/aten_functions.py:609-677). Here logsumexp
     # is the real one.
     dev = out.device
-    rng = torch.zeros((2,), dtype=torch.int64, device=dev)
-    unused = torch.zeros((), dtype=torch.int64, device=dev)
-    debug_mask = torch.zeros((), dtype=out.dtype, device=dev)
+    rng = _placeholder((2,), torch.int64, dev)
+    unused = _placeholder((), torch.int64, dev)
+    debug_mask = _placeholder((), out.dtype, dev)
     return (out, _lse_as_traced(lse), None, None, query.shape[2], key.shape[2], rng, unused, debug_mask)
 
 
@@ -367,8 +384,8 @@ def aten__scaled_dot_product_efficient_attention(
     dev = out.device
     if not compute_log_sumexp:
         lse = lse.new_empty((*lse.shape[:-1], 0))
-    seed = torch.zeros((), dtype=torch.int64, device=dev)
-    return out, _lse_as_traced(lse), seed, seed.clone()
+    seed = _placeholder((), torch.int64, dev)
+    return out, _lse_as_traced(lse), seed, seed
 
 
 # _scaled_dot_product_cudnn_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_bias,
@@ -387,8 +404,8 @@ def aten__scaled_dot_product_cudnn_attention(
     else:
         out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
     dev = out.device
-    rng = torch.zeros((), dtype=torch.int64, device=dev)
-    return (out, _lse_as_traced(lse.unsqueeze(-1)), None, None, query.shape[2], key.shape[2], rng, rng.clone(), None)
+    rng = _placeholder((), torch.int64, dev)
+    return (out, _lse_as_traced(lse.unsqueeze(-1)), None, None, query.shape[2], key.shape[2], rng, rng, None)
 
 
 def _sdpa_math(query, key, value, attn_mask, is_causal, scale):
