@@ -207,6 +207,15 @@ def main():
                 us, rot = time_case(make, lambda t: ops.layer_norm(t[0], t[1], t[2], 1e-5), nbytes, args.iters, use_graph)
                 report(name, us, rot, nbytes=nbytes)
 
+        # the variant the fused GPT-2 graph launches: fp32 residual stream in, bf16 GEMM operand out
+        for rows, cols in ((8192, 1600), (65536, 1600)):
+            name = f"layer_norm fp32->bf16 {rows}x{cols}"
+            if keep(name):
+                nbytes = rows * cols * (4 + 2) + 8 * rows
+                make = lambda i, rows=rows, cols=cols: (randn((rows, cols), torch.float32), randn((cols,), torch.float32, 0.02, 1.0), randn((cols,), torch.float32, 0.02))
+                us, rot = time_case(make, lambda t: ops.layer_norm(t[0], t[1], t[2], 1e-5, torch.bfloat16), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+
     if "softmax" in wanted:
         for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
             shape = (96, 1024, 1024)
