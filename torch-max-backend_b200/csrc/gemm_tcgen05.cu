@@ -680,12 +680,15 @@ int pick_pair_bn(const b200_gemm_args& g) {
     if (v == 128 || v == 192 || v == 256) return v;
   }
   const int64_t pairs = sm_count() / 2;
-  auto cost = [&](int bn, double per_col) {
+  // Time of a tile ~ (BN + 270) columns' worth: the measured fixed share per tile (issue loop,
+  // accumulator hand-off, epilogue) is about as large as the width-proportional part, so wide
+  // tiles win unless they cost an extra wave.
+  auto cost = [&](int bn) {
     const int64_t tiles = ((g.m + 2 * BM - 1) / (2 * BM)) * ((g.n + bn - 1) / bn) * g.batch;
     const int64_t waves = (tiles + pairs - 1) / pairs;
-    return (double)waves * (bn * per_col + 24);
+    return (double)waves * (bn + 270);
   };
-  const double c256 = cost(256, 1.0), c192 = cost(192, 1.04), c128 = cost(128, 1.12);
+  const double c256 = cost(256), c192 = cost(192), c128 = cost(128);
   if (c256 <= c192 && c256 <= c128) return 256;
   return c192 <= c128 ? 192 : 128;
 }
