@@ -194,6 +194,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the b200 kernels have no CPU fallback")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    # Every micro-batch launches the same ~340 kernels with the same shapes: replay them from a
+    # CUDA graph (the backend's own switch; export TORCH_MOJO_BACKEND_CUDA_GRAPHS=0 for the eager plan).
+    os.environ.setdefault("TORCH_MOJO_BACKEND_CUDA_GRAPHS", "1")
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
@@ -262,11 +265,18 @@ def main():
             step_e2e()
         e2e_ms, _ = timed(step_e2e, args.steps)
 
-        # one instrumented step: CUDA events around every kernel launch of this library
+        # one instrumented step: CUDA events around every kernel launch of this library (the eager
+        # plan: inside a replayed CUDA graph there is nothing to bracket)
+        graphs_flag = os.environ.get("TORCH_MOJO_BACKEND_CUDA_GRAPHS")
+        os.environ["TORCH_MOJO_BACKEND_CUDA_GRAPHS"] = "0"
         native.profiler = native.KernelProfiler()
         step_resident()
         prof = native.profiler.summary()
         native.profiler = None
+        if graphs_flag is None:
+            os.environ.pop("TORCH_MOJO_BACKEND_CUDA_GRAPHS", None)
+        else:
+            os.environ["TORCH_MOJO_BACKEND_CUDA_GRAPHS"] = graphs_flag
 
     tokens = float(my_seqs * SEQ_LEN * args.steps)
     agg = aggregate_throughput(tokens, elapsed_ms, device)
@@ -304,7 +314,9 @@ def main():
         "config": {"workload": f"gpt2-{args.model} forward (config: GPT-2 XL bf16, global batch 64 x 1024 "
                                f"batch-sharded), micro-batch {MICRO_BATCH} sequences",
                    "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "parallelism": f"batch-shard x{world}, no collective",
-                   "l2": "inputs larger than L2 (weights 3 GB, activations 52 MB per tensor)"},
+                   "l2": "inputs larger than L2 (weights 3 GB, activations 52 MB per tensor)",
+                   "launch": "CUDA-graph replay of the launch plan"
+                             if os.environ.get("TORCH_MOJO_BACKEND_CUDA_GRAPHS", "0") == "1" else "eager launch plan"},
         "tflops_per_gpu": value / world * flops_per_token(cfg, SEQ_LEN) / 1e12,
         "clocks": clocks.summary(),
         "e2e": {"value": agg_e2e["units"] / (agg_e2e["ms"] / 1e3), "unit": "tokens/s",

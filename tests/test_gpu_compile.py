@@ -183,10 +183,20 @@ def test_cuda_graph_replay_matches_eager_plan(tmb, monkeypatch):
     monkeypatch.setenv("TORCH_MOJO_BACKEND_CUDA_GRAPHS", "1")
     torch._dynamo.reset()
     compiled = torch.compile(model, backend=tmb.mojo_backend)
+    from torch_mojo_backend import native
+
+    counts = []
     with torch.no_grad():
         for i in range(4):  # call 1 eager, call 2 captures, calls 3-4 replay with fresh input buffers
+            before = native.launch_count
             out = compiled(ids.clone())
+            counts.append(native.launch_count - before)
             assert torch.equal(out, eager), f"call {i}"
+    # A replay accounts for exactly the kernels an eager call launches; a call that captures
+    # (call 2, and call 3 if the allocator handed calls 1 and 2 the same input address, so that the
+    # input first looked static) runs a warm-up as well and counts twice.
+    k = counts[0]
+    assert k > 0 and counts[1] == 2 * k and counts[2] in (k, 2 * k) and counts[3] == k, counts
 
 
 def test_no_device_timeout_recorded():

@@ -16,6 +16,8 @@ from __future__ import annotations
 
 import torch
 
+from torch_mojo_backend import native
+
 
 def _signature(args):
     sig = []
@@ -37,6 +39,7 @@ class GraphRunner:
         self._copy_idx = ()
         self._pinned_ptrs = {}
         self._outputs = None
+        self._kernels = 0  # kernels of this library inside the captured graph
         self.replays = 0
 
     def _reset(self):
@@ -70,6 +73,7 @@ class GraphRunner:
             self._static_args[i].copy_(args[i], non_blocking=True)
         self._graph.replay()
         self.replays += 1
+        native.launch_count += self._kernels  # the replay launched them; the op wrappers did not run
         return self._outputs
 
     def _capture(self, args, ptrs):
@@ -89,6 +93,10 @@ class GraphRunner:
             self.plan.run(self._static_args)  # warm-up on the side stream (allocator, attributes)
         torch.cuda.current_stream(device).wait_stream(stream)
         graph = torch.cuda.CUDAGraph()
+        before = native.launch_count
         with torch.cuda.graph(graph):
             self._outputs = self.plan.run(self._static_args)
+        # recorded, not launched: they count once per replay instead
+        self._kernels = native.launch_count - before
+        native.launch_count = before
         self._graph = graph
