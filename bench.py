@@ -40,7 +40,7 @@ import torch.distributed as dist  # noqa: E402
 GLOBAL_BATCH = 64
 SEQ_LEN = 1024
 NCU_DRAM_BYTES_MLP_DOWN = 252.54e6 + 38.88e6
-MICRO_BATCH = 8
+MICRO_BATCH = 64  # sequences per forward call: the rank's whole shard when it has no more than this
 VOCAB = 50257
 
 
@@ -53,6 +53,7 @@ def parse_args():
     p.add_argument("--model", choices=["xl", "small"], default="xl", help="small is for quick checks only")
     p.add_argument("--cpu-sample-tokens", type=int, default=1024)
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--micro-batch", type=int, default=MICRO_BATCH, help="sequences per forward call")
     return p.parse_args()
 
 
@@ -222,7 +223,7 @@ def main():
     all_ids = torch.randint(0, cfg.vocab_size, (GLOBAL_BATCH, SEQ_LEN), generator=torch.Generator().manual_seed(0))
     ids_host = all_ids[start:end].contiguous().pin_memory()
     ids_dev = ids_host.to(device)
-    micro = [(i, min(i + MICRO_BATCH, my_seqs)) for i in range(0, my_seqs, MICRO_BATCH)]
+    micro = [(i, min(i + args.micro_batch, my_seqs)) for i in range(0, my_seqs, args.micro_batch)]
 
     def step_resident():
         out = None
@@ -300,8 +301,11 @@ def main():
         # DRAM bytes of one launch of the GEMM with the largest time share (MLP down-projection,
         # 8192x6400x1600 + fp32 residual; algorithmic 229 MB) from its ncu capture, summarised in
         # profiles/gemm_tcgen05_xl_out_8192x6400x1600.md: dram__bytes_read.sum + dram__bytes_write.sum
-        "traffic": NCU_DRAM_BYTES_MLP_DOWN if args.model == "xl" else None,
-        "traffic_unit": "bytes per launch (ncu capture, MLP down-projection GEMM)",
+        # (captured at 8192 rows per launch; operand, residual and output bytes all grow with the
+        # row count, so the figure is scaled to the rows one launch of this run processes)
+        "traffic": NCU_DRAM_BYTES_MLP_DOWN * (min(args.micro_batch, my_seqs) * SEQ_LEN / 8192.0)
+        if args.model == "xl" else None,
+        "traffic_unit": "bytes per launch (ncu capture of the MLP down-projection GEMM at 8192 rows, scaled by rows)",
         "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
         "launches_timed": gemm["launches"],
         "per_op_ms": {k: round(v["ms"], 3) for k, v in prof.items()},
@@ -312,7 +316,7 @@ def main():
         "ms_per_step": agg["ms"] / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"gpt2-{args.model} forward (config: GPT-2 XL bf16, global batch 64 x 1024 "
-                               f"batch-sharded), micro-batch {MICRO_BATCH} sequences",
+                               f"batch-sharded), micro-batch {args.micro_batch} sequences",
                    "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "parallelism": f"batch-shard x{world}, no collective",
                    "l2": "inputs larger than L2 (weights 3 GB, activations 52 MB per tensor)",
                    "launch": "CUDA-graph replay of the launch plan"

@@ -304,3 +304,20 @@ def test_fp32_matmul_precision_levels_use_the_tensor_cores(level, rtol):
     scale = want.abs().max().item()
     assert (got.cpu() - want).abs().max().item() <= rtol * scale
     assert (got_mm.cpu() - (want - bias)).abs().max().item() <= rtol * scale
+
+
+def test_tcgen05_output_beyond_2_31_elements(ops):
+    """LM-head shape at the benchmark's largest forward: [65536, 64] x [64, 50257] -> fp32 logits,
+    3.3e9 output elements (13 GB), so every output offset that is not computed in 64 bits wraps.
+    Checked on rows from the first, a middle and the last tile against the CPU oracle."""
+    m, k, n = 65536, 64, 50257
+    g = torch.Generator(device="cuda").manual_seed(80)
+    a = torch.randn((m, k), generator=g, device="cuda").bfloat16()
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.1).bfloat16()
+    y = ops.gemm(a, w.t(), None, None, 1.0, 1.0, 0, torch.float32, ROUTE_TC)
+    assert y.shape == (m, n) and y.dtype == torch.float32
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, 32767, 32768, 42719, 65279, 65280, 65535])
+    want = a[rows.cuda()].float().cpu() @ w.float().cpu().t()
+    assert_parity(y[rows.cuda()], want, bf16=False, scale=k**0.5 * 0.4)
+    del y
+    torch.cuda.empty_cache()
