@@ -62,7 +62,8 @@ def test_sdpa_fused_qkv_strided_views_and_kv_longer(ops):
 
 
 @pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("q_len,kv_len", [(1, 1), (77, 300), (64, 200), (129, 129), (300, 77), (128, 64)])
+@pytest.mark.parametrize("q_len,kv_len", [(1, 1), (77, 300), (64, 200), (129, 129), (300, 77), (128, 64),
+                                          (256, 256), (257, 513), (384, 384), (512, 300), (640, 640), (130, 1000)])
 def test_sdpa_tensor_core_route_ragged_lengths(ops, causal, q_len, kv_len):
     """head_dim 64 bf16 takes the tcgen05 kernel: ragged tiles, kv_len != q_len (causal mask is
     top-left aligned), single-row and single-key cases; forced route so that a silent reroute fails."""
@@ -147,6 +148,37 @@ def test_sdpa_benchmark_shapes_bf16(ops, shape):
     # and LSE of row 0 is the single scaled score q0.k0 / sqrt(d)
     s00 = (q[:, :, 0, :].float() * k[:, :, 0, :].float()).sum(-1) / shape[-1] ** 0.5
     assert_parity(lse[:, :, 0], s00, bf16=False, scale=max(s00.abs().max().item(), 1.0))
+
+
+def test_sdpa_many_items_per_cta_and_l2_groups(ops):
+    """More work items than CTAs and more (batch, head) pairs than one L2 group holds (the
+    kernel walks pairs in groups sized for L2 and, inside a group, query tiles heaviest first):
+    every item must still land on its own rows. Checked on a sample of pairs against the oracle."""
+    B, H, T = 3, 67, 768   # 201 pairs, 3 query-tile pairs each: 603 items on 148 CTAs
+    q, k, v = gen((B, H, T, 64), torch.bfloat16, 40), gen((B, H, T, 64), torch.bfloat16, 41), gen((B, H, T, 64), torch.bfloat16, 42)
+    out, lse = ops.sdpa(q.cuda(), k.cuda(), v.cuda(), True, None, 2)
+    for b, h in ((0, 0), (0, 66), (1, 33), (2, 13), (2, 66)):
+        want, want_lse = ref_ops.sdpa(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], True)
+        assert_parity(out[b:b + 1, h:h + 1], want, bf16=True, what=f"pair ({b},{h})")
+        assert_parity(lse[b:b + 1, h:h + 1], want_lse, bf16=False, scale=max(want_lse.abs().max().item(), 1.0) * 10)
+    # size-independent property over every pair: row 0 attends only to key 0
+    assert torch.equal(out[:, :, 0, :].cpu(), v[:, :, 0, :])
+
+
+def test_sdpa_large_scores_trigger_lazy_rescale(ops):
+    """Scores whose running maximum keeps growing along the keys (so the accumulator in tensor
+    memory has to be rescaled after the first tile, the rare path of the lazy-rescale scheme)."""
+    B, H, T = 1, 2, 512
+    q = gen((B, H, T, 64), torch.bfloat16, 43)
+    k = gen((B, H, T, 64), torch.bfloat16, 44)
+    # keys grow along the sequence so that later tiles hold much larger scores
+    k = (k.float() * torch.linspace(0.5, 6.0, T).view(1, 1, T, 1)).to(torch.bfloat16)
+    v = gen((B, H, T, 64), torch.bfloat16, 45)
+    for causal in (False, True):
+        out, lse = ops.sdpa(q.cuda(), k.cuda(), v.cuda(), causal, None, 2)
+        want, want_lse = ref_ops.sdpa(q, k, v, causal)
+        assert_parity(out, want, bf16=True)
+        assert_parity(lse, want_lse, bf16=False, scale=max(want_lse.abs().max().item(), 1.0) * 10)
 
 
 def test_no_device_timeout_recorded():

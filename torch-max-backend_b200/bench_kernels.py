@@ -268,7 +268,7 @@ def main():
                 report(name, us, rot, nbytes=nbytes)
 
     if "sdpa" in wanted:
-        for B, H, T, D in ((8, 12, 1024, 64), (4, 25, 2048, 64), (8, 25, 1024, 64)):
+        for B, H, T, D in ((8, 12, 1024, 64), (4, 25, 2048, 64), (8, 25, 1024, 64), (64, 25, 1024, 64)):
             name = f"sdpa bf16 causal {B}x{H}x{T}x{D}"
             if not keep(name):
                 continue
