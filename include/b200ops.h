@@ -60,6 +60,8 @@ extern "C" {
 #define B200_ROUTE_SIMT 1     /* generic strided CUDA-core kernel, any layout */
 #define B200_ROUTE_TCGEN05 2  /* TMA-fed tcgen05/TMEM tensor-core kernel */
 #define B200_ROUTE_SKINNY 3   /* decode shapes, HBM bound: split-K small-M GEMM; split-KV attention for <= 16 query rows */
+#define B200_ROUTE_SPLIT3 4   /* fp32 GEMM on the bf16 tensor cores: operands split into bf16 halves, three products
+                                 accumulated in fp32 by one tensor-core launch (~2^-16 relative); needs workspace */
 
 typedef void* b200_stream_t; /* cudaStream_t */
 
@@ -74,6 +76,14 @@ B200_API const char* b200_last_error(void);
 /* Reads (and clears) the current device's status word; *word == 0 means no kernel gave up.
  * Synchronises the device: test/debug use only. */
 B200_API int32_t b200_device_status(uint32_t* word);
+
+/* Test hook for the bounded waits: enqueues a one-warp kernel that waits, for at most limit_ns
+ * (<= 100 ms), on a barrier nothing signals, and then gives up the way every kernel of the library
+ * gives up a wait that ran out (CTA abort flag, bit 2 of the status word, normal return). Nothing
+ * faults and nothing hangs; afterwards b200_device_status() reports B200_ERR_DEVICE_TIMEOUT once
+ * and the device is as usable as before. No counterpart in the reference (its kernels trap or
+ * spin); the production kernels use the same wait with a 2 s limit. */
+B200_API int32_t b200_debug_wait_timeout(uint64_t limit_ns, b200_stream_t stream);
 
 /* ---- row kernels (HBM bound) -------------------------------------------------------- */
 
@@ -125,17 +135,53 @@ B200_API int32_t b200_reduce_lastdim(const void* x, void* y, int64_t rows, int64
                             int64_t x_row_stride, int32_t op, int32_t in_dtype,
                             int32_t out_dtype, b200_stream_t stream);
 
+/* ---- index-driven row kernels (HBM bound) ---------------------------------------------- */
+
+/* out[r, :] = table_a[idx_a[r], :] (+ table_b[idx_b[r % idx_b_len], :]) for r < rows: an embedding
+ * gather, optionally summed with a second gather whose indices repeat with period idx_b_len (the
+ * positional table of a [batch, seq] batch: idx_b = arange(seq)). Tables are [rows_x, cols] with the
+ * given row strides and unit column stride; indices are int64; out is contiguous [rows, cols] in
+ * out_dtype (bf16 tables may be widened to fp32 on the way out; the sum is taken in fp32). table_b
+ * may be NULL. An index outside its table contributes zeros and sets bit 3 of the device status word.
+ * Replaces: aten_embedding (torch_mojo_backend/aten_functions.py:1779-1831) and the add of the token
+ * and positional embeddings that follows it in a GPT-2 graph (aten_add, :938). */
+B200_API int32_t b200_embedding_sum(const void* table_a, const int64_t* idx_a, int64_t rows_a,
+                           int64_t a_row_stride, const void* table_b, const int64_t* idx_b,
+                           int64_t rows_b, int64_t b_row_stride, int64_t idx_b_len, void* out,
+                           int64_t rows, int64_t cols, int32_t table_dtype, int32_t out_dtype,
+                           b200_stream_t stream);
+
+/* Index of the maximum over the last dim of x[rows, cols] -> out[rows] (int64). Ties go to the
+ * smallest index, a NaN counts as the maximum (torch.argmax). Rows need no alignment (the 50257-wide
+ * logits have a ragged pitch).
+ * Replaces: aten_argmax (torch_mojo_backend/aten_functions.py:1108-1150), the step that turns the
+ * LM head's logits into token ids. */
+B200_API int32_t b200_argmax_lastdim(const void* x, int64_t* out, int64_t rows, int64_t cols,
+                            int64_t x_row_stride, int32_t dtype, b200_stream_t stream);
+
+/* dst[o, 0:inner] = src[o, 0:inner] for o < outer; rows are dst_row_stride / src_row_stride elements
+ * of elem_bytes apart. One call per input writes a concatenation along any dim (outer = product of
+ * the leading dims, inner = the input's extent along the dim times the trailing dims), and writing a
+ * new token's K / V rows into a preallocated cache is the same copy with dst pointing at the slot.
+ * Replaces: aten_cat (torch_mojo_backend/aten_functions.py:1432-1449). */
+B200_API int32_t b200_copy_rows(void* dst, const void* src, int64_t outer, int64_t inner,
+                       int64_t dst_row_stride, int64_t src_row_stride, int32_t elem_bytes,
+                       b200_stream_t stream);
+
 /* ---- GEMM ---------------------------------------------------------------------------- */
 
 /* C[b] = act(alpha * A[b] @ B[b] + beta * bias) + residual, fp32 accumulation.
  * A is [m,k], B is [k,n], both with arbitrary element strides (a transposed view is just a
- * stride pair); C is [m,n] with unit column stride. bias is NULL, a 1-D [n] row
+ * stride pair); C is [m,n] with unit column stride. fp32 operands: B200_ROUTE_AUTO takes the
+ * split-precision tensor-core route for all but small problems (relative error ~2^-16, inside the
+ * 1e-4 bar of the fp32 configurations); B200_ROUTE_SIMT is the exact fp32 CUDA-core kernel. bias is NULL, a 1-D [n] row
  * (bias_row_stride == 0) or a 2-D [m,n] matrix; residual is NULL or [m,n].
  * Replaces: aten_mm / aten_addmm / aten_bmm
  * (torch_mojo_backend/aten_functions.py:2631-2634, 970-992, 1414-1428) and the eager GEMM
  * bridges Bf16GemmBF16 / MatmulBiasSpec
  * (torch_mojo_backend/eager_kernels/bf16_matmul_ops.mojo:66-188,
- *  torch_mojo_backend/eager_kernels/matmul_ops.mojo:3500). */
+ *  torch_mojo_backend/eager_kernels/matmul_ops.mojo:3500) and, for fp32 operands, the tensor-core
+ * fp32 GEMM (torch_mojo_backend/eager_kernels/tf32_gemm_kernels.mojo:91,690,723). */
 typedef struct b200_gemm_args {
   const void* a;
   const void* b;

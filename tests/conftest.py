@@ -4,6 +4,9 @@ from pathlib import Path
 
 # Before the package is imported: lowerings get call counters (map_to) in test runs.
 os.environ.setdefault("TORCH_MOJO_BACKEND_TESTING", "1")
+# The GEMM tuning switches (B200_GEMM_PAIR / B200_GEMM_TILE_N) are read once per process unless
+# this is set; the GEMM tests flip them between calls.
+os.environ.setdefault("B200_GEMM_ENV_LIVE", "1")
 
 ROOT = Path(__file__).resolve().parents[1]
 for p in (ROOT, ROOT / "torch-max-backend_b200"):

@@ -214,3 +214,27 @@ def test_only_first_output_used_sees_the_current_node():
     finally:
         MAPPING_TORCH_ATEN_TO_MOJO[aten.native_layer_norm] = original
     assert seen["first_only"] is True
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float64])
+def test_hot_ops_refuse_floating_dtypes_without_a_kernel(dtype):
+    """No silent trip through a vendor library: a float16 / float64 operand of one of the ops this
+    backend exists for is an error in the lowering (which the graph walk turns into a
+    MojoCompilerError while it builds the plan)."""
+    from torch_mojo_backend import aten_functions as af
+
+    x = torch.zeros((4, 8), dtype=dtype)
+    for call in (
+        lambda: af.aten_mm(x, x.t()),
+        lambda: af.aten_addmm(x[:, :4], x, x.t()),
+        lambda: af.aten_bmm(x[None], x.t()[None]),
+        lambda: af.aten__softmax(x, -1, False),
+        lambda: af.aten_native_layer_norm(x, [8], None, None, 1e-5),
+        lambda: af.aten_gelu(x),
+        lambda: af.aten_sum(x, [-1]),
+        lambda: af.aten_mean(x, [-1]),
+        lambda: af.aten_amax(x, [-1]),
+        lambda: af.aten_scaled_dot_product_attention(x[None, None], x[None, None], x[None, None]),
+    ):
+        with pytest.raises(NotImplementedError, match="not supported by the b200 kernels"):
+            call()

@@ -68,6 +68,22 @@ class _StandIns:
         return [x.sum(-1), x.mean(-1), x.amax(-1)][op].to(out_dtype or x.dtype)
 
     @staticmethod
+    def embedding_sum(table, indices, table2=None, indices2=None, out_dtype=None):
+        _StandIns._record(table, ("embedding_sum", table2 is not None, out_dtype))
+        y = F.embedding(indices, table).float()
+        if table2 is not None:
+            y = y + F.embedding(indices2, table2).float()
+        return y.to(out_dtype or table.dtype)
+
+    @staticmethod
+    def argmax(x):
+        return torch.argmax(x, -1)
+
+    @staticmethod
+    def cat(tensors, dim=0):
+        return torch.cat(list(tensors), dim)
+
+    @staticmethod
     def sdpa(q, k, v, causal=False, scale=None, route=0):
         out = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
         return out, torch.zeros(q.shape[:3])
@@ -99,6 +115,8 @@ def test_gpt2_bf16_policy_chains_are_folded(stand_ins):
     assert sum(1 for c in gemms if c[1] == native.EPILOGUE_GELU_TANH) == 2, "MLP up-projection carries the GELU"
     assert sum(1 for c in gemms if c[3]) == 4, "both projections of each block carry the residual add"
     assert gemms[-1][2] == torch.float32 and not gemms[-1][3], "LM head stores fp32 logits"
+    assert [c for c in stand_ins.calls if c[0] == "embedding_sum"] == [("embedding_sum", True, torch.float32)], \
+        "token + positional embeddings are one gather that writes the fp32 residual stream"
 
 
 def test_fused_gemm_wiring_matches_eager(stand_ins):
@@ -118,6 +136,32 @@ def test_fused_gemm_wiring_matches_eager(stand_ins):
     torch.testing.assert_close(got, fn(x, w1, b1, w2, b2, res), rtol=2e-2, atol=5e-2)
     assert [c for c in stand_ins.calls if c[0] == "gemm"] == [
         ("gemm", native.EPILOGUE_GELU_TANH, bf, False), ("gemm", 0, torch.float32, True)]
+
+
+def test_embedding_sum_fusion_and_its_limits(stand_ins):
+    wte = torch.randn(50, 16, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    wpe = torch.randn(12, 16, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    idx = torch.randint(0, 50, (3, 12), generator=torch.Generator().manual_seed(3))
+
+    def fused(idx, wte, wpe):
+        pos = torch.arange(idx.shape[1])
+        return F.embedding(idx, wte).float() + F.embedding(pos, wpe).float()
+
+    got = torch.compile(fused, backend=mojo_backend)(idx, wte, wpe)
+    torch.testing.assert_close(got, fused(idx, wte, wpe))
+    assert [c for c in stand_ins.calls if c[0] == "embedding_sum"] == [("embedding_sum", True, torch.float32)]
+
+    # an embedding whose result has a second consumer keeps its own gather
+    stand_ins.calls.clear()
+    torch._dynamo.reset()
+
+    def shared(idx, wte, wpe):
+        tok = F.embedding(idx, wte)
+        return tok + F.embedding(torch.arange(idx.shape[1]), wpe), tok.sum()
+
+    got2 = torch.compile(shared, backend=mojo_backend)(idx, wte, wpe)
+    torch.testing.assert_close(got2[0], shared(idx, wte, wpe)[0])
+    assert [c[1] for c in stand_ins.calls if c[0] == "embedding_sum"] == [False, False]
 
 
 def test_chain_with_a_second_consumer_is_not_folded(stand_ins):
@@ -258,19 +302,33 @@ def test_export_with_frozen_weights_matches_eager(stand_ins):
         exported.execute(x, x)
 
 
-def test_fp32_split_gemm_wiring(stand_ins):
-    """The "high" fp32 matmul precision level: three bf16 GEMMs chained through the fp32 residual
-    input reproduce the fp32 product to ~1e-5; "highest" leaves a single fp32 GEMM."""
+def test_fp32_gemm_precision_levels_wiring(stand_ins, monkeypatch):
+    """fp32 mm / addmm: "highest" and "high" hand the fp32 operands to one b200 GEMM call (whose own
+    routing puts all but small products on the tensor cores in split precision), "medium" rounds
+    the operands to bf16 first, and TORCH_MOJO_BACKEND_EXACT_FP32 pins the exact CUDA-core route."""
     g = torch.Generator().manual_seed(0)
     a, b, bias = torch.randn(256, 512, generator=g), torch.randn(512, 192, generator=g) * 0.05, torch.randn(192, generator=g)
     want = torch.addmm(bias.double(), a.double(), b.double()).float()
+    seen = []
+    real_gemm = stand_ins.gemm
+
+    def spy(a_, b_, *rest):
+        seen.append((a_.dtype, rest[6] if len(rest) > 6 else 0))
+        return real_gemm(a_, b_, *rest)
+
+    monkeypatch.setattr(stand_ins, "gemm", staticmethod(spy))
     old = torch.get_float32_matmul_precision()
     try:
-        for level, calls, tol in (("highest", 1, 1e-5), ("high", 3, 1e-4), ("medium", 1, 2e-2)):
+        for level, dtype, tol in (("highest", torch.float32, 1e-5), ("high", torch.float32, 1e-5), ("medium", torch.bfloat16, 2e-2)):
             torch.set_float32_matmul_precision(level)
-            stand_ins.calls.clear()
+            seen.clear()
             got = af.aten_addmm(bias, a, b)
-            assert len(stand_ins.calls) == calls
+            assert seen == [(dtype, 0)], level
+            assert got.dtype == torch.float32
             assert (got - want).abs().max().item() <= tol * want.abs().max().item()
+        monkeypatch.setenv("TORCH_MOJO_BACKEND_EXACT_FP32", "1")
+        seen.clear()
+        af.aten_mm(a, b)
+        assert seen == [(torch.float32, native.ROUTE_SIMT)]
     finally:
         torch.set_float32_matmul_precision(old)

@@ -203,3 +203,80 @@ def test_no_device_timeout_recorded():
     from torch_mojo_backend import native
 
     assert native.device_status() == 0
+
+
+def test_kernel_ops_under_dynamic_shapes(tmb):
+    """mark_dynamic on the batch and on the sequence length: GEMM, LayerNorm, softmax and attention
+    receive symbolic sizes, one compiled artefact serves every size, and every size matches the
+    oracle (reference: tests/test_compiler.py:484-507, extended from `x + y` to the kernel ops)."""
+    from torch._dynamo import mark_dynamic
+
+    from torch_mojo_backend import native
+
+    H, D, C = 4, 64, 256
+    g = torch.Generator().manual_seed(7)
+    w_qkv, b_qkv = torch.randn((C, 3 * C), generator=g) * 0.05, torch.randn((3 * C,), generator=g) * 0.02
+    ln_w, ln_b = torch.randn((C,), generator=g) * 0.02 + 1.0, torch.randn((C,), generator=g) * 0.02
+
+    def fn(x, w_qkv, b_qkv, ln_w, ln_b):
+        B, T, _ = x.shape
+        h = F.layer_norm(x, (C,), ln_w, ln_b, 1e-5)
+        qkv = torch.addmm(b_qkv, h.view(B * T, C), w_qkv).view(B, T, 3, H, D)
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return torch.softmax(y.transpose(1, 2).reshape(B, T, C), -1)
+
+    calls = {"n": 0}
+
+    class Counting(tmb.mojo_backend):
+        def __init__(self, *a, **kw):
+            calls["n"] += 1
+            super().__init__(*a, **kw)
+
+    torch._dynamo.reset()
+    compiled = torch.compile(fn, backend=Counting)
+    params = [t.cuda() for t in (w_qkv, b_qkv, ln_w, ln_b)]
+    before = native.launch_count
+    for batch, seq in ((3, 40), (2, 17), (5, 40), (2, 129), (4, 64)):  # sizes 0 and 1 are specialised by Dynamo
+        x = torch.randn((batch, seq, C), generator=g)
+        xg = x.cuda()
+        mark_dynamic(xg, 0)
+        mark_dynamic(xg, 1)
+        with torch.no_grad():
+            got = compiled(xg, *params)
+        assert_parity(got, fn(x, w_qkv, b_qkv, ln_w, ln_b), bf16=False, what=f"batch {batch} seq {seq}")
+    assert calls["n"] == 1, "one compiled artefact must serve every size"
+    assert native.launch_count - before >= 5 * 4  # LayerNorm, GEMM, attention, softmax per call
+
+
+def test_unsupported_dtype_is_a_compile_time_error(tmb):
+    """float16 operands of a hot op: MojoCompilerError while the plan is built, with the
+    reference's message contract, not a run through a vendor library."""
+    from torch_mojo_backend.torch_compile_backend.compiler import MojoCompilerError
+
+    def fn(a, b):
+        return a @ b
+
+    torch._dynamo.reset()
+    compiled = torch.compile(fn, backend=tmb.mojo_backend)
+    a = torch.randn((8, 8), dtype=torch.float16, device="cuda")
+    with pytest.raises(Exception) as info:
+        compiled(a, a)
+    text = str(info.value)
+    assert "not supported by the b200 kernels" in text and "aten_mm" in text
+    assert isinstance(info.value, MojoCompilerError) or "MojoCompilerError" in text
+
+
+def test_view_of_padded_logits(tmb):
+    """mm with an output pitch that is padded at run time (n = 50257), then a view that merges rows
+    and columns: the trace assumed contiguous strides, the lowering must still produce the right
+    values (it copies when the run-time layout cannot be viewed)."""
+    def fn(x, w):
+        return (x @ w.t()).view(-1)
+
+    g = torch.Generator().manual_seed(8)
+    x = (torch.randn((16, 64), generator=g)).to(torch.bfloat16)
+    w = (torch.randn((50257, 64), generator=g) * 0.1).to(torch.bfloat16)
+    got = run_compiled(tmb, fn, x, w)
+    assert got.shape == (16 * 50257,)
+    assert_parity(got, (x.float() @ w.float().t()).view(-1), bf16=True)

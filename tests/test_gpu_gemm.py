@@ -105,6 +105,52 @@ def test_tcgen05_addmm_m8192(ops, k, n, b_layout):
     assert_parity(y32, cpu_gemm(a, b_cpu, bias, out_dtype=torch.float32), bf16=False, scale=k**0.5 * 4)
 
 
+@pytest.mark.parametrize("b_layout", ["nk", "kn"])
+def test_lm_head_m8192_n50257(ops, b_layout):
+    """The widest cell of the GEMM sweep, [8192, 768] x [768, 50257] in bf16 with fp32 logits: the
+    tied-head layout (t() view of [N, K], the tensor-core route with a ragged last column tile and
+    a padded output pitch) and a contiguous [K, N] weight (its 100514-byte row pitch cannot be
+    described to TMA, so AUTO must fall to the strided CUDA-core kernel, never to a wrong answer).
+    Rows from the first, a middle and the last row tile against the CPU oracle."""
+    m, k, n = 8192, 768, 50257
+    g = torch.Generator(device="cuda").manual_seed(81)
+    a = torch.randn((m, k), generator=g, device="cuda").bfloat16()
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.1).bfloat16()
+    b_gpu = w.t() if b_layout == "nk" else w.t().contiguous()
+    y = ops.gemm(a, b_gpu, None, None, 1.0, 1.0, 0, torch.float32)
+    assert y.shape == (m, n) and y.dtype == torch.float32
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, 4095, 4096, 8063, 8064, 8191])
+    want = a[rows.cuda()].float().cpu() @ w.float().cpu().t()
+    assert_parity(y[rows.cuda()], want, bf16=False, scale=k**0.5 * 0.4)
+    # bf16 output of the same product (the aten.mm contract for bf16 operands)
+    yb = ops.gemm(a[:512], b_gpu)
+    assert yb.dtype == torch.bfloat16
+    assert_parity(yb, (a[:512].float().cpu() @ w.float().cpu().t()), bf16=True)
+
+
+@pytest.mark.parametrize("m", [1, 16, 64])
+@pytest.mark.parametrize("k,n", [(768, 2304), (768, 768), (768, 3072), (3072, 768), (768, 50257)])
+@pytest.mark.parametrize("b_layout", ["nk", "kn"])
+def test_decode_shapes_of_the_sweep(ops, m, k, n, b_layout):
+    """M in {1, 16, 64} on every (K, N) of the GEMM sweep, both weight layouts, bias, route AUTO
+    (whatever it resolves to: split-K, plain tensor-core or the strided kernel), bf16 and fp32
+    results against the CPU oracle."""
+    a = gen((m, k), torch.bfloat16, 90)
+    bias = gen((n,), torch.bfloat16, 92, 0.02)
+    if b_layout == "nk":
+        w = gen((n, k), torch.bfloat16, 91, 0.1)
+        b_cpu, b_gpu = w.t(), w.cuda().t()
+    else:
+        b_cpu = gen((k, n), torch.bfloat16, 91, 0.1)
+        b_gpu = b_cpu.cuda()
+    want = a.float() @ b_cpu.float() + bias.float()
+    y32 = ops.gemm(a.cuda(), b_gpu, bias.cuda(), None, 1.0, 1.0, 0, torch.float32)
+    assert_parity(y32, want, bf16=False)
+    y16 = ops.gemm(a.cuda(), b_gpu, bias.cuda())
+    assert y16.dtype == torch.bfloat16 and y16.shape == (m, n)
+    assert_parity(y16, want, bf16=True)
+
+
 @pytest.mark.parametrize("m,n,k", [(1000, 50257, 768), (129, 200, 72), (33, 72, 200), (128, 256, 64), (300, 1000, 1600)])
 def test_tcgen05_ragged(ops, m, n, k):
     a = gen((m, k), torch.bfloat16, 13)
@@ -279,11 +325,65 @@ def test_no_device_timeout_recorded():
     assert native.device_status() == 0
 
 
-@pytest.mark.parametrize("level,rtol", [("high", 1e-4), ("medium", 2e-2)])
-def test_fp32_matmul_precision_levels_use_the_tensor_cores(level, rtol):
-    """torch.set_float32_matmul_precision("high") runs an fp32 mm / addmm as three bf16
-    tensor-core GEMMs (two-term bf16 split of each operand), "medium" as one; "high" must still
-    meet the fp32 tolerance of the default exact route."""
+ROUTE_SPLIT3 = 4
+
+
+@pytest.mark.parametrize("k,n", KN)
+@pytest.mark.parametrize("b_layout", ["nk", "kn"])
+def test_fp32_m8192_split_precision_route(ops, k, n, b_layout):
+    """fp32 operands at M = 8192 on the four (K, N) of the sweep, both weight layouts, bias: AUTO
+    resolves to the split-precision tensor-core route (operands as bf16 hi / lo halves, three products
+    accumulated in fp32 by one tensor-core launch) and must meet the fp32 bar, 1e-4 relative,
+    against an fp64 oracle; the exact CUDA-core route must agree with it to the same bar."""
+    import ctypes
+
+    from torch_mojo_backend import native
+
+    m = 8192
+    g = torch.Generator(device="cuda").manual_seed(100)
+    a = torch.randn((m, k), generator=g, device="cuda")
+    bias = torch.randn((n,), generator=g, device="cuda") * 0.02
+    w = torch.randn((n, k) if b_layout == "nk" else (k, n), generator=g, device="cuda")
+    b = w.t() if b_layout == "nk" else w
+    c = torch.empty((m, n), device="cuda")
+    args = ops.fill_gemm_args(a, b, bias, None, c, 1.0, 1.0, 0, 0)
+    assert native.lib().b200_gemm_route(ctypes.byref(args)) == ROUTE_SPLIT3
+    assert native.lib().b200_gemm_workspace_bytes(ctypes.byref(args)) >= (m + n) * 2 * k * 2
+    y = ops.gemm(a, b, bias)
+    assert y.dtype == torch.float32
+    want = torch.addmm(bias.double(), a.double(), b.double())
+    scale = want.abs().max().item()
+    err = (y.double() - want).abs().max().item()
+    assert err <= 1e-4 * scale, f"max|diff| {err:.3e} at scale {scale:.3e}"
+    rows = slice(0, 512)
+    exact = ops.gemm(a[rows], b, bias, None, 1.0, 1.0, 0, None, ROUTE_SIMT)
+    assert (exact.double() - want[rows]).abs().max().item() <= 1e-4 * scale
+    # a missing workspace is an error, not a silent reroute
+    assert native.lib().b200_gemm(ctypes.byref(args), None, 0, None) == -4
+
+
+@pytest.mark.parametrize("m,n,k", [(257, 130, 75), (1000, 1000, 333), (300, 50257, 768), (4096, 33, 4096)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False)])
+def test_fp32_split_precision_odd_shapes_and_layouts(ops, m, n, k, ta, tb):
+    """Forced split-precision route on ragged extents (K not a multiple of the 64-element k-block,
+    unaligned pitches, the 50257-column logits) and on transposed views of either operand, with
+    alpha / beta / gelu / residual in the epilogue."""
+    a = gen((k, m) if ta else (m, k), torch.float32, 110)
+    b = gen((n, k) if tb else (k, n), torch.float32, 111, 0.1)
+    a_cpu, a_gpu = (a.t(), a.cuda().t()) if ta else (a, a.cuda())
+    b_cpu, b_gpu = (b.t(), b.cuda().t()) if tb else (b, b.cuda())
+    bias, res = gen((n,), torch.float32, 112), gen((m, n), torch.float32, 113)
+    y = ops.gemm(a_gpu, b_gpu, bias.cuda(), res.cuda(), 0.5, 2.0, 1, None, ROUTE_SPLIT3)
+    acc = 0.5 * (a_cpu.double() @ b_cpu.double()) + 2.0 * bias.double()
+    want = torch.nn.functional.gelu(acc, approximate="tanh") + res.double()
+    assert_parity(y, want.float(), bf16=False)
+
+
+@pytest.mark.parametrize("level,rtol", [("highest", 1e-4), ("high", 1e-4), ("medium", 2e-2)])
+def test_fp32_matmul_precision_levels(level, rtol):
+    """fp32 mm / addmm through the lowering: "highest" and "high" meet the fp32 bar (on the tensor
+    cores, in split precision, for a product of this size), "medium" rounds the operands to bf16;
+    one GEMM call either way."""
     from torch_mojo_backend import aten_functions as af
     from torch_mojo_backend import native
 
@@ -299,7 +399,7 @@ def test_fp32_matmul_precision_levels_use_the_tensor_cores(level, rtol):
         got_mm = af.aten_mm(a.cuda(), w.cuda().t())
     finally:
         torch.set_float32_matmul_precision(old)
-    assert launches == (3 if level == "high" else 1)
+    assert launches == 1
     assert got.dtype == torch.float32
     scale = want.abs().max().item()
     assert (got.cpu() - want).abs().max().item() <= rtol * scale

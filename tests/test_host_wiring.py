@@ -101,3 +101,26 @@ def test_meta_implementations_give_traced_shapes():
         assert o.shape == q.shape and o.stride() == (320, 8, 32, 1) and lse.shape == (2, 4, 10)
         with pytest.raises(RuntimeError, match="cannot be multiplied"):
             ops.gemm(torch.empty(3, 4, device="cuda"), torch.empty(5, 6, device="cuda"))
+
+
+def test_gemm_fake_output_has_the_real_ops_strides():
+    """The Meta implementation (what FakeTensor tracing sees) must describe the tensor the CUDA
+    implementation returns, padded row pitch of a wide unaligned output included."""
+    a = torch.empty(16, 64, dtype=torch.bfloat16, device="meta")
+    w = torch.empty(64, 50257, dtype=torch.bfloat16, device="meta")
+    y = ops.gemm(a, w, None, None, 1.0, 1.0, 0, torch.float32)
+    assert tuple(y.shape) == (16, 50257) and y.stride() == (50264, 1)
+    small = ops.gemm(a, torch.empty(64, 1000, dtype=torch.bfloat16, device="meta"))
+    assert small.stride() == (1000, 1)
+    one_row = ops.gemm(a[:1], w)
+    assert one_row.stride() == (50257, 1)
+
+
+def test_view_lowering_copies_when_the_runtime_layout_is_not_the_traced_one():
+    from torch_mojo_backend import aten_functions as af
+
+    padded = torch.arange(4 * 8, dtype=torch.float32).reshape(4, 8)[:, :5]  # row pitch 8, 5 columns
+    flat = af.aten_view(padded, [-1])
+    assert flat.shape == (20,) and torch.equal(flat, padded.reshape(-1))
+    split = af.aten__unsafe_view(padded, [2, 2, 5])  # splitting the row dim stays a view
+    assert split.data_ptr() == padded.data_ptr()

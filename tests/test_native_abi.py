@@ -89,3 +89,30 @@ def test_missing_library_fails_loudly(native, monkeypatch, tmp_path):
     # the failure is latched: later calls raise the same error instead of retrying silently
     with pytest.raises(native.NativeLibraryError):
         native.lib()
+
+
+@pytest.mark.gpu
+def test_bounded_wait_runs_out_and_reports_a_status(native):
+    """A device-side wait whose limit runs out (a barrier nothing signals, 100 us) ends the kernel
+    with a status bit instead of hanging: the host reads B200_ERR_DEVICE_TIMEOUT once, the word is
+    cleared by the read, and the next kernel on the device runs and is correct."""
+    import torch
+
+    from torch_mojo_backend import ops
+
+    lib = native.lib()
+    assert native.device_status() == 0
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.b200_debug_wait_timeout(0, stream) == -1          # limit validated on the host
+    assert lib.b200_debug_wait_timeout(10**9, stream) == -1
+    assert lib.b200_debug_wait_timeout(100_000, stream) == 0
+    torch.cuda.synchronize()  # returns: the kernel gave up by itself
+    word = ctypes.c_uint32(0)
+    assert lib.b200_device_status(ctypes.byref(word)) == native.ERR_DEVICE_TIMEOUT
+    assert word.value == native.STATUS_TEST_TIMEOUT
+    assert lib.b200_device_status(ctypes.byref(word)) == 0 and word.value == 0  # cleared by the first read
+    a = torch.randn((256, 128), device="cuda").bfloat16()
+    w = torch.randn((192, 128), device="cuda").bfloat16()
+    y = ops.gemm(a, w.t(), None, None, 1.0, 1.0, 0, torch.float32)
+    torch.testing.assert_close(y.cpu(), a.float().cpu() @ w.float().cpu().t(), rtol=1e-4, atol=1e-3)
+    assert native.device_status() == 0

@@ -41,15 +41,58 @@ def test_static_scratch_entry_matches_workspace_entry(m, k, n):
         native.check("gemm", lib.b200_gemm(ctypes.byref(g_ws), workspace.data_ptr(), need, stream))
 
         g_static = ops.fill_gemm_args(a, b, bias, res, got, 1.0, 1.0, native.EPILOGUE_GELU_TANH, native.ROUTE_AUTO)
+        torch.cuda.synchronize()
         reserved_before = torch.cuda.memory_reserved()
+        free_before, _ = torch.cuda.mem_get_info()
         native.check("gemm_small_m_static", lib.b200_gemm_small_m_static(ctypes.byref(g_static), stream))
         torch.cuda.synchronize()
+        # torch's allocator did not grow, and neither did the device's own count of used memory (a
+        # cudaMalloc inside the library would not show in the first figure, it does in the second);
+        # the first call's one-time lookup of the static array's address allocates nothing either
         assert torch.cuda.memory_reserved() == reserved_before
+        assert torch.cuda.mem_get_info()[0] >= free_before
         # same kernels, same fixed reduction order: the two entry points agree bit for bit, which is
         # inside the 1e-4 fp32 tolerance the other GEMM tests use
         assert torch.equal(got, want), f"call {call}: max|diff| {(got - want).abs().max().item():.3e}"
         ref = torch.nn.functional.gelu(a.float() @ b.float() + bias.float(), approximate="tanh") + res
         torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4 * ref.abs().max().item())
+
+
+def test_static_scratch_entry_validates_like_the_workspace_entry():
+    """Same host-side checks as b200_gemm, before any launch: a misaligned output or residual
+    pointer, a row pitch shorter than a row and a bad enum are refused with a status."""
+    from torch_mojo_backend import native, ops
+
+    lib = native.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    a, b, bias, res = _problem(16, 6400, 1600, seed=9)
+    out = torch.empty((16, 1600), dtype=torch.float32, device="cuda")
+    before = native.launch_count
+
+    def args():
+        return ops.fill_gemm_args(a, b, bias, res, out, 1.0, 1.0, 0, 0)
+
+    g = args()
+    g.c = out.data_ptr() + 2  # fp32 output at a 2-byte offset
+    assert lib.b200_gemm_small_m_static(ctypes.byref(g), stream) == -3
+    assert lib.b200_gemm(ctypes.byref(g), None, 0, stream) == -3
+    g = args()
+    g.residual = res.data_ptr() + 1
+    assert lib.b200_gemm_small_m_static(ctypes.byref(g), stream) == -3
+    g = args()
+    g.bias = bias.data_ptr() + 1
+    assert lib.b200_gemm_small_m_static(ctypes.byref(g), stream) == -3
+    g = args()
+    g.c_row_stride = 1599  # rows would overlap
+    assert lib.b200_gemm_small_m_static(ctypes.byref(g), stream) == -1
+    g = args()
+    g.route = 17
+    assert lib.b200_gemm_small_m_static(ctypes.byref(g), stream) == -1
+    g = args()
+    g.epilogue = 9
+    assert lib.b200_gemm_small_m_static(ctypes.byref(g), stream) == -1
+    torch.cuda.synchronize()
+    assert native.launch_count == before and native.device_status() == 0
 
 
 def test_static_scratch_entry_refuses_what_it_cannot_hold():

@@ -2,6 +2,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200 {
 
@@ -47,7 +48,40 @@ int sm_count() {
   return cached[dev];
 }
 
+namespace {
+
+// One warp waits on an mbarrier that nothing ever signals, with the caller's limit, and then
+// leaves the way the GEMM and attention kernels leave when one of their waits runs out: abort
+// flag, status bit, return.
+__global__ void wait_timeout_kernel(unsigned long long limit_ns, unsigned int* status) {
+  __shared__ __align__(8) unsigned long long barrier_storage;
+  __shared__ uint32_t abort_flag_storage;
+  volatile uint32_t* abort_flag = &abort_flag_storage;
+  const uint32_t bar = ptx::smem_u32(&barrier_storage);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar, 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  const bool arrived = ptx::mbar_wait_limited(bar, 0, abort_flag, limit_ns);
+  __syncthreads();
+  if (threadIdx.x == 0 && (!arrived || *abort_flag != 0)) atomicOr(status, STATUS_TEST_TIMEOUT);
+}
+
+}  // namespace
 }  // namespace b200
+
+extern "C" B200_API int32_t b200_debug_wait_timeout(uint64_t limit_ns, b200_stream_t stream_) {
+  using namespace b200;
+  B200_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ull, B200_ERR_INVALID_ARG,
+               "debug_wait_timeout: limit must be in (0, 100 ms]");
+  unsigned int* status = device_status_ptr();
+  B200_REQUIRE(status != nullptr, B200_ERR_CUDA, "debug_wait_timeout: device status word unavailable");
+  wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(limit_ns, status);
+  B200_CHECK_LAUNCH("debug_wait_timeout");
+  return B200_OK;
+}
 
 extern "C" B200_API int32_t b200_abi_version(void) { return B200_ABI_VERSION; }
 

@@ -45,6 +45,8 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 unsigned int* device_status_ptr();
 constexpr unsigned int STATUS_GEMM_TIMEOUT = 1u << 0;
 constexpr unsigned int STATUS_SDPA_TIMEOUT = 1u << 1;
+constexpr unsigned int STATUS_TEST_TIMEOUT = 1u << 2;  // b200_debug_wait_timeout
+constexpr unsigned int STATUS_INDEX_OUT_OF_RANGE = 1u << 3;  // an embedding index outside its table
 
 int sm_count();  // SM count of the current device (cached per device)
 

@@ -160,15 +160,12 @@ int32_t launch_gemm_skinny(const b200_gemm_args& g, void* scratch, size_t scratc
 extern "C" B200_API int32_t b200_gemm_small_m_static(const b200_gemm_args* args, b200_stream_t stream_) {
   using namespace b200;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  B200_REQUIRE(args != nullptr, B200_ERR_INVALID_ARG, "gemm_small_m_static: null args");
+  // the same checks as b200_gemm, before anything is launched
+  const int32_t st = validate_gemm_args(args);
+  if (st != B200_OK) return st;
   const b200_gemm_args& g = *args;
-  B200_REQUIRE(g.m > 0 && g.n > 0 && g.k > 0 && g.batch == 1 && g.a != nullptr && g.b != nullptr && g.c != nullptr,
-               B200_ERR_INVALID_ARG, "gemm_small_m_static: needs one non-empty problem with non-null a, b, c");
-  B200_REQUIRE(valid_dtype(g.in_dtype) && valid_dtype(g.out_dtype) && (g.bias == nullptr || valid_dtype(g.bias_dtype)) &&
-                   (g.residual == nullptr || valid_dtype(g.residual_dtype)),
-               B200_ERR_INVALID_ARG, "gemm_small_m_static: bad dtype enum");
-  B200_REQUIRE(g.epilogue >= B200_EPILOGUE_NONE && g.epilogue <= B200_EPILOGUE_GELU_ERF, B200_ERR_INVALID_ARG,
-               "gemm_small_m_static: bad epilogue enum");
+  B200_REQUIRE(g.m > 0 && g.n > 0 && g.k > 0 && g.batch == 1, B200_ERR_INVALID_ARG,
+               "gemm_small_m_static: needs one non-empty problem (batch == 1)");
   const char* why = gemm_skinny_ineligible(g);
   B200_REQUIRE(why == nullptr, B200_ERR_UNSUPPORTED,
                "gemm_small_m_static: these arguments do not take the split-K route (%s); use b200_gemm", why);

@@ -75,6 +75,11 @@ struct Params {
   int64_t num_tiles;
   unsigned int* status;
   int32_t fast_ok;  // pointers/pitches allow the branch-free vector epilogue on interior tiles
+  // The K loop runs k_parts passes over K; pass i reads A at k offset a_part_off[i] and B at k offset
+  // b_part_off[i] (elements). One pass with offsets 0 is a plain GEMM; three passes over operands
+  // stored as [hi | lo] halves are the split-precision product a_hi b_lo + a_lo b_hi + a_hi b_hi.
+  int32_t k_parts;
+  int32_t a_part_off[3], b_part_off[3];
 };
 
 __device__ __forceinline__ float act(float v, int32_t epilogue) {
@@ -228,7 +233,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  const int64_t num_kb = (p.K + BK - 1) / BK;
+  const int64_t kb_per_part = (p.K + BK - 1) / BK;
+  const int64_t num_kb = kb_per_part * p.k_parts;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -243,7 +249,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int32_t m0 = mt * kTileM + (int32_t)rank * BM, n0 = nt * BN + (int32_t)rank * C_::B_ROWS * (PAIR ? 1 : 0);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait_relaxed(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
-          const int32_t k0 = (int32_t)(kb * BK);
+          const int32_t part = (int32_t)(kb / kb_per_part);
+          const int32_t k_in_part = (int32_t)((kb - part * kb_per_part) * BK);
+          const int32_t k0 = k_in_part + p.a_part_off[part], k0b = k_in_part + p.b_part_off[part];
           if (PAIR) {
             // Both CTAs' copies are counted on the even CTA's barrier, which expects the bytes of
             // both. (The peer's bytes may land before the expectation is posted; the phase cannot
@@ -251,20 +259,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t bar = ptx::mapa(full_bar(s), 0);
             if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + C_::B_STAGE_BYTES));
             ptx::tma_load_3d_pair(a_base + s * A_STAGE_BYTES, &tmap_a, bar, k0, m0, (int32_t)b);
-            ptx::tma_load_3d_pair(b_base + s * C_::B_STAGE_BYTES, &tmap_b, bar, k0, n0, (int32_t)b);
+            ptx::tma_load_3d_pair(b_base + s * C_::B_STAGE_BYTES, &tmap_b, bar, k0b, n0, (int32_t)b);
             if (++s == kStages) { s = 0; phase ^= 1; }
             continue;
           }
           ptx::mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + C_::B_STAGE_BYTES);
           ptx::tma_load_3d(a_base + s * A_STAGE_BYTES, &tmap_a, full_bar(s), k0, m0, (int32_t)b);
           if (!B_MN_MAJOR) {
-            ptx::tma_load_3d(b_base + s * C_::B_STAGE_BYTES, &tmap_b, full_bar(s), k0, n0, (int32_t)b);
+            ptx::tma_load_3d(b_base + s * C_::B_STAGE_BYTES, &tmap_b, full_bar(s), k0b, n0, (int32_t)b);
           } else {
             // B stored [K, N]: BN/64 boxes of 64(n) x 64(k), each one swizzle atom wide in n.
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
               ptx::tma_load_3d(b_base + s * C_::B_STAGE_BYTES + j * (64 * BK * 2), &tmap_b,
-                               full_bar(s), n0 + j * 64, k0, (int32_t)b);
+                               full_bar(s), n0 + j * 64, k0b, (int32_t)b);
           }
           if (++s == kStages) { s = 0; phase ^= 1; }
         }
@@ -543,6 +551,8 @@ int32_t fill_params(const b200_gemm_args& g, Params& p, int tile_m, int tile_n, 
   p.tiles_m = (int32_t)((g.m + tile_m - 1) / tile_m);
   p.tiles_n = (int32_t)((g.n + tile_n - 1) / tile_n);
   p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * g.batch;
+  p.k_parts = 1;
+  for (int i = 0; i < 3; ++i) { p.a_part_off[i] = 0; p.b_part_off[i] = 0; }
   p.status = device_status_ptr();
   B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "gemm(tcgen05): device status word unavailable");
   {
@@ -557,12 +567,20 @@ int32_t fill_params(const b200_gemm_args& g, Params& p, int tile_m, int tile_n, 
   return B200_OK;
 }
 
+// Copies a multi-pass K schedule into the kernel parameters (after fill_params set the defaults).
+void apply_k_parts(Params& p, const GemmKParts* kp) {
+  if (kp == nullptr) return;
+  p.k_parts = kp->parts;
+  for (int i = 0; i < 3; ++i) { p.a_part_off[i] = kp->a_off[i]; p.b_part_off[i] = kp->b_off[i]; }
+}
+
 template <int BN, bool B_MN_MAJOR, typename Tout>
-int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
+int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream, const GemmKParts* kp) {
   using C_ = Cfg<BN>;
   CUtensorMap tmap_a, tmap_b;
+  const uint64_t k_extent = kp != nullptr ? (uint64_t)kp->k_storage : (uint64_t)g.k;  // K extent of the stored operands
   {
-    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch};
+    const uint64_t dims[3] = {k_extent, (uint64_t)g.m, (uint64_t)g.batch};
     const uint64_t strides[2] = {(uint64_t)g.a_row_stride * 2,
                                  (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_row_stride * g.m) * 2};
     const uint32_t box[3] = {BK, BM, 1};
@@ -571,7 +589,7 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
   }
   if (!B_MN_MAJOR) {
     // B^T is [n, k] with row pitch b_col_stride.
-    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.batch};
+    const uint64_t dims[3] = {k_extent, (uint64_t)g.n, (uint64_t)g.batch};
     const uint64_t strides[2] = {(uint64_t)g.b_col_stride * 2,
                                  (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_col_stride * g.n) * 2};
     const uint32_t box[3] = {BK, BN, 1};
@@ -579,9 +597,9 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
     if (st != B200_OK) return st;
   } else {
     // B is [k, n] with row pitch b_row_stride.
-    const uint64_t dims[3] = {(uint64_t)g.n, (uint64_t)g.k, (uint64_t)g.batch};
+    const uint64_t dims[3] = {(uint64_t)g.n, k_extent, (uint64_t)g.batch};
     const uint64_t strides[2] = {(uint64_t)g.b_row_stride * 2,
-                                 (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_row_stride * g.k) * 2};
+                                 (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_row_stride * k_extent) * 2};
     const uint32_t box[3] = {64, BK, 1};
     int32_t st = encode_tensor_map(&tmap_b, B200_BF16, 3, g.b, dims, strides, box, true);
     if (st != B200_OK) return st;
@@ -590,6 +608,7 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
   {
     int32_t st = fill_params(g, p, BM, BN, sizeof(Tout));
     if (st != B200_OK) return st;
+    apply_k_parts(p, kp);
   }
 
   auto kernel = gemm_tcgen05_kernel<BN, B_MN_MAJOR, Tout>;
@@ -611,12 +630,13 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream) {
 
 // The CTA-pair form: clusters of two CTAs, each pair walking 256 x BN tiles.
 template <int BN, typename Tout>
-int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream) {
+int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream, const GemmKParts* kp) {
   using C_ = Cfg<BN, true>;
   static_assert(C_::kSmemBytes <= 227 * 1024, "pair configuration exceeds the shared memory of an SM");
   CUtensorMap tmap_a, tmap_b;
+  const uint64_t k_extent = kp != nullptr ? (uint64_t)kp->k_storage : (uint64_t)g.k;
   {
-    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch};
+    const uint64_t dims[3] = {k_extent, (uint64_t)g.m, (uint64_t)g.batch};
     const uint64_t strides[2] = {(uint64_t)g.a_row_stride * 2,
                                  (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_row_stride * g.m) * 2};
     const uint32_t box[3] = {BK, BM, 1};
@@ -624,7 +644,7 @@ int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream) {
     if (st != B200_OK) return st;
   }
   {
-    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.batch};
+    const uint64_t dims[3] = {k_extent, (uint64_t)g.n, (uint64_t)g.batch};
     const uint64_t strides[2] = {(uint64_t)g.b_col_stride * 2,
                                  (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_col_stride * g.n) * 2};
     const uint32_t box[3] = {BK, (uint32_t)C_::B_ROWS, 1};
@@ -634,6 +654,7 @@ int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream) {
   Params p;
   int32_t st = fill_params(g, p, 2 * BM, BN, sizeof(Tout));
   if (st != B200_OK) return st;
+  apply_k_parts(p, kp);
 
   auto kernel = gemm_tcgen05_kernel<BN, false, Tout, true>;
   static thread_local bool attr_set[64] = {false};
@@ -666,19 +687,39 @@ int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream) {
   return B200_OK;
 }
 
+// Tuning switches, read from the environment on every call only while B200_GEMM_ENV_LIVE is set (the
+// tests flip them between calls); otherwise once, at the first GEMM.
+struct Tuning {
+  int pair_mode;  // B200_GEMM_PAIR: -1 unset, 0 off, 1 forced wherever eligible
+  int tile_n;     // B200_GEMM_TILE_N: 0 unset, else 128 | 192 | 256
+};
+
+Tuning read_tuning() {
+  Tuning t = {-1, 0};
+  if (const char* v = getenv("B200_GEMM_PAIR")) t.pair_mode = atoi(v);
+  if (const char* v = getenv("B200_GEMM_TILE_N")) {
+    const int n = atoi(v);
+    if (n == 128 || n == 192 || n == 256) t.tile_n = n;
+  }
+  return t;
+}
+
+Tuning tuning() {
+  static const bool live = getenv("B200_GEMM_ENV_LIVE") != nullptr;
+  static const Tuning at_load = read_tuning();
+  return live ? read_tuning() : at_load;
+}
+
 // Whether the CTA-pair kernel is used, and with which tile width (0 = not used).
 // B200_GEMM_PAIR=0 turns it off, =1 forces it wherever it is eligible (tuning and tests).
 int pick_pair_bn(const b200_gemm_args& g) {
   if (!b_is_k_major(g)) return 0;
-  int mode = -1;
-  if (const char* v = getenv("B200_GEMM_PAIR")) mode = atoi(v);
+  const Tuning t = tuning();
+  const int mode = t.pair_mode;
   if (mode == 0) return 0;
   // Small problems have too few 256-row tiles to fill 74 pairs; they keep the single-CTA kernel.
   if (mode != 1 && (g.m < 1024 || g.n < 512)) return 0;
-  if (const char* forced = getenv("B200_GEMM_TILE_N")) {
-    const int v = atoi(forced);
-    if (v == 128 || v == 192 || v == 256) return v;
-  }
+  if (t.tile_n != 0) return t.tile_n;
   const int64_t pairs = sm_count() / 2;
   // Time of a tile ~ (BN + 270) columns' worth: the measured fixed share per tile (issue loop,
   // accumulator hand-off, epilogue) is about as large as the width-proportional part, so wide
@@ -697,10 +738,7 @@ int pick_pair_bn(const b200_gemm_args& g) {
 // proportional to BN plus a fixed epilogue/prologue share).
 int pick_bn(const b200_gemm_args& g) {
   // B200_GEMM_TILE_N=128|192|256 pins the tile width (tuning and tests).
-  if (const char* forced = getenv("B200_GEMM_TILE_N")) {
-    const int v = atoi(forced);
-    if (v == 128 || v == 192 || v == 256) return v;
-  }
+  if (tuning().tile_n != 0) return tuning().tile_n;
   if (g.n <= 128) return 128;
   const int sms = sm_count();
   // Per-tile cost: the main loop is proportional to BN, but narrower tiles need more operand
@@ -739,11 +777,11 @@ const char* gemm_tcgen05_ineligible(const b200_gemm_args& g) {
   return nullptr;
 }
 
-int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream) {
+int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream, const GemmKParts* kp) {
   const bool mn = !b_is_k_major(g);
   const bool f32 = g.out_dtype == B200_F32;
   if (const int pbn = pick_pair_bn(g)) {
-#define PAIR_LAUNCH(BN_) (f32 ? launch_pair_cfg<BN_, float>(g, stream) : launch_pair_cfg<BN_, __nv_bfloat16>(g, stream))
+#define PAIR_LAUNCH(BN_) (f32 ? launch_pair_cfg<BN_, float>(g, stream, kp) : launch_pair_cfg<BN_, __nv_bfloat16>(g, stream, kp))
     if (pbn == 256) return PAIR_LAUNCH(256);
     if (pbn == 192) return PAIR_LAUNCH(192);
     return PAIR_LAUNCH(128);
@@ -751,7 +789,7 @@ int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream) {
   }
   const int bn = pick_bn(g);
 #define TC_LAUNCH(BN_, MN_)                                                   \
-  (f32 ? launch_cfg<BN_, MN_, float>(g, stream) : launch_cfg<BN_, MN_, __nv_bfloat16>(g, stream))
+  (f32 ? launch_cfg<BN_, MN_, float>(g, stream, kp) : launch_cfg<BN_, MN_, __nv_bfloat16>(g, stream, kp))
   if (bn == 256) return mn ? TC_LAUNCH(256, true) : TC_LAUNCH(256, false);
   if (bn == 192) return mn ? TC_LAUNCH(192, true) : TC_LAUNCH(192, false);
   return mn ? TC_LAUNCH(128, true) : TC_LAUNCH(128, false);

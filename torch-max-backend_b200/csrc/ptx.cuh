@@ -74,8 +74,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // up, raises the abort flag for its CTA and returns through the normal teardown.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-// Bounded mbarrier wait. Returns false when the CTA-wide abort flag is (or becomes) set.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// Bounded mbarrier wait with an explicit limit. Returns false when the CTA-wide abort flag is (or
+// becomes) set; the thread whose wait ran out sets it.
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint64_t limit_ns) {
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -84,13 +86,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }
     }
   }
   return true;
+}
+
+// Bounded mbarrier wait with the library-wide limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, kWaitLimitNs);
 }
 
 // Same bound, for waits that are not latency critical (a producer waiting for a free slot):

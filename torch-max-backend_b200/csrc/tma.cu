@@ -1,5 +1,6 @@
 #include "tma.cuh"
 
+#include <cstring>
 #include <mutex>
 
 namespace b200 {
@@ -23,6 +24,36 @@ EncodeTiledFn resolve_encoder() {
   return fn;
 }
 
+// Encoded maps are cached: the driver call costs microseconds, which is a visible share of a
+// decode-shaped launch, and a model replays the same few (pointer, shape) combinations for ever.
+// The key is everything the encoder sees; a map is a pure function of it, so a stale entry cannot
+// exist (a buffer that is freed and re-allocated at the same address with the same shape encodes
+// to the same map). Direct-mapped, behind one mutex (the lookup is a 100-byte compare).
+struct MapKey {
+  const void* base;
+  uint64_t dims[5];
+  uint64_t strides[4];
+  uint32_t box[5];
+  int32_t dtype, rank, swizzle, device;
+};
+
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+
+constexpr int kMapCacheSlots = 1024;
+MapSlot g_map_cache[kMapCacheSlots];
+std::mutex g_map_mutex;
+
+uint64_t hash_key(const MapKey& k) {
+  const unsigned char* p = reinterpret_cast<const unsigned char*>(&k);
+  uint64_t h = 1469598103934665603ull;  // FNV-1a
+  for (size_t i = 0; i < sizeof(MapKey); ++i) h = (h ^ p[i]) * 1099511628211ull;
+  return h;
+}
+
 }  // namespace
 
 int32_t encode_tensor_map(CUtensorMap* out, int32_t dtype, int rank, const void* base,
@@ -31,6 +62,26 @@ int32_t encode_tensor_map(CUtensorMap* out, int32_t dtype, int rank, const void*
   EncodeTiledFn fn = resolve_encoder();
   B200_REQUIRE(fn != nullptr, B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   B200_REQUIRE(rank >= 1 && rank <= 5, B200_ERR_INVALID_ARG, "tensor map rank %d", rank);
+  MapKey key;
+  memset(&key, 0, sizeof(key));  // padding and unused entries take part in the compare
+  key.base = base;
+  key.dtype = dtype; key.rank = rank; key.swizzle = swizzle_128b ? 1 : 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  key.device = dev;
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+    if (i + 1 < rank) key.strides[i] = strides_bytes[i];
+  }
+  MapSlot& slot = g_map_cache[hash_key(key) % kMapCacheSlots];
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (slot.used && memcmp(&slot.key, &key, sizeof(key)) == 0) {
+      *out = slot.map;
+      return B200_OK;
+    }
+  }
   cuuint64_t gdims[5];
   cuuint64_t gstrides[4];
   cuuint32_t gbox[5];
@@ -54,6 +105,12 @@ int32_t encode_tensor_map(CUtensorMap* out, int32_t dtype, int rank, const void*
               (unsigned long long)(rank > 1 ? dims[1] : 0),
               (unsigned long long)(rank > 2 ? dims[2] : 0), box[0], rank > 1 ? box[1] : 0,
               rank > 2 ? box[2] : 0);
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    slot.key = key;
+    slot.map = *out;
+    slot.used = true;
+  }
   return B200_OK;
 }
 

@@ -97,47 +97,45 @@ def _kernel_dtype(*tensors) -> bool:
     return all(t is None or native.supported_dtype(t.dtype) for t in tensors)
 
 
+def _require_kernel_dtype(op: str, *tensors) -> None:
+    """The ops this backend exists for have no second implementation: a floating-point dtype the
+    kernels do not take (float16, float64) is an error -- raised while the launch plan is built, so
+    the user sees a MojoCompilerError at compile time -- not a silent trip through a vendor library."""
+    for t in tensors:
+        if t is not None and t.dtype.is_floating_point and not native.supported_dtype(t.dtype):
+            raise NotImplementedError(
+                f"{op}: dtype {t.dtype} is not supported by the b200 kernels (float32 and bfloat16 are); "
+                "there is no library fallback"
+            )
+
+
 # ==============================================================================================
 # GEMM family
 # ==============================================================================================
 
 
-def _fp32_on_tensor_cores(a, b) -> str | None:
-    """"high" / "medium" when a 2-D fp32 product should run on the bf16 tensor cores, as
-    torch.set_float32_matmul_precision defines those levels ("high": each fp32 number treated as
-    the sum of two bfloat16 numbers; "medium": bfloat16 operands), else None. The default
-    ("highest") keeps the exact-fp32 CUDA-core kernel. Small products stay there too."""
-    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.dim() != 2 or b.dim() != 2:
-        return None
-    level = torch.get_float32_matmul_precision()
-    if level == "highest" or a.shape[0] * a.shape[1] * b.shape[1] < (1 << 24):
-        return None
-    return level
-
-
-def _fp32_split_gemm(level, a, b, bias, alpha, beta):
-    """alpha * a @ b + beta * bias for fp32 a, b on the bf16 tensor cores. With x = x_hi + x_lo
-    (x_hi = bf16(x), x_lo = bf16(x - x_hi)), a @ b ~= a_hi b_lo + a_lo b_hi + a_hi b_hi (the
-    dropped a_lo b_lo term is ~2^-16 of the product): three GEMMs that accumulate in fp32 through
-    the residual input of the epilogue, smallest terms first."""
-    a_hi, b_hi = a.bfloat16(), b.bfloat16()
-    if level == "medium":
-        return ops.gemm(a_hi, b_hi, bias, None, alpha, beta, 0, torch.float32)
-    a_lo = (a - a_hi.float()).bfloat16()
-    b_lo = (b - b_hi.float()).bfloat16()
-    c = ops.gemm(a_hi, b_lo, None, None, alpha, 1.0, 0, torch.float32)
-    c = ops.gemm(a_lo, b_hi, None, c, alpha, 1.0, 0, torch.float32)
-    return ops.gemm(a_hi, b_hi, bias, c, alpha, beta, 0, torch.float32)
+def _fp32_gemm(a, b, bias, alpha, beta):
+    """alpha * a @ b + beta * bias for 2-D fp32 operands, by torch.get_float32_matmul_precision():
+    "highest" and "high" take b200_gemm's own choice for fp32 -- all but small products run on the
+    tensor cores as three bf16 products of the operands' (hi, lo) halves accumulated in fp32 by one
+    launch (relative error ~2^-16, inside the 1e-4 bar of the fp32 configurations), small ones on
+    the exact CUDA-core kernel; "medium" rounds the operands to bf16 (one product).
+    TORCH_MOJO_BACKEND_EXACT_FP32=1 pins every fp32 product to the exact kernel."""
+    if os.environ.get("TORCH_MOJO_BACKEND_EXACT_FP32", "0").lower() in ("1", "true", "yes"):
+        return ops.gemm(a, b, bias, None, alpha, beta, 0, None, native.ROUTE_SIMT)
+    if torch.get_float32_matmul_precision() == "medium" and a.shape[0] * a.shape[1] * b.shape[1] >= (1 << 24):
+        return ops.gemm(a.bfloat16(), b.bfloat16(), bias, None, alpha, beta, 0, torch.float32)
+    return ops.gemm(a, b, bias, None, alpha, beta)
 
 
 # mm(Tensor self, Tensor mat2) -> Tensor
 @map_to(aten.mm)
 def aten_mm(x, y):
+    _require_kernel_dtype("aten.mm", x, y)
     if not _kernel_dtype(x, y):
-        return aten.mm.default(x, y)
-    level = _fp32_on_tensor_cores(x, y)
-    if level is not None:
-        return _fp32_split_gemm(level, x, y, None, 1.0, 1.0)
+        return aten.mm.default(x, y)  # integer matrices: shape glue, not a hot op
+    if x.dtype == torch.float32 and y.dtype == torch.float32 and x.dim() == 2 and y.dim() == 2:
+        return _fp32_gemm(x, y, None, 1.0, 1.0)
     return ops.gemm(x, y)
 
 
@@ -146,19 +144,22 @@ def aten_mm(x, y):
 def aten_addmm(input, mat1, mat2, *, beta=1.0, alpha=1.0):
     # beta * input + alpha * (mat1 @ mat2), input broadcast to [m, n]; the scaling and the add
     # happen in the GEMM epilogue on the fp32 accumulator.
+    _require_kernel_dtype("aten.addmm", input, mat1, mat2)
     if not _kernel_dtype(input, mat1, mat2):
-        return aten.addmm.default(input, mat1, mat2, beta=beta, alpha=alpha)
-    level = _fp32_on_tensor_cores(mat1, mat2)
-    if level is not None and input.dtype == torch.float32:
-        return _fp32_split_gemm(level, mat1, mat2, input, float(alpha), float(beta))
+        return aten.addmm.default(input, mat1, mat2, beta=beta, alpha=alpha)  # integer matrices: shape glue
+    if float(beta) == 0.0:
+        input = None  # torch ignores `input` altogether then (a NaN or inf in it must not propagate)
+    if mat1.dtype == torch.float32 and mat2.dtype == torch.float32 and mat1.dim() == 2 and mat2.dim() == 2:
+        return _fp32_gemm(mat1, mat2, input, float(alpha), float(beta))
     return ops.gemm(mat1, mat2, input, None, float(alpha), float(beta))
 
 
 # bmm(Tensor self, Tensor mat2) -> Tensor
 @map_to(aten.bmm)
 def aten_bmm(input, mat2):
+    _require_kernel_dtype("aten.bmm", input, mat2)
     if not _kernel_dtype(input, mat2):
-        return aten.bmm.default(input, mat2)
+        return aten.bmm.default(input, mat2)  # integer matrices: shape glue
     return ops.gemm(input, mat2)
 
 
@@ -183,8 +184,11 @@ def aten__softmax(self, dim: int, half_to_float: bool):
 # softmax.int(Tensor self, int dim, ScalarType? dtype=None) -> Tensor
 @map_to(aten.softmax)
 def aten_softmax(input, dim=-1, dtype=None):
-    if not _kernel_dtype(input) or (dtype is not None and dtype not in (torch.float32, input.dtype)):
-        return torch.softmax(input, dim, dtype=dtype)
+    _require_kernel_dtype("aten._softmax", input)
+    if not input.dtype.is_floating_point:
+        raise NotImplementedError(f"aten._softmax: dtype {input.dtype} is not a floating-point type")
+    if dtype is not None and dtype not in (torch.float32, input.dtype):
+        raise NotImplementedError(f"aten._softmax: output dtype {dtype} for input {input.dtype} is not supported")
     if input.dim() == 0:
         return torch.ones_like(input, dtype=dtype or input.dtype)
     if input.dtype == torch.float32:
@@ -198,8 +202,7 @@ def aten_softmax(input, dim=-1, dtype=None):
 #   -> (Tensor, Tensor, Tensor)
 @map_to(aten.native_layer_norm)
 def aten_native_layer_norm(input, normalized_shape, weight, bias, eps):
-    if not _kernel_dtype(input, weight, bias):
-        return aten.native_layer_norm.default(input, normalized_shape, weight, bias, eps)
+    _require_kernel_dtype("aten.native_layer_norm", input, weight, bias)
     k = len(normalized_shape)
     lead = input.shape[: input.dim() - k]
     cols = math.prod(normalized_shape)
@@ -232,8 +235,7 @@ def _traced_output_dtype(index: int, default: torch.dtype) -> torch.dtype:
 # gelu(Tensor self, *, str approximate='none') -> Tensor
 @map_to(aten.gelu)
 def aten_gelu(input, approximate="none"):
-    if not _kernel_dtype(input):
-        return aten.gelu.default(input, approximate=approximate)
+    _require_kernel_dtype("aten.gelu", input)
     return ops.gelu(input, approximate)
 
 
@@ -266,8 +268,10 @@ def _reduce_dims(input, dim, keepdim, op, dtype):
 @map_to(aten.sum)
 def aten_sum(input, dim=None, keepdim=False, *, dtype=None):
     out_dtype = dtype or input.dtype
+    _require_kernel_dtype("aten.sum", input)
     if not _kernel_dtype(input) or not native.supported_dtype(out_dtype) or input.numel() == 0:
-        # Integer/bool sums (promoted to int64 by torch) and empty reductions are shape glue.
+        # Integer/bool sums (promoted to int64 by torch: token counts, mask sizes) and empty
+        # reductions are shape glue, not a hot op.
         if dim is None:
             return torch.sum(input, dtype=dtype)
         return torch.sum(input, dim, keepdim, dtype=dtype)
@@ -279,7 +283,10 @@ def aten_sum(input, dim=None, keepdim=False, *, dtype=None):
 @map_to(aten.mean)
 def aten_mean(input, dim=None, keepdim=False, *, dtype=None):
     out_dtype = dtype or input.dtype
-    if not _kernel_dtype(input) or not native.supported_dtype(out_dtype) or input.numel() == 0:
+    _require_kernel_dtype("aten.mean", input)
+    if not native.supported_dtype(out_dtype):
+        raise NotImplementedError(f"aten.mean: output dtype {out_dtype} is not supported by the b200 kernels")
+    if input.numel() == 0:
         if dim is None:
             return torch.mean(input, dtype=dtype)
         return torch.mean(input, dim, keepdim, dtype=dtype)
@@ -289,8 +296,9 @@ def aten_mean(input, dim=None, keepdim=False, *, dtype=None):
 # amax(Tensor self, int[1] dim=[], bool keepdim=False) -> Tensor
 @map_to(aten.amax)
 def aten_amax(input, dim=[], keepdim=False):
+    _require_kernel_dtype("aten.amax", input)
     if not _kernel_dtype(input) or input.numel() == 0:
-        return torch.amax(input, dim, keepdim)
+        return torch.amax(input, dim, keepdim)  # integer maxima / empty reductions: shape glue
     return _reduce_dims(input, dim, keepdim, native.REDUCE_AMAX, input.dtype)
 
 
@@ -299,31 +307,31 @@ def aten_amax(input, dim=[], keepdim=False):
 # ==============================================================================================
 
 
-def _lse_as_traced(lse, index=1):
-    """The log-sum-exp output in the shape the traced graph recorded for this overload
-    ([B, H, T] for flash, [B, H, T, 1] for cuDNN, [B, H, 0] for efficient attention without
-    compute_log_sumexp)."""
-    node = CURRENT_FX_NODE.get()
-    val = node.meta.get("val") if node is not None else None
-    if not isinstance(val, (tuple, list)) or index >= len(val) or not isinstance(val[index], torch.Tensor):
-        return lse
-    want = tuple(val[index].shape)
-    if want == tuple(lse.shape):
-        return lse
-    if all(isinstance(d, int) for d in want) and math.prod(want) == lse.numel():
-        return lse.reshape(want)
-    return lse.new_empty(want)
-
-
-def _sdpa_kernel(query, key, value, is_causal, scale):
-    """[B, H, T, D] attention through the kernel; 3-D inputs are treated as one batch."""
-    squeeze = query.dim() == 3
-    if squeeze:
-        query, key, value = query.unsqueeze(0), key.unsqueeze(0), value.unsqueeze(0)
-    if key.shape[1] != query.shape[1]:
+def _repeat_kv_heads(query, key, value):
+    """Grouped-query attention: every K/V head serves `rep` consecutive query heads."""
+    if key.dim() == 4 and key.shape[1] != query.shape[1]:
         rep = query.shape[1] // key.shape[1]
         key = key.repeat_interleave(rep, dim=1)
         value = value.repeat_interleave(rep, dim=1)
+    return key, value
+
+
+def _kernel_takes_attention(query, key, value) -> bool:
+    """Whether b200::sdpa has a kernel for these operands (fp32 / bf16, head_dim <= 128); anything
+    else is computed as GEMM -> softmax -> GEMM by `_sdpa_math`."""
+    return _kernel_dtype(query, key, value) and query.shape[-1] <= 128 and query.dim() in (3, 4)
+
+
+def _sdpa_kernel(query, key, value, is_causal, scale):
+    """[B, H, T, D] attention through the kernel; 3-D inputs are treated as one batch.
+    Returns (out, natural-log LSE [B, H, T])."""
+    _require_kernel_dtype("scaled_dot_product_attention", query, key, value)
+    if not _kernel_takes_attention(query, key, value):
+        return _sdpa_math(query, key, value, None, is_causal, scale, want_lse=True)
+    squeeze = query.dim() == 3
+    if squeeze:
+        query, key, value = query.unsqueeze(0), key.unsqueeze(0), value.unsqueeze(0)
+    key, value = _repeat_kv_heads(query, key, value)
     out, lse = ops.sdpa(query, key, value, bool(is_causal), scale)
     if squeeze:
         out, lse = out.squeeze(0), lse.squeeze(0)
@@ -359,12 +367,22 @@ def aten__scaled_dot_product_flash_attention(
     out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
     # The remaining outputs exist for the backward/dropout replay; the reference fabricates
     # placeholders for them too (torch_mojo_backend/aten_functions.py:609-677). Here logsumexp
-    # is the real one.
+    # ([B, H, T] fp32, the shape torch gives this overload) is the real one.
     dev = out.device
     rng = _placeholder((2,), torch.int64, dev)
     unused = _placeholder((), torch.int64, dev)
     debug_mask = _placeholder((), out.dtype, dev)
-    return (out, _lse_as_traced(lse), None, None, query.shape[2], key.shape[2], rng, unused, debug_mask)
+    return (out, lse, None, None, query.shape[2], key.shape[2], rng, unused, debug_mask)
+
+
+def _lse_padded_to_32(lse):
+    """torch's memory-efficient attention reports logsumexp as [B, H, T rounded up to 32] (its
+    kernel's alignment); the padding holds +inf there and nothing reads it."""
+    t = lse.shape[-1]
+    pad = (-t) % 32
+    if pad == 0:
+        return lse
+    return torch.nn.functional.pad(lse, (0, pad), value=float("inf"))
 
 
 # _scaled_dot_product_efficient_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_bias,
@@ -377,15 +395,16 @@ def aten__scaled_dot_product_efficient_attention(
     if dropout_p != 0.0:
         raise NotImplementedError("attention dropout is not supported (inference forward only)")
     if attn_bias is not None:
-        out = _sdpa_math(query, key, value, attn_bias, is_causal, scale)
-        lse = torch.zeros(query.shape[:-1], dtype=torch.float32, device=query.device)
+        out, lse = _sdpa_math(query, key, value, attn_bias, is_causal, scale, want_lse=bool(compute_log_sumexp))
     else:
         out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
     dev = out.device
-    if not compute_log_sumexp:
-        lse = lse.new_empty((*lse.shape[:-1], 0))
+    if compute_log_sumexp:
+        lse = _lse_padded_to_32(lse)
+    else:
+        lse = torch.empty((*query.shape[:-2], 0), dtype=torch.float32, device=dev)
     seed = _placeholder((), torch.int64, dev)
-    return out, _lse_as_traced(lse), seed, seed
+    return out, lse, seed, seed
 
 
 # _scaled_dot_product_cudnn_attention(Tensor query, Tensor key, Tensor value, Tensor? attn_bias,
@@ -399,44 +418,49 @@ def aten__scaled_dot_product_cudnn_attention(
     if dropout_p != 0.0:
         raise NotImplementedError("attention dropout is not supported (inference forward only)")
     if attn_bias is not None:
-        out = _sdpa_math(query, key, value, attn_bias, is_causal, scale)
-        lse = torch.zeros(query.shape[:-1], dtype=torch.float32, device=query.device)
+        out, lse = _sdpa_math(query, key, value, attn_bias, is_causal, scale, want_lse=True)
     else:
         out, lse = _sdpa_kernel(query, key, value, is_causal, scale)
     dev = out.device
     rng = _placeholder((), torch.int64, dev)
-    return (out, _lse_as_traced(lse.unsqueeze(-1)), None, None, query.shape[2], key.shape[2], rng, rng, None)
+    # this overload reports logsumexp as [B, H, T, 1]
+    return (out, lse.unsqueeze(-1), None, None, query.shape[2], key.shape[2], rng, rng, None)
 
 
-def _sdpa_math(query, key, value, attn_mask, is_causal, scale):
-    """Attention with an explicit mask: GEMM -> masked softmax kernel -> GEMM
-    (reference: aten__scaled_dot_product_attention_math, torch_mojo_backend/aten_functions.py:443-504)."""
+def _sdpa_math(query, key, value, attn_mask, is_causal, scale, want_lse=False):
+    """Attention with an explicit mask (or operands no attention kernel takes): GEMM -> masked
+    softmax kernel -> GEMM (reference: aten__scaled_dot_product_attention_math,
+    torch_mojo_backend/aten_functions.py:443-504). A bool mask keeps where it is True, a float
+    mask is added to the scaled scores, `is_causal` masks on top of either (top-left aligned).
+    Returns (out, lse): lse is the natural-log LSE [..., L] in fp32 when `want_lse`, else None."""
     d = query.shape[-1]
     if scale is None:
         scale = 1.0 / math.sqrt(d)
     lead = query.shape[:-2]
     L, S = query.shape[-2], key.shape[-2]
-    if key.dim() == 4 and key.shape[1] != query.shape[1]:
-        rep = query.shape[1] // key.shape[1]
-        key = key.repeat_interleave(rep, dim=1)
-        value = value.repeat_interleave(rep, dim=1)
+    key, value = _repeat_kv_heads(query, key, value)
     q3 = query.reshape(-1, L, d)
     k3 = key.reshape(-1, S, d)
     v3 = value.reshape(-1, S, value.shape[-1])
     scores = aten_bmm(q3, k3.transpose(1, 2)).reshape(*lead, L, S)
-    if attn_mask is not None:
-        if attn_mask.dtype == torch.bool:
-            scores = (scores * scale).masked_fill(~attn_mask, float("-inf"))
-        else:
-            scores = scores * scale + attn_mask
+    lse = None
+    if attn_mask is not None or want_lse:
+        scores = scores.float() * scale if want_lse else scores * scale
+        if attn_mask is not None:
+            if attn_mask.dtype == torch.bool:
+                scores = scores.masked_fill(~attn_mask, float("-inf"))
+            else:
+                scores = scores + attn_mask
         if is_causal:
             causal = torch.ones(L, S, dtype=torch.bool, device=query.device).tril()
             scores = scores.masked_fill(~causal, float("-inf"))
+        if want_lse:
+            lse = torch.logsumexp(scores, dim=-1)  # small reduction over fp32 scores: glue
         probs = aten_softmax(scores, -1)
     else:
         probs = ops.softmax(scores, scale, bool(is_causal), L)
     out = aten_bmm(probs.reshape(-1, L, S).to(v3.dtype), v3)
-    return out.reshape(*lead, L, value.shape[-1])
+    return out.reshape(*lead, L, value.shape[-1]), lse
 
 
 # _scaled_dot_product_attention_math(Tensor query, Tensor key, Tensor value, Tensor? attn_mask=None,
@@ -449,7 +473,13 @@ def aten__scaled_dot_product_attention_math(
 ):
     if dropout_p != 0.0:
         raise NotImplementedError("attention dropout is not supported (inference forward only)")
-    out = _sdpa_math(query, key, value, attn_mask, is_causal, scale)
+    if dropout_mask is not None:
+        raise NotImplementedError("dropout_mask is not supported in aten._scaled_dot_product_attention_math")
+    if attn_mask is None and _kernel_takes_attention(query, key, value):
+        out = _sdpa_kernel(query, key, value, is_causal, scale)[0]
+    else:
+        out = _sdpa_math(query, key, value, attn_mask, is_causal, scale)[0]
+    # the second output (attention weights) is materialised by torch only for the backward pass
     return out, torch.zeros((), dtype=out.dtype, device=out.device)
 
 
@@ -461,9 +491,10 @@ def aten_scaled_dot_product_attention(
 ):
     if dropout_p != 0.0:
         raise NotImplementedError("attention dropout is not supported (inference forward only)")
-    if attn_mask is None and _kernel_dtype(query, key, value) and query.dim() in (3, 4):
+    _require_kernel_dtype("aten.scaled_dot_product_attention", query, key, value)
+    if attn_mask is None and _kernel_takes_attention(query, key, value):
         return _sdpa_kernel(query, key, value, is_causal, scale)[0]
-    return _sdpa_math(query, key, value, attn_mask, is_causal, scale)
+    return _sdpa_math(query, key, value, attn_mask, is_causal, scale)[0]
 
 
 # ==============================================================================================
@@ -509,6 +540,13 @@ def fused_gemm(a, b, bias, residual, *, alpha, beta, epilogue, out_dtype, out_sh
 
 
 @_count_calls
+def fused_embedding_sum(table, indices, table2, indices2, *, out_dtype):
+    """`embedding(table, indices).to(out_dtype) + embedding(table2, indices2).to(out_dtype)` (token
+    plus positional embeddings) as one gather kernel that adds in fp32 and writes `out_dtype`."""
+    return ops.embedding_sum(table, indices, table2, indices2, out_dtype)
+
+
+@_count_calls
 def contiguous_or_alias(x):
     """`clone(memory_format=contiguous)` of a fresh kernel output: no copy when the memory is
     already in that order."""
@@ -527,7 +565,7 @@ def fused_masked_softmax(x, mask, *, fill, scale, invert):
     return ops.softmax(masked)
 
 
-for _fused in (fused_layer_norm, fused_gemm, contiguous_or_alias, fused_masked_softmax):
+for _fused in (fused_layer_norm, fused_gemm, contiguous_or_alias, fused_masked_softmax, fused_embedding_sum):
     MAPPING_TORCH_ATEN_TO_MOJO[_fused] = _fused
 
 
@@ -562,16 +600,71 @@ def _passthrough(op):
     return run
 
 
+# embedding(Tensor weight, Tensor indices, SymInt padding_idx=-1, bool scale_grad_by_freq=False,
+#   bool sparse=False) -> Tensor
+@map_to(aten.embedding)
+def aten_embedding(weight, indices, padding_idx=-1, scale_grad_by_freq=False, sparse=False):
+    # padding_idx, scale_grad_by_freq and sparse only matter for the backward pass
+    # (reference: torch_mojo_backend/aten_functions.py:1779-1831)
+    if not _kernel_dtype(weight) or weight.dim() != 2:
+        return aten.embedding.default(weight, indices, padding_idx, scale_grad_by_freq, sparse)
+    return ops.embedding_sum(weight, indices)
+
+
+# argmax(Tensor self, int? dim=None, bool keepdim=False) -> Tensor
+@map_to(aten.argmax)
+def aten_argmax(input, dim=None, keepdim=False):
+    if not _kernel_dtype(input) or input.numel() == 0 or input.dim() == 0:
+        return torch.argmax(input, dim, keepdim)  # integer inputs / degenerate shapes: shape glue
+    if dim is None:
+        out = ops.argmax(input.reshape(-1))
+        return out.reshape([1] * input.dim()) if keepdim else out
+    x, moved = _move_dim_last(input, dim)
+    out = ops.argmax(x)
+    return out.unsqueeze(dim % input.dim()) if keepdim else out
+
+
+# cat(Tensor[] tensors, int dim=0) -> Tensor
+@map_to(aten.cat)
+def aten_cat(tensors, dim=0):
+    tensors = list(tensors)
+    if len({t.dtype for t in tensors}) != 1 or any(t.dim() == 0 for t in tensors):
+        return torch.cat(tensors, dim)  # type promotion across inputs: shape glue
+    return ops.cat(tensors, dim)
+
+
+def _view_or_copy(x, size):
+    """aten.view / aten._unsafe_view of a tensor whose run-time strides may differ from the ones the
+    trace assumed (a GEMM result with a padded row pitch): stay a view when the layout allows it,
+    copy otherwise -- never fail on a stride the user's program knows nothing about."""
+    try:
+        return x.view(size)
+    except (RuntimeError, ValueError):  # eager raises RuntimeError, the FakeTensor reference ValueError
+        return x.reshape(size)
+
+
+# view(Tensor(a) self, SymInt[] size) -> Tensor(a)
+@map_to(aten.view)
+def aten_view(x, size):
+    return _view_or_copy(x, size)
+
+
+# _unsafe_view(Tensor self, SymInt[] size) -> Tensor
+@map_to(aten._unsafe_view)
+def aten__unsafe_view(x, size):
+    return _view_or_copy(x, size)
+
+
 _GLUE_OPS = [
-    aten.view, aten._unsafe_view, aten.reshape, aten.transpose, aten.t, aten.permute, aten.expand,
+    aten.reshape, aten.transpose, aten.t, aten.permute, aten.expand,
     aten.clone, aten.contiguous, aten.split, aten.split_with_sizes, aten.slice, aten.select,
-    aten.unsqueeze, aten.squeeze, aten.cat, aten.stack, aten.alias, aten.detach, aten.arange,
+    aten.unsqueeze, aten.squeeze, aten.stack, aten.alias, aten.detach, aten.arange,
     aten.full, aten.full_like, aten.zeros, aten.zeros_like, aten.ones, aten.ones_like, aten.empty,
     aten.empty_like, aten.scalar_tensor, aten.tril, aten.triu, aten.eq, aten.ne, aten.lt, aten.le,
     aten.gt, aten.ge, aten.masked_fill, aten.where, aten.add, aten.sub, aten.mul, aten.div,
     aten.neg, aten.pow, aten.tanh, aten.exp, aten.log, aten.sqrt, aten.rsqrt, aten.abs,
     aten.sigmoid, aten.relu, aten.silu, aten.erf, aten.reciprocal, aten.minimum, aten.maximum,
-    aten.clamp, aten._to_copy, aten.embedding, aten.argmax, aten.logical_not, aten.logical_and,
+    aten.clamp, aten._to_copy, aten.logical_not, aten.logical_and,
     aten.logical_or, aten.bitwise_and, aten.bitwise_or, aten.bitwise_not, aten.cumsum, aten.all,
     aten.any, aten.index, aten.index_select, aten.gather, aten.sym_size, aten.sym_numel,
     aten.lift_fresh_copy, aten.copy, aten.repeat, aten.flip, aten.unbind, aten.max, aten.min,

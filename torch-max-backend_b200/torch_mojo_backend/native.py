@@ -34,8 +34,15 @@ ROUTE_AUTO = 0
 ROUTE_SIMT = 1
 ROUTE_TCGEN05 = 2
 ROUTE_SKINNY = 3
+ROUTE_SPLIT3 = 4
 
 ERR_DEVICE_TIMEOUT = -6
+
+# bits of the per-device status word (b200_device_status)
+STATUS_GEMM_TIMEOUT = 1
+STATUS_SDPA_TIMEOUT = 2
+STATUS_TEST_TIMEOUT = 4
+STATUS_INDEX_OUT_OF_RANGE = 8
 
 STATIC_SCRATCH_BYTES = 8 * 1024 * 1024  # B200_STATIC_SCRATCH_BYTES of include/b200ops.h
 
@@ -48,11 +55,15 @@ EXPORTED_SYMBOLS = (
     "b200_status_string",
     "b200_last_error",
     "b200_device_status",
+    "b200_debug_wait_timeout",
     "b200_layer_norm",
     "b200_softmax_lastdim",
     "b200_softmax_masked",
     "b200_gelu",
     "b200_reduce_lastdim",
+    "b200_embedding_sum",
+    "b200_argmax_lastdim",
+    "b200_copy_rows",
     "b200_gemm_route",
     "b200_gemm_workspace_bytes",
     "b200_gemm",
@@ -181,6 +192,8 @@ def _declare(dll: ctypes.CDLL) -> None:
     dll.b200_last_error.argtypes = []
     dll.b200_device_status.restype = i32
     dll.b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
+    dll.b200_debug_wait_timeout.restype = i32
+    dll.b200_debug_wait_timeout.argtypes = [ctypes.c_uint64, vp]
     dll.b200_layer_norm.restype = i32
     dll.b200_layer_norm.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, f32, i32, i32, i32, vp]
     dll.b200_softmax_lastdim.restype = i32
@@ -191,6 +204,12 @@ def _declare(dll: ctypes.CDLL) -> None:
     dll.b200_gelu.argtypes = [vp, vp, i64, i32, i32, vp]
     dll.b200_reduce_lastdim.restype = i32
     dll.b200_reduce_lastdim.argtypes = [vp, vp, i64, i64, i64, i32, i32, i32, vp]
+    dll.b200_embedding_sum.restype = i32
+    dll.b200_embedding_sum.argtypes = [vp, vp, i64, i64, vp, vp, i64, i64, i64, vp, i64, i64, i32, i32, vp]
+    dll.b200_argmax_lastdim.restype = i32
+    dll.b200_argmax_lastdim.argtypes = [vp, vp, i64, i64, i64, i32, vp]
+    dll.b200_copy_rows.restype = i32
+    dll.b200_copy_rows.argtypes = [vp, vp, i64, i64, i64, i64, i32, vp]
     dll.b200_gemm_route.restype = i32
     dll.b200_gemm_route.argtypes = [ctypes.POINTER(GemmArgs)]
     dll.b200_gemm_workspace_bytes.restype = ctypes.c_size_t

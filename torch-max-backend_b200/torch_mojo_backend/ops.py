@@ -42,6 +42,13 @@ _lib.define(
 _lib.define(
     "sdpa(Tensor q, Tensor k, Tensor v, bool causal=False, float? scale=None, int route=0) -> (Tensor, Tensor)"
 )
+_lib.define(
+    "embedding_sum(Tensor table, Tensor indices, Tensor? table2=None, Tensor? indices2=None,"
+    " ScalarType? out_dtype=None) -> Tensor"
+)
+_lib.define("argmax(Tensor x) -> Tensor")
+_lib.define("cat(Tensor[] tensors, int dim=0) -> Tensor")
+_lib.define("kv_append(Tensor(a!) cache, Tensor new, int position) -> ()")
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -245,6 +252,17 @@ def _gemm_out_shape(a, b):
     raise RuntimeError(f"gemm: operands must both be 2-D or both 3-D, got {a.dim()}-D and {b.dim()}-D")
 
 
+def _gemm_empty_out(out_shape, dtype, device, operand_dim):
+    """The output buffer of a GEMM. Rows of a wide 2-D output whose pitch is not a multiple of 16
+    bytes (e.g. the 50257-column logits) would be misaligned for vector stores: such an output gets
+    a padded pitch and is returned as the [m, n] view of it (the same idea as a padded leading
+    dimension in BLAS). Used by the CUDA and the Meta implementation alike."""
+    m, n = out_shape[-2], out_shape[-1]
+    if operand_dim == 2 and n % 8 != 0 and n >= 1024 and m > 1:
+        return torch.empty((m, (n + 7) // 8 * 8), dtype=dtype, device=device)[:, :n]
+    return torch.empty(out_shape, dtype=dtype, device=device)
+
+
 def fill_gemm_args(a, b, bias, residual, c, alpha, beta, epilogue, route) -> native.GemmArgs:
     """Marshals tensors into the C struct; separate from the launch so that tests can inspect it."""
     g = native.GemmArgs()
@@ -301,13 +319,7 @@ def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, 
     out_shape = _gemm_out_shape(a, b)
     out_dtype = out_dtype or a.dtype
     m, n = out_shape[-2], out_shape[-1]
-    if a.dim() == 2 and n % 8 != 0 and n >= 1024 and m > 1:
-        # Rows of a wide output whose pitch is not a multiple of 16 bytes (e.g. the 50257-column
-        # logits) would be misaligned for vector stores: allocate a padded pitch and return the
-        # [m, n] view of it (the same idea as a padded leading dimension in BLAS).
-        c = torch.empty((m, (n + 7) // 8 * 8), dtype=out_dtype, device=device)[:, :n]
-    else:
-        c = torch.empty(out_shape, dtype=out_dtype, device=device)
+    c = _gemm_empty_out(out_shape, out_dtype, device, a.dim())
     if c.numel() == 0:
         return c
     if a.dim() == 2:
@@ -320,8 +332,8 @@ def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, 
         bias = bias.contiguous()
     g = fill_gemm_args(a, b, bias, residual, c, alpha, beta, epilogue, route)
     workspace, workspace_bytes = None, 0
-    if m <= 128 and a.dim() == 2:
-        # only small-M problems can resolve to the split-K route, the one that needs scratch
+    if a.dim() == 2 and (m <= 128 or a.dtype == torch.float32):
+        # the routes that need scratch: split-K for small M, split-precision for fp32 operands
         workspace_bytes = native.lib().b200_gemm_workspace_bytes(ctypes.byref(g))
         if workspace_bytes:
             workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=device)
@@ -334,7 +346,9 @@ def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, 
 
 
 def _gemm_meta(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, out_dtype=None, route=0):
-    return torch.empty(_gemm_out_shape(a, b), dtype=out_dtype or a.dtype, device=a.device)
+    # same strides as the real op (padded pitch included), so that what the trace records about
+    # views of the result holds at run time
+    return _gemm_empty_out(_gemm_out_shape(a, b), out_dtype or a.dtype, a.device, a.dim())
 
 
 # ---- sdpa -----------------------------------------------------------------------------------
@@ -396,6 +410,147 @@ def _sdpa_meta(q, k, v, causal=False, scale=None, route=0):
     return o, torch.empty((B, H, T), dtype=torch.float32, device=q.device)
 
 
+# ---- embedding (+ second table) ---------------------------------------------------------------
+
+
+def _embedding_sum_cuda(table, indices, table2=None, indices2=None, out_dtype=None):
+    device = native.require_cuda("embedding_sum", table, indices, table2, indices2)
+    out_dtype = out_dtype or table.dtype
+    if table.dim() != 2 or table.stride(1) != 1:
+        raise RuntimeError("embedding_sum: the table must be [rows, cols] with a unit column stride")
+    if indices.dtype != torch.int64:
+        indices = indices.long()
+    idx = indices.contiguous()
+    rows, cols = idx.numel(), table.shape[1]
+    idx2, period = None, 0
+    if table2 is not None:
+        if table2.dtype != table.dtype or table2.dim() != 2 or table2.shape[1] != cols or table2.stride(1) != 1:
+            raise RuntimeError("embedding_sum: the second table must match the first in dtype and width")
+        idx2 = (indices2 if indices2.dtype == torch.int64 else indices2.long()).contiguous()
+        period = idx2.numel()
+        # indices2 broadcasts against indices from the right: its flattened length must tile the rows
+        if period == 0 or rows % period != 0 or tuple(indices.shape[indices.dim() - idx2.dim():]) != tuple(idx2.shape):
+            raise RuntimeError(
+                f"embedding_sum: indices2 {tuple(indices2.shape)} does not broadcast over indices {tuple(indices.shape)}")
+    out = torch.empty((*indices.shape, cols), dtype=out_dtype, device=device)
+    if out.numel() == 0:
+        return out
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_embedding_sum(
+            table.data_ptr(), idx.data_ptr(), table.shape[0], table.stride(0), _ptr(table2), _ptr(idx2),
+            table2.shape[0] if table2 is not None else 0, table2.stride(0) if table2 is not None else 0, period,
+            out.data_ptr(), rows, cols, native.dtype_enum(table.dtype), native.dtype_enum(out_dtype),
+            native.current_stream(device),
+        )
+    native.check("embedding_sum", status)
+    nb = rows * cols * (table.element_size() * (2 if table2 is not None else 1) + out.element_size())
+    _launched(device, start, "embedding", 0.0, float(nb))
+    return out
+
+
+def _embedding_sum_meta(table, indices, table2=None, indices2=None, out_dtype=None):
+    return torch.empty((*indices.shape, table.shape[1]), dtype=out_dtype or table.dtype, device=table.device)
+
+
+# ---- argmax over the last dim -----------------------------------------------------------------
+
+
+def _argmax_cuda(x):
+    device = native.require_cuda("argmax", x)
+    if x.dim() == 0 or x.shape[-1] == 0:
+        raise RuntimeError("argmax: needs a non-empty last dim")
+    # contiguous tensors and 2-D views with a padded pitch (the logits) are read in place
+    xr, rows, cols, row_stride = _as_rows(x)
+    out = torch.empty(x.shape[:-1], dtype=torch.int64, device=device)
+    if out.numel() == 0:
+        return out
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_argmax_lastdim(
+            xr.data_ptr(), out.data_ptr(), rows, cols, row_stride, native.dtype_enum(x.dtype), native.current_stream(device))
+    native.check("argmax", status)
+    _launched(device, start, "argmax", 0.0, float(rows * cols * x.element_size()))
+    return out
+
+
+def _argmax_meta(x):
+    return torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+
+
+# ---- concatenation and cache append (strided block copies) -------------------------------------
+
+
+def _copy_block(dst, src, dim, device):
+    """dst and src have the same shape except that dst may be a slice (along `dim`) of a larger
+    contiguous tensor; both are dense from `dim` on."""
+    outer = math.prod(src.shape[:dim])
+    inner = math.prod(src.shape[dim:])
+    if outer == 0 or inner == 0:
+        return
+    dst_stride = dst.stride(dim - 1) if dim > 0 else inner
+    src_stride = src.stride(dim - 1) if dim > 0 else inner
+    with torch.cuda.device(device):
+        status = native.lib().b200_copy_rows(dst.data_ptr(), src.data_ptr(), outer, inner, dst_stride, src_stride,
+                                             src.element_size(), native.current_stream(device))
+    native.check("copy_rows", status)
+    native.launch_count += 1
+
+
+def _cat_cuda(tensors, dim=0):
+    tensors = [t for t in tensors if not (t.dim() == 1 and t.numel() == 0)]  # torch skips legacy empty tensors
+    device = native.require_cuda("cat", *tensors)
+    first = tensors[0]
+    dim = dim % first.dim()
+    dtype = first.dtype
+    for t in tensors:
+        if t.dtype != dtype:
+            raise RuntimeError("cat: mixed dtypes are not supported")
+    shape = list(first.shape)
+    shape[dim] = sum(t.shape[dim] for t in tensors)
+    out = torch.empty(shape, dtype=dtype, device=device)
+    start = _prof_begin(device)
+    offset = 0
+    for t in tensors:
+        tc = t if t.is_contiguous() else t.contiguous()
+        _copy_block(out.narrow(dim, offset, t.shape[dim]), tc, dim, device)
+        offset += t.shape[dim]
+    if start is not None:
+        native.profiler.end(device, start, "cat", 0.0, 2.0 * out.numel() * out.element_size())
+    return out
+
+
+def _cat_meta(tensors, dim=0):
+    tensors = [t for t in tensors if not (t.dim() == 1 and t.numel() == 0)]
+    first = tensors[0]
+    dim = dim % first.dim()
+    shape = list(first.shape)
+    shape[dim] = sum(t.shape[dim] for t in tensors)
+    return torch.empty(shape, dtype=first.dtype, device=first.device)
+
+
+def _kv_append_cuda(cache, new, position):
+    """cache[..., position : position + t, :] = new, in place: the decode-loop alternative to
+    `torch.cat([cache, new], dim=-2)`, which re-copies the whole cache every step. cache is a
+    contiguous [..., T_max, D]; new is [..., t, D] with the same leading dims."""
+    device = native.require_cuda("kv_append", cache, new)
+    if cache.dim() < 2 or new.dim() != cache.dim() or cache.dtype != new.dtype:
+        raise RuntimeError("kv_append: cache and new must have the same rank and dtype")
+    if tuple(cache.shape[:-2]) != tuple(new.shape[:-2]) or cache.shape[-1] != new.shape[-1]:
+        raise RuntimeError(f"kv_append: shapes {tuple(cache.shape)} and {tuple(new.shape)} do not match")
+    t = new.shape[-2]
+    if position < 0 or position + t > cache.shape[-2]:
+        raise RuntimeError(f"kv_append: positions [{position}, {position + t}) outside a cache of {cache.shape[-2]}")
+    if not cache.is_contiguous():
+        raise RuntimeError("kv_append: the cache must be contiguous")
+    nc = new if new.is_contiguous() else new.contiguous()
+    _copy_block(cache.narrow(-2, position, t), nc, cache.dim() - 2, device)
+
+
+def _kv_append_meta(cache, new, position):
+    return None
+
+
 def _refuse_cpu(name):
     def impl(*args, **kwargs):
         raise RuntimeError(
@@ -414,6 +569,10 @@ for _name, _cuda, _meta in (
     ("reduce", _reduce_cuda, _reduce_meta),
     ("gemm", _gemm_cuda, _gemm_meta),
     ("sdpa", _sdpa_cuda, _sdpa_meta),
+    ("embedding_sum", _embedding_sum_cuda, _embedding_sum_meta),
+    ("argmax", _argmax_cuda, _argmax_meta),
+    ("cat", _cat_cuda, _cat_meta),
+    ("kv_append", _kv_append_cuda, _kv_append_meta),
 ):
     _lib.impl(_name, _cuda, "CUDA")
     _lib.impl(_name, _refuse_cpu(_name), "CPU")
@@ -426,3 +585,7 @@ gelu = torch.ops.b200.gelu
 reduce = torch.ops.b200.reduce
 gemm = torch.ops.b200.gemm
 sdpa = torch.ops.b200.sdpa
+embedding_sum = torch.ops.b200.embedding_sum
+argmax = torch.ops.b200.argmax
+cat = torch.ops.b200.cat
+kv_append = torch.ops.b200.kv_append

@@ -17,6 +17,9 @@ epilogues:
            contract is SoftmaxRows(scale, causal, q_len), eager_kernels/nn_ops.mojo:392-409; the
            mask here is explicit, so nothing is assumed about its values)
 
+  * `embedding(wte, idx)[.to(dt)] + embedding(wpe, pos)[.to(dt)]`  => one gather kernel that reads
+        both tables, adds in fp32 and writes `dt` (token + positional embeddings)
+
 Every intermediate node of a chain must have exactly one user; chains with symbolic shapes are
 left alone. Fused nodes call functions registered in MAPPING_TORCH_ATEN_TO_MOJO under themselves,
 so the graph walk treats them like any other lowering. TORCH_MOJO_BACKEND_NO_FUSION=1 disables
@@ -261,6 +264,61 @@ def _fuse_masked_softmax(graph) -> int:
     return count
 
 
+def _embedding_operand(node):
+    """(table, indices, cast dtype or None) when `node` is `embedding(table, indices)` or a plain
+    dtype cast of one, each link with a single user; else None."""
+    dtype = None
+    cast = _plain_cast(node)
+    if cast is not None:
+        if len(node.users) != 1:
+            return None
+        dtype = cast
+        node = node.args[0]
+    if not _is_call(node, aten.embedding.default) or len(node.users) != 1 or not _static_tensor(node):
+        return None
+    table, indices = node.args[:2]
+    vt, vi = _val(table), _val(indices)
+    if not (isinstance(vt, torch.Tensor) and isinstance(vi, torch.Tensor)) or vt.dim() != 2:
+        return None
+    if not native.supported_dtype(vt.dtype) or vi.dtype not in (torch.int64, torch.int32):
+        return None
+    return table, indices, dtype
+
+
+def _fuse_embedding_sum(graph) -> int:
+    """`embedding(wte, idx)[.to(dt)] + embedding(wpe, pos)[.to(dt)]`, pos broadcasting over idx from
+    the right (the token + positional embeddings of a GPT-style model; reference contract:
+    aten_embedding, torch_mojo_backend/aten_functions.py:1779-1831, followed by aten_add)."""
+    count = 0
+    for node in list(graph.nodes):
+        if not (_is_call(node, aten.add.Tensor) and node.kwargs.get("alpha", 1) == 1 and len(node.args) == 2):
+            continue
+        if not all(isinstance(x, torch.fx.Node) for x in node.args) or not _static_tensor(node):
+            continue
+        lhs, rhs = _embedding_operand(node.args[0]), _embedding_operand(node.args[1])
+        if lhs is None or rhs is None or node.args[0] is node.args[1]:
+            continue
+        # the operand whose indices carry the full shape goes first
+        if _val(lhs[1]).dim() < _val(rhs[1]).dim():
+            lhs, rhs = rhs, lhs
+        (t1, i1, d1), (t2, i2, d2) = lhs, rhs
+        v1, v2, vt1, vt2, vo = _val(i1), _val(i2), _val(t1), _val(t2), _val(node)
+        if d1 != d2 or vt1.dtype != vt2.dtype or vt1.shape[1] != vt2.shape[1]:
+            continue
+        out_dtype = d1 or vt1.dtype
+        if vo.dtype != out_dtype or not native.supported_dtype(out_dtype):
+            continue
+        if vt1.dtype == torch.float32 and out_dtype != torch.float32:
+            continue
+        if v2.dim() > v1.dim() or tuple(v1.shape[v1.dim() - v2.dim():]) != tuple(v2.shape) or v2.numel() == 0:
+            continue
+        if tuple(vo.shape) != (*v1.shape, vt1.shape[1]):
+            continue
+        _replace(graph, node, af.fused_embedding_sum, (t1, i1, t2, i2), {"out_dtype": out_dtype})
+        count += 1
+    return count
+
+
 def fuse_graph(gm: torch.fx.GraphModule) -> dict[str, int]:
     """Rewrites gm.graph in place and returns how many chains of each kind were folded."""
     graph = gm.graph
@@ -269,6 +327,7 @@ def fuse_graph(gm: torch.fx.GraphModule) -> dict[str, int]:
         "gemm_epilogue": _fuse_gemm_epilogues(graph),
         "attention_output_copy": _drop_attention_output_copies(graph),
         "masked_softmax": _fuse_masked_softmax(graph),
+        "embedding_sum": _fuse_embedding_sum(graph),
     }
     if any(stats.values()):
         graph.eliminate_dead_code()
