@@ -209,6 +209,31 @@ def test_tcgen05_cta_pair_kernel(ops, monkeypatch, tile_n):
     assert_parity(y3, torch.bmm(a3.float(), w3.float().transpose(1, 2)), bf16=True)
 
 
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_tcgen05_cta_pair_kernel_mn_major_b(ops, monkeypatch, tile_n):
+    """The CTA-pair kernel on a contiguous [K, N] weight (HF Conv1D layout): each CTA stages its half
+    of the tile's columns as 64-column boxes. Forced on ragged shapes, with bias + gelu + fp32
+    residual; bit-for-bit equal to the single-CTA kernel; and the default for large problems."""
+    monkeypatch.setenv("B200_GEMM_TILE_N", str(tile_n))
+    for m, n, k in ((700, 1000, 328), (100, 520, 64), (1024, 768, 1600), (512, 2304, 768)):
+        a = gen((m, k), torch.bfloat16, 58, 0.5)
+        b = gen((k, n), torch.bfloat16, 59, 0.1)
+        bias = gen((n,), torch.bfloat16, 60)
+        res = gen((m, n), torch.float32, 61)
+        outs = {}
+        for pair in ("0", "1"):
+            monkeypatch.setenv("B200_GEMM_PAIR", pair)
+            outs[pair] = ops.gemm(a.cuda(), b.cuda(), bias.cuda(), res.cuda(), 1.0, 1.0, 1, torch.float32, ROUTE_TC)
+        want = torch.nn.functional.gelu(a.float() @ b.float() + bias.float(), approximate="tanh") + res
+        assert_parity(outs["1"], want, bf16=False)
+        assert torch.equal(outs["0"], outs["1"])
+    monkeypatch.delenv("B200_GEMM_PAIR", raising=False)
+    monkeypatch.delenv("B200_GEMM_TILE_N", raising=False)
+    a, b = gen((2048, 512), torch.bfloat16, 62, 0.5), gen((512, 1536), torch.bfloat16, 63, 0.1)
+    y = ops.gemm(a.cuda(), b.cuda(), None, None, 1.0, 1.0, 0, torch.bfloat16, ROUTE_TC)
+    assert_parity(y, a.float() @ b.float(), bf16=True)
+
+
 def test_tcgen05_cta_pair_kernel_is_the_default_for_large_problems(ops, monkeypatch):
     """Without any override a large K-major problem takes the pair kernel; its result must equal
     the single-CTA kernel's."""

@@ -17,10 +17,10 @@
 // Tiles are walked in bands of kBandM row-tiles (column-tile outer, row-tile inner inside a band):
 // a band's slice of A is re-used from L2 across all its column tiles while the (smaller) B stays
 // L2-resident.
-// Large problems with K-major B run the CTA-pair form (PAIR): clusters of two CTAs, each pair
-// owning a 256 x BN tile through tcgen05.mma.cta_group::2. Each CTA stages its own 128 rows of A
-// and its own BN/2 rows of B^T (plain TMA loads whose completion bytes are counted on the even
-// CTA's barrier), the even CTA's elected lane issues the 256 x BN x 16 MMAs for both and commits
+// Large problems run the CTA-pair form (PAIR): clusters of two CTAs, each pair owning a 256 x BN
+// tile through tcgen05.mma.cta_group::2. Each CTA stages its own 128 rows of A and its own half of
+// the tile's B columns -- BN/2 rows of B^T for a K-major B, BN/2/64 boxes of 64 columns for an
+// MN-major one (plain TMA loads whose completion bytes are counted on the even CTA's barrier), the even CTA's elected lane issues the 256 x BN x 16 MMAs for both and commits
 // to the barriers of both, and each CTA's epilogue warps drain their own 128 accumulator rows and
 // report to the even CTA's `tmem_empty`. A stage is a third smaller than the single-CTA stage of
 // the same BN, so the ring is six stages deep instead of four.
@@ -172,7 +172,8 @@ template <int BN, bool B_MN_MAJOR, typename Tout, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, Tout* __restrict__ C, Params p) {
-  static_assert(!(PAIR && B_MN_MAJOR), "the pair kernel stages B^T rows (K-major B) only");
+  static_assert(!(PAIR && B_MN_MAJOR) || (BN / 2) % 64 == 0,
+                "MN-major B in the pair kernel: each CTA's half of the columns is a whole number of 64-column boxes");
   using C_ = Cfg<BN, PAIR>;
   constexpr int kStages = C_::kStages;
   constexpr int kTileM = PAIR ? 2 * BM : BM;        // rows of C per tile (per CTA pair when PAIR)
@@ -247,10 +248,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int32_t mt, nt;
         tile_coords<kBand>(t, p, b, mt, nt);
         const int32_t m0 = mt * kTileM + (int32_t)rank * BM, n0 = nt * BN + (int32_t)rank * C_::B_ROWS * (PAIR ? 1 : 0);
-        for (int64_t kb = 0; kb < num_kb; ++kb) {
+        int32_t part = 0, k_in_part = 0;  // position of the k-block inside the (possibly multi-pass) K walk
+        for (int64_t kb = 0; kb < num_kb; ++kb, k_in_part += BK) {
           if (!ptx::mbar_wait_relaxed(empty_bar(s), phase ^ 1, abort_flag)) { ok = false; break; }
-          const int32_t part = (int32_t)(kb / kb_per_part);
-          const int32_t k_in_part = (int32_t)((kb - part * kb_per_part) * BK);
+          if (k_in_part >= (int32_t)(kb_per_part * BK)) { k_in_part = 0; ++part; }
           const int32_t k0 = k_in_part + p.a_part_off[part], k0b = k_in_part + p.b_part_off[part];
           if (PAIR) {
             // Both CTAs' copies are counted on the even CTA's barrier, which expects the bytes of
@@ -259,7 +260,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t bar = ptx::mapa(full_bar(s), 0);
             if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + C_::B_STAGE_BYTES));
             ptx::tma_load_3d_pair(a_base + s * A_STAGE_BYTES, &tmap_a, bar, k0, m0, (int32_t)b);
-            ptx::tma_load_3d_pair(b_base + s * C_::B_STAGE_BYTES, &tmap_b, bar, k0b, n0, (int32_t)b);
+            if (!B_MN_MAJOR) {
+              ptx::tma_load_3d_pair(b_base + s * C_::B_STAGE_BYTES, &tmap_b, bar, k0b, n0, (int32_t)b);
+            } else {
+              // B stored [K, N]: this CTA's half of the tile's columns as boxes of 64(n) x 64(k)
+#pragma unroll
+              for (int j = 0; j < C_::B_ROWS / 64; ++j)
+                ptx::tma_load_3d_pair(b_base + s * C_::B_STAGE_BYTES + j * (64 * BK * 2), &tmap_b, bar,
+                                      n0 + j * 64, k0b, (int32_t)b);
+            }
             if (++s == kStages) { s = 0; phase ^= 1; }
             continue;
           }
@@ -629,7 +638,7 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream, const GemmKPart
 }
 
 // The CTA-pair form: clusters of two CTAs, each pair walking 256 x BN tiles.
-template <int BN, typename Tout>
+template <int BN, bool B_MN_MAJOR, typename Tout>
 int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream, const GemmKParts* kp) {
   using C_ = Cfg<BN, true>;
   static_assert(C_::kSmemBytes <= 227 * 1024, "pair configuration exceeds the shared memory of an SM");
@@ -643,11 +652,19 @@ int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream, const Gemm
     int32_t st = encode_tensor_map(&tmap_a, B200_BF16, 3, g.a, dims, strides, box, true);
     if (st != B200_OK) return st;
   }
-  {
+  if (!B_MN_MAJOR) {
     const uint64_t dims[3] = {k_extent, (uint64_t)g.n, (uint64_t)g.batch};
     const uint64_t strides[2] = {(uint64_t)g.b_col_stride * 2,
                                  (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_col_stride * g.n) * 2};
     const uint32_t box[3] = {BK, (uint32_t)C_::B_ROWS, 1};
+    int32_t st = encode_tensor_map(&tmap_b, B200_BF16, 3, g.b, dims, strides, box, true);
+    if (st != B200_OK) return st;
+  } else {
+    // B is [k, n] with row pitch b_row_stride.
+    const uint64_t dims[3] = {(uint64_t)g.n, k_extent, (uint64_t)g.batch};
+    const uint64_t strides[2] = {(uint64_t)g.b_row_stride * 2,
+                                 (uint64_t)(g.batch > 1 ? g.b_batch_stride : g.b_row_stride * k_extent) * 2};
+    const uint32_t box[3] = {64, BK, 1};
     int32_t st = encode_tensor_map(&tmap_b, B200_BF16, 3, g.b, dims, strides, box, true);
     if (st != B200_OK) return st;
   }
@@ -656,7 +673,7 @@ int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream, const Gemm
   if (st != B200_OK) return st;
   apply_k_parts(p, kp);
 
-  auto kernel = gemm_tcgen05_kernel<BN, false, Tout, true>;
+  auto kernel = gemm_tcgen05_kernel<BN, B_MN_MAJOR, Tout, true>;
   static thread_local bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -713,13 +730,15 @@ Tuning tuning() {
 // Whether the CTA-pair kernel is used, and with which tile width (0 = not used).
 // B200_GEMM_PAIR=0 turns it off, =1 forces it wherever it is eligible (tuning and tests).
 int pick_pair_bn(const b200_gemm_args& g) {
-  if (!b_is_k_major(g)) return 0;
+  // MN-major B ([K, N] contiguous) comes in 64-column boxes, so a CTA's half of the tile must be a
+  // multiple of 64 columns: tile widths 128 and 256 only.
+  const bool mn_major = !b_is_k_major(g);
   const Tuning t = tuning();
   const int mode = t.pair_mode;
   if (mode == 0) return 0;
   // Small problems have too few 256-row tiles to fill 74 pairs; they keep the single-CTA kernel.
   if (mode != 1 && (g.m < 1024 || g.n < 512)) return 0;
-  if (t.tile_n != 0) return t.tile_n;
+  if (t.tile_n != 0) return (mn_major && t.tile_n == 192) ? 0 : t.tile_n;
   const int64_t pairs = sm_count() / 2;
   // Time of a tile ~ (BN + 270) columns' worth: the measured fixed share per tile (issue loop,
   // accumulator hand-off, epilogue) is about as large as the width-proportional part, so wide
@@ -729,7 +748,7 @@ int pick_pair_bn(const b200_gemm_args& g) {
     const int64_t waves = (tiles + pairs - 1) / pairs;
     return (double)waves * (bn + 270);
   };
-  const double c256 = cost(256), c192 = cost(192), c128 = cost(128);
+  const double c256 = cost(256), c192 = mn_major ? 1e300 : cost(192), c128 = cost(128);
   if (c256 <= c192 && c256 <= c128) return 256;
   return c192 <= c128 ? 192 : 128;
 }
@@ -781,10 +800,11 @@ int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream, const 
   const bool mn = !b_is_k_major(g);
   const bool f32 = g.out_dtype == B200_F32;
   if (const int pbn = pick_pair_bn(g)) {
-#define PAIR_LAUNCH(BN_) (f32 ? launch_pair_cfg<BN_, float>(g, stream, kp) : launch_pair_cfg<BN_, __nv_bfloat16>(g, stream, kp))
-    if (pbn == 256) return PAIR_LAUNCH(256);
-    if (pbn == 192) return PAIR_LAUNCH(192);
-    return PAIR_LAUNCH(128);
+#define PAIR_LAUNCH(BN_, MN_) \
+  (f32 ? launch_pair_cfg<BN_, MN_, float>(g, stream, kp) : launch_pair_cfg<BN_, MN_, __nv_bfloat16>(g, stream, kp))
+    if (pbn == 256) return mn ? PAIR_LAUNCH(256, true) : PAIR_LAUNCH(256, false);
+    if (pbn == 192) return PAIR_LAUNCH(192, false);
+    return mn ? PAIR_LAUNCH(128, true) : PAIR_LAUNCH(128, false);
 #undef PAIR_LAUNCH
   }
   const int bn = pick_bn(g);

@@ -6,6 +6,8 @@
 // kernel with scalar accesses.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace b200 {
 namespace {
 
@@ -179,6 +181,110 @@ layer_norm_warp_kernel(const Tin* __restrict__ x, const Tp* __restrict__ gamma,
   }
 }
 
+// The same computation with WPR warps per row: each lane keeps 1/WPR of the chunks (fewer registers
+// per thread, more resident warps, and the loads of a row are spread over more warps) and the partial
+// sums of a row's warps meet in shared memory. The loop over row groups is there for grids smaller
+// than the number of groups; launching one CTA per group measured faster than a persistent grid
+// (fresh CTAs overlap one group's loads with another's arithmetic, a looping CTA serialises them).
+constexpr int kLnWarps = 8;
+template <typename Tin, typename Tp, typename Tout, int N, int MAXC, int WPR>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layer_norm_rows_kernel(const Tin* __restrict__ x, const Tp* __restrict__ gamma,
+                       const Tp* __restrict__ beta, Tout* __restrict__ y,
+                       float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t rows,
+                       int cols, int64_t x_row_stride, float eps) {
+  constexpr int kRowsPerCta = kLnWarps / WPR;
+  __shared__ float part[2][kLnWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = warp % WPR;        // which share of the row this warp holds
+  const int slot = warp / WPR;       // which of the CTA's rows
+  const int nchunks = cols / N;
+  const int64_t groups = (rows + kRowsPerCta - 1) / kRowsPerCta;
+  for (int64_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+    const int64_t row = grp * kRowsPerCta + slot;
+    const bool live = row < rows;
+    const Tin* xr = x + (live ? row : 0) * x_row_stride;
+    float v[MAXC][N];
+    float2 sum2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * (sub + WPR * i);
+      if (live && c < nchunks) {
+        Chunk<Tin, N>::load(xr + c * N, v[i]);
+#pragma unroll
+        for (int j = 0; j < N; j += 2) sum2 = __fadd2_rn(sum2, make_float2(v[i][j], v[i][j + 1]));
+      }
+    }
+    float total = warp_sum(sum2.x + sum2.y);
+    if (WPR > 1) {
+      if (lane == 0) part[0][warp] = total;
+      __syncthreads();
+      total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < WPR; ++w) total += part[0][slot * WPR + w];
+    }
+    const float mean = total / (float)cols;
+    const float2 neg_mean2 = make_float2(-mean, -mean);
+    float2 sq2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * (sub + WPR * i);
+      if (live && c < nchunks) {
+#pragma unroll
+        for (int j = 0; j < N; j += 2) {
+          const float2 d = __fadd2_rn(make_float2(v[i][j], v[i][j + 1]), neg_mean2);
+          v[i][j] = d.x;
+          v[i][j + 1] = d.y;
+          sq2 = __ffma2_rn(d, d, sq2);
+        }
+      }
+    }
+    float sq = warp_sum(sq2.x + sq2.y);
+    if (WPR > 1) {
+      if (lane == 0) part[1][warp] = sq;
+      __syncthreads();  // also orders this row's reads of part[0] before the next row's writes
+      sq = 0.0f;
+#pragma unroll
+      for (int w = 0; w < WPR; ++w) sq += part[1][slot * WPR + w];
+    }
+    const float rstd = 1.0f / sqrtf(sq / (float)cols + eps);
+    const float2 rstd2 = make_float2(rstd, rstd);
+    Tout* yr = y + (live ? row : 0) * (int64_t)cols;
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * (sub + WPR * i);
+      if (live && c < nchunks) {
+        float g[N], b[N], o[N];
+        if (gamma != nullptr) {
+          Chunk<Tp, N>::load_keep(gamma + c * N, g);
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j) g[j] = 1.0f;
+        }
+        if (beta != nullptr) {
+          Chunk<Tp, N>::load_keep(beta + c * N, b);
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j) b[j] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < N; j += 2) {
+          const float2 t = __fmul2_rn(make_float2(v[i][j], v[i][j + 1]), rstd2);
+          const float2 r = __ffma2_rn(t, make_float2(g[j], g[j + 1]), make_float2(b[j], b[j + 1]));
+          o[j] = r.x;
+          o[j + 1] = r.y;
+        }
+        Chunk<Tout, N>::store(yr + c * N, o);
+      }
+    }
+    if (live && lane == 0 && sub == 0) {
+      if (mean_out != nullptr) mean_out[row] = mean;
+      if (rstd_out != nullptr) rstd_out[row] = rstd;
+    }
+    if (WPR > 1) __syncthreads();  // part[1] is read before the next row overwrites it
+  }
+}
+
 // Generic: one CTA per row, scalar accesses, three passes over the row (L1/L2 serve the
 // re-reads).
 template <typename Tin, typename Tp, typename Tout>
@@ -229,6 +335,22 @@ int32_t launch_layer_norm(const void* x, const void* gamma, const void* beta, vo
                       rows <= (int64_t)INT32_MAX * kWarpsPerCta;
   if (vec_ok) {
     const int per_lane = (int)((cols / N + 31) / 32);
+    if (per_lane > 8) {
+      // Wide rows (more than 8 chunks per lane, e.g. 1600 fp32 columns): two warps per row. Measured
+      // on [65536, 1600] fp32 -> bf16: 1.00 of the copy bandwidth against 0.90 with one warp per row
+      // (half the registers per thread, twice the resident warps); narrower rows measured no gain.
+      constexpr int kRowsPerCta = kLnWarps / 2;
+      const int64_t groups = (rows + kRowsPerCta - 1) / kRowsPerCta;
+      B200_REQUIRE(groups <= INT32_MAX, B200_ERR_UNSUPPORTED, "layer_norm: too many rows");
+      const unsigned grid2 = (unsigned)groups;
+      const int share = (per_lane + 1) / 2;
+#define LNR(MAXC) layer_norm_rows_kernel<Tin, Tp, Tout, N, MAXC, 2><<<grid2, kLnWarps * 32, 0, stream>>>( \
+      xp, gp, bp, yp, mean, rstd, rows, (int)cols, x_row_stride, eps)
+      if (share <= 5) LNR(5); else if (share <= 7) LNR(7); else LNR(8);
+#undef LNR
+      B200_CHECK_LAUNCH("layer_norm");
+      return B200_OK;
+    }
     const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
 #define LN_LAUNCH(MAXC)                                                                   \
   layer_norm_warp_kernel<Tin, Tp, Tout, N, MAXC><<<grid, kRowThreads, 0, stream>>>(         \
