@@ -151,6 +151,27 @@ def test_decode_shapes_of_the_sweep(ops, m, k, n, b_layout):
     assert_parity(y16, want, bf16=True)
 
 
+@pytest.mark.parametrize("m", [1, 3, 16, 17, 64])
+@pytest.mark.parametrize("k,n", [(768, 2304), (768, 768), (768, 3072), (3072, 768), (768, 50257)])
+@pytest.mark.parametrize("b_layout", ["nk", "kn"])
+def test_decode_shapes_of_the_sweep_fp32(ops, m, k, n, b_layout):
+    """The fp32 half of the decode cells: M in {1, 16, 64} (and two ragged row counts) on every
+    (K, N) of the sweep, both weight layouts, bias + residual, route AUTO; 1e-4 relative against an
+    fp64 oracle."""
+    a = gen((m, k), torch.float32, 93)
+    bias, res = gen((n,), torch.float32, 95, 0.02), gen((m, n), torch.float32, 96)
+    if b_layout == "nk":
+        w = gen((n, k), torch.float32, 94, 0.1)
+        b_cpu, b_gpu = w.t(), w.cuda().t()
+    else:
+        b_cpu = gen((k, n), torch.float32, 94, 0.1)
+        b_gpu = b_cpu.cuda()
+    want = (a.double() @ b_cpu.double() + bias.double() + res.double()).float()
+    y = ops.gemm(a.cuda(), b_gpu, bias.cuda(), res.cuda())
+    assert y.dtype == torch.float32 and y.shape == (m, n)
+    assert_parity(y, want, bf16=False)
+
+
 @pytest.mark.parametrize("m,n,k", [(1000, 50257, 768), (129, 200, 72), (33, 72, 200), (128, 256, 64), (300, 1000, 1600)])
 def test_tcgen05_ragged(ops, m, n, k):
     a = gen((m, k), torch.bfloat16, 13)

@@ -51,6 +51,8 @@ int32_t resolve_route(const b200_gemm_args& g) {
     if (why != nullptr) B200_FAIL(B200_ERR_UNSUPPORTED, "gemm: split-precision route refused: %s", why);
     return B200_ROUTE_SPLIT3;
   }
+  // one to eight rows of either dtype: the CUDA-core small-M route (exact fp32 products)
+  if (g.route == B200_ROUTE_AUTO && gemm_gemv_ineligible(g) == nullptr) return B200_ROUTE_SKINNY;
   if (g.route == B200_ROUTE_AUTO && g.in_dtype == B200_F32 && gemm_split_ineligible(g) == nullptr &&
       (double)g.m * (double)g.n * (double)g.k >= kSplitMinMacs)
     return B200_ROUTE_SPLIT3;

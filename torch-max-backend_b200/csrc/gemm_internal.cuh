@@ -23,6 +23,12 @@ struct GemmKParts {
 };
 int32_t launch_gemm_tcgen05(const b200_gemm_args& g, cudaStream_t stream, const GemmKParts* k_parts = nullptr);
 
+// At most 8 rows (fp32 or bf16): CUDA-core partial sums over (column block, K slice) CTAs.
+const char* gemm_gemv_ineligible(const b200_gemm_args& g);
+int gemm_gemv_slices(const b200_gemm_args& g);
+size_t gemm_gemv_scratch_bytes(const b200_gemm_args& g);
+int32_t launch_gemm_gemv_partials(const b200_gemm_args& g, float* partial, int slices, cudaStream_t stream);
+
 // fp32 operands on the tensor cores: each operand is split into bf16 halves (x = hi + lo), written
 // K-major into scratch, and one tensor-core launch accumulates a_hi b_lo + a_lo b_hi + a_hi b_hi.
 const char* gemm_split_ineligible(const b200_gemm_args& g);

@@ -1,8 +1,9 @@
 // Small-M (decode-shaped) GEMM: the weights are read once and the problem is HBM-bound, but with
 // few rows there are too few output tiles to keep every SM streaming. The K range is therefore
-// split across CTAs: the tensor-core kernel runs in batched mode with one "batch" per K slice
-// and writes fp32 partial tiles into a scratch buffer [splits, m, n]; a second kernel adds the
-// slices in a fixed order (deterministic, no atomics) and applies the epilogue.
+// split across CTAs: stage 1 writes fp32 partial sums into a scratch buffer [splits, m, n] -- the
+// tensor-core kernel in batched mode (one "batch" per K slice) for 9 to 128 bf16 rows, the
+// CUDA-core kernels of gemm_gemv.cu for up to 8 rows of either dtype -- and a second kernel adds
+// the slices in a fixed order (deterministic, no atomics) and applies the epilogue.
 //
 // The scratch buffer is the caller's workspace (b200_gemm_workspace_bytes says how large).
 #include "gemm_internal.cuh"
@@ -93,6 +94,7 @@ int gemm_skinny_splits(const b200_gemm_args& g) {
 }
 
 const char* gemm_skinny_ineligible(const b200_gemm_args& g) {
+  if (gemm_gemv_ineligible(g) == nullptr) return nullptr;  // up to 8 rows: the CUDA-core stage 1
   if (g.batch != 1) return "batched";
   if (g.m > 128) return "more than 128 rows";
   if (gemm_tcgen05_ineligible(g) != nullptr) return "operands not eligible for the tensor-core kernel";
@@ -101,18 +103,25 @@ const char* gemm_skinny_ineligible(const b200_gemm_args& g) {
 }
 
 size_t gemm_skinny_scratch_bytes(const b200_gemm_args& g) {
+  if (gemm_gemv_ineligible(g) == nullptr) return gemm_gemv_scratch_bytes(g);
   const int s = gemm_skinny_splits(g);
   return s < 2 ? 0 : (size_t)s * (size_t)g.m * (size_t)g.n * sizeof(float);
 }
 
 int32_t launch_gemm_skinny(const b200_gemm_args& g, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
-  const int splits = gemm_skinny_splits(g);
-  B200_REQUIRE(splits >= 2, B200_ERR_UNSUPPORTED, "gemm(skinny): no K split for these arguments");
+  const bool gemv = gemm_gemv_ineligible(g) == nullptr;
+  const int splits = gemv ? gemm_gemv_slices(g) : gemm_skinny_splits(g);
+  B200_REQUIRE(gemv || splits >= 2, B200_ERR_UNSUPPORTED, "gemm(skinny): no K split for these arguments");
   const size_t need = (size_t)splits * (size_t)g.m * (size_t)g.n * sizeof(float);
   B200_REQUIRE(scratch != nullptr && scratch_bytes >= need, B200_ERR_WORKSPACE,
                "gemm(skinny): scratch of %zu bytes needed, %zu given", need, scratch_bytes);
   B200_REQUIRE(aligned_to(scratch, 16), B200_ERR_ALIGNMENT, "gemm(skinny): scratch not 16-byte aligned");
 
+  if (gemv) {
+    // Stage 1 on the CUDA cores: fp32 partial sums of every (column block, K slice).
+    const int32_t st = launch_gemm_gemv_partials(g, static_cast<float*>(scratch), splits, stream);
+    if (st != B200_OK) return st;
+  } else {
   // Stage 1: batched tensor-core GEMM, one batch per K slice, fp32 partials into the scratch.
   b200_gemm_args part = g;
   const int64_t ks = g.k / splits;
@@ -134,6 +143,7 @@ int32_t launch_gemm_skinny(const b200_gemm_args& g, void* scratch, size_t scratc
   B200_REQUIRE(why == nullptr, B200_ERR_UNSUPPORTED, "gemm(skinny): K slices not eligible: %s", why);
   int32_t st = launch_gemm_tcgen05(part, stream);
   if (st != B200_OK) return st;
+  }
 
   // Stage 2: add the slices and apply the epilogue.
   ReduceParams rp;
