@@ -80,7 +80,7 @@ def time_case(make_inputs, run, bytes_per_copy, iters, use_graph):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="gemm,gemm_fused,gemm_fp32_split,layer_norm,softmax,gelu,reduce,sdpa,sdpa_decode")
+    ap.add_argument("--ops", default="gemm,gemm_fused,gemm_fp32_routes,layer_norm,softmax,gelu,reduce,embedding,argmax,sdpa,sdpa_decode")
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--only", default="", help="substring filter on the case name")
     ap.add_argument("--no-graph", action="store_true", help="plain launches (what an ncu capture wants)")
@@ -142,14 +142,12 @@ def main():
                         bound = "tensor" if m >= 512 else "hbm"
                         report(name, us, rot, 2.0 * m * n * k, nbytes, bound)
 
-    if "gemm_fp32_split" in wanted:
-        # fp32 operands on the bf16 tensor cores: torch.set_float32_matmul_precision("high") makes the
-        # lowering split each operand into two bf16 terms and run three tensor-core GEMMs.
-        from torch_mojo_backend import aten_functions as af
-
+    if "gemm_fp32_routes" in wanted:
+        # fp32 operands: the exact CUDA-core route against the default (split precision on the tensor
+        # cores: operands as bf16 hi / lo halves, three products accumulated in fp32 by one launch).
         for m, k, n in ((8192, 768, 2304), (8192, 1600, 6400)):
-            for level in ("highest", "high"):
-                name = f"gemm_fp32_split {level} {m}x{k}x{n} B=nk +bias"
+            for label, route in (("exact", 1), ("split", 4)):
+                name = f"gemm_fp32_routes {label} {m}x{k}x{n} B=nk +bias"
                 if not keep(name):
                     continue
                 nbytes = 4 * (m * k + k * n + m * n + n)
@@ -157,13 +155,8 @@ def main():
                 def make(i, m=m, k=k, n=n):
                     return randn((m, k), torch.float32), randn((n, k), torch.float32, 0.05).t(), randn((n,), torch.float32, 0.02)
 
-                old_level = torch.get_float32_matmul_precision()
-                torch.set_float32_matmul_precision(level)
-                try:
-                    us, rot = time_case(make, lambda t: af.aten_addmm(t[2], t[0], t[1]), nbytes,
-                                        max(4, args.iters // 4), use_graph)
-                finally:
-                    torch.set_float32_matmul_precision(old_level)
+                us, rot = time_case(make, lambda t, route=route: ops.gemm(t[0], t[1], t[2], None, 1.0, 1.0, 0, None, route),
+                                    nbytes, max(4, args.iters // 4), use_graph)
                 report(name, us, rot, 2.0 * m * n * k, nbytes, "tensor")
 
     if "gemm_fused" in wanted:
@@ -267,8 +260,36 @@ def main():
                 us, rot = time_case(make, lambda t, op=op: ops.reduce(t[0], op), nbytes, args.iters, use_graph)
                 report(name, us, rot, nbytes=nbytes)
 
+    if "embedding" in wanted:
+        # token + positional embeddings of a GPT-2 XL batch: bf16 tables, fp32 residual stream out
+        for B, T, C in ((8, 1024, 1600), (64, 1024, 1600)):
+            name = f"embedding_sum bf16->fp32 {B}x{T}x{C}"
+            if not keep(name):
+                continue
+            nbytes = B * T * C * (2 + 2 + 4)
+            wte, wpe = randn((50257, C), torch.bfloat16, 0.02), randn((1024, C), torch.bfloat16, 0.02)
+            pos = torch.arange(T, device=dev)
+            make = lambda i, B=B, T=T: (torch.randint(0, 50257, (B, T), device=dev, generator=gen),)
+            us, rot = time_case(make, lambda t: ops.embedding_sum(wte, t[0], wpe, pos, torch.float32), nbytes, args.iters, use_graph)
+            report(name, us, rot, nbytes=nbytes)
+
+    if "argmax" in wanted:
+        # top-1 over the fp32 logits (50257 columns, padded pitch) of 8 and 64 sequences
+        for rows in (8192, 65536):
+            name = f"argmax fp32 {rows}x50257"
+            if not keep(name):
+                continue
+            nbytes = rows * 50257 * 4
+            reps = 1 if rows > 8192 else 2
+            make = lambda i, rows=rows: (randn((rows, 50264), torch.float32)[:, :50257],)
+            if rows > 8192:
+                one = make(0)
+                make = lambda i, one=one: one  # 13 GB: one copy, far larger than L2
+            us, rot = time_case(make, lambda t: ops.argmax(t[0]), nbytes, max(3, args.iters // 4), use_graph)
+            report(name, us, rot, nbytes=nbytes)
+
     if "sdpa" in wanted:
-        for B, H, T, D in ((8, 12, 1024, 64), (4, 25, 2048, 64), (8, 25, 1024, 64), (64, 25, 1024, 64)):
+        for B, H, T, D in ((8, 12, 1024, 64), (4, 25, 2048, 64), (8, 25, 1024, 64), (16, 25, 1024, 64), (64, 25, 1024, 64)):
             name = f"sdpa bf16 causal {B}x{H}x{T}x{D}"
             if not keep(name):
                 continue

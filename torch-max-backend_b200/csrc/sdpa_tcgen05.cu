@@ -118,6 +118,11 @@ __device__ unsigned long long g_probe[160][48];
 #define PROBE_ADD(n, t)
 #endif
 
+// The issuing warps' long waits (for the softmax group to hand over S or P: most of a unit's time)
+// back off between polls, so that the polling does not take issue slots from the softmax warps that
+// share their SM sub-partitions.
+#define ISSUER_WAIT ptx::mbar_wait_relaxed
+
 struct Item {
   int32_t q0;      // first query row of tile A; tile B starts at q0 + BM
   int32_t b, h;
@@ -307,7 +312,7 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const int qb = qk.items & 1;
       PROBE_T0(t0);
       // the group must have pulled its previous scores out of S_g
-      bool go = k_qk == 0 || ptx::mbar_wait(bar_s_free, (k_qk - 1) & 1, abort_flag);
+      bool go = k_qk == 0 || ISSUER_WAIT(bar_s_free, (k_qk - 1) & 1, abort_flag);
       PROBE_ADD(c_wait_a, t0);
       PROBE_T0(t1);
       if (qk.j == 0) go = go && ptx::mbar_wait(q_full(qb), (qk.items >> 1) & 1, abort_flag);
@@ -342,7 +347,7 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // scores of unit k + 1 first (the group released S_g at the start of unit k), then P V of unit k
         if (!issue_next_qk()) break;
         PROBE_T0(t0);
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_p_full, k_pv & 1, abort_flag))) break;
+        if (!__all_sync(0xffffffffu, ISSUER_WAIT(bar_p_full, k_pv & 1, abort_flag))) break;
         ptx::tc_fence_after_sync();
         PROBE_ADD(c_wait_p, t0);
         PROBE_T0(t2);

@@ -344,14 +344,18 @@ _PLACEHOLDERS: dict = {}
 def _placeholder(shape, dtype, device):
     """A zero tensor for the attention outputs that only a backward pass or dropout replay would
     read (philox seed / offset, debug mask). One per (shape, dtype, device), made once: filling a
-    fresh one per call costs a kernel launch per attention layer for values nobody reads."""
-    capturing = torch.device(device).type == "cuda" and torch.cuda.is_current_stream_capturing()
-    if torch._guards.detect_fake_mode() is not None or capturing:
-        return torch.zeros(shape, dtype=dtype, device=device)  # tracing / capture: nothing is cached
-    key = (tuple(shape), dtype, device)
+    fresh one per call costs a kernel launch per attention layer for values nobody reads. While a
+    CUDA graph is being captured the tensor made by the eager call that precedes every capture is
+    re-used (allocating inside the capture would put a fill kernel into the graph)."""
+    if torch._guards.detect_fake_mode() is not None:
+        return torch.zeros(shape, dtype=dtype, device=device)  # tracing: nothing is cached
+    key = (tuple(shape), dtype, torch.device(device))
     t = _PLACEHOLDERS.get(key)
     if t is None:
-        t = _PLACEHOLDERS[key] = torch.zeros(shape, dtype=dtype, device=device)
+        t = torch.zeros(shape, dtype=dtype, device=device)
+        capturing = torch.device(device).type == "cuda" and torch.cuda.is_current_stream_capturing()
+        if not capturing:
+            _PLACEHOLDERS[key] = t
     return t
 
 
