@@ -104,8 +104,9 @@ def export_to_max_graph(
         frozen[spec.arg.name] = value
 
     gm = exported_program.graph_module
+    # repack first: the fusion pass rewrites mm / addmm nodes into fused nodes this pass does not match
+    _repack_gemm_weights(gm.graph, frozen)
     if fusion.fusion_enabled():
         fusion.fuse_graph(gm)
-    _repack_gemm_weights(gm.graph, frozen)
     plan, blueprint = _GraphFactory(frozen).create_graph(gm.graph)
     return ExportedPlan(plan, blueprint, num_user_inputs, cuda_graph)

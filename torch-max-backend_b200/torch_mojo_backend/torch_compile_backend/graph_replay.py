@@ -41,8 +41,10 @@ class GraphRunner:
         self._outputs = None
         self._kernels = 0  # kernels of this library inside the captured graph
         self.replays = 0
+        self._eager_only = False
 
     def _reset(self):
+        self._eager_only = False
         self._graph = None
         self._static_args = None
         self._outputs = None
@@ -55,19 +57,23 @@ class GraphRunner:
         if sig != self._sig or not all(isinstance(a, torch.Tensor) and a.is_cuda or not isinstance(a, torch.Tensor) for a in args):
             self._sig = sig
             self._reset()
+        if self._eager_only:
+            return self.plan.run(args)
         if self._graph is None:
             if self._first_ptrs is None:
                 # first call with this signature: eager warm-up, remember addresses
                 self._first_ptrs = ptrs
                 return self.plan.run(args)
-            self._capture(args, ptrs)
+            if not self._try_capture(args, ptrs):
+                return self.plan.run(args)
         else:
             for i, p in self._pinned_ptrs.items():
                 if ptrs[i] != p:
                     # an argument assumed static moved: capture again with it as a copied input
                     self._first_ptrs = [None if j == i else q for j, q in enumerate(self._first_ptrs)]
                     self._graph = None
-                    self._capture(args, ptrs)
+                    if not self._try_capture(args, ptrs):
+                        return self.plan.run(args)
                     break
         for i in self._copy_idx:
             self._static_args[i].copy_(args[i], non_blocking=True)
@@ -75,6 +81,23 @@ class GraphRunner:
         self.replays += 1
         native.launch_count += self._kernels  # the replay launched them; the op wrappers did not run
         return self._outputs
+
+    def _try_capture(self, args, ptrs) -> bool:
+        """Captures the plan; a plan that cannot be captured (an op that synchronises, e.g.
+        `_local_scalar_dense`, `nonzero`, boolean-mask indexing) is latched to the eager launch plan
+        for this signature instead of failing on every call."""
+        try:
+            self._capture(args, ptrs)
+            return True
+        except Exception as e:  # noqa: BLE001 -- whatever the capture raised, the eager plan still works
+            import warnings
+
+            self._graph = None
+            self._eager_only = True
+            torch.cuda.synchronize()
+            warnings.warn(f"CUDA-graph capture of the launch plan failed ({type(e).__name__}: {e}); "
+                          "running this signature eagerly", RuntimeWarning, stacklevel=3)
+            return False
 
     def _capture(self, args, ptrs):
         self._copy_idx = tuple(
