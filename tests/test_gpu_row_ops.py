@@ -199,6 +199,33 @@ def test_gelu_reference_known_answers(ops, approximate):
         assert torch.equal(xin.cpu()[: len(bits)].view(torch.uint16), bits), "input must be untouched"
 
 
+@pytest.mark.parametrize("approximate", ["none", "tanh"])
+def test_gelu_bf16_every_bit_pattern(ops, approximate):
+    """All 65536 bf16 inputs against the formula evaluated in float64 and rounded once: the kernel's
+    approximations (MUFU ex2 / rcp, the erfc fit of the erf form) must land on the correctly rounded
+    bf16 value nearly everywhere and never more than one bf16 step away; NaN and infinity classes must
+    agree. Inputs whose exact result is subnormal, and the left tail where the float64 formula itself
+    cancels (x < -5.5), are held to an absolute bound instead."""
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.uint16)
+    x = bits.view(torch.bfloat16)
+    got = ops.gelu(x.cuda(), approximate).cpu()
+    assert torch.equal(x.view(torch.uint16), bits)
+    xd = x.double()
+    want64 = F.gelu(xd, approximate=approximate)
+    want = want64.to(torch.bfloat16)
+    finite_in = torch.isfinite(xd)
+    assert torch.equal(torch.isnan(got), torch.isnan(want))
+    assert torch.equal(torch.isposinf(got), torch.isposinf(want))
+    body = finite_in & (xd > -5.5) & (want64.abs() >= 2.0**-120) & torch.isfinite(want.float())
+    gb = got.view(torch.int16).to(torch.int32)[body]
+    wb = want.view(torch.int16).to(torch.int32)[body]
+    steps = (gb - wb).abs()
+    assert int(steps.max()) <= 1, f"{int((steps > 1).sum())} results more than one bf16 step off"
+    assert float((steps == 0).double().mean()) >= 0.999
+    rest = finite_in & ~body
+    assert float((got.double()[rest] - want64[rest]).abs().max()) < 1e-9
+
+
 def test_gelu_unaligned_offset(ops):
     base = gen((1000,), torch.float32, 22).cuda()
     x = base[3:900]  # 12-byte offset: vector path must not be taken blindly

@@ -249,16 +249,19 @@ def main():
                 report(name, us, rot, nbytes=nbytes)
 
     if "reduce" in wanted:
-        for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
-            for op, oname in ((0, "sum"), (1, "mean"), (2, "amax")):
-                name = f"reduce {oname} {dname} 8192x768"
-                if not keep(name):
-                    continue
-                s = 2 if dtype == torch.bfloat16 else 4
-                nbytes = 8192 * 768 * s
-                make = lambda i, dtype=dtype: (randn((8192, 768), dtype),)
-                us, rot = time_case(make, lambda t, op=op: ops.reduce(t[0], op), nbytes, args.iters, use_graph)
-                report(name, us, rot, nbytes=nbytes)
+        # [8192,768] is one hidden-state matrix of the small configuration (12 - 25 MB: a 4 - 6 us kernel,
+        # launch ramp included); [65536,1600] is the benchmark's, large enough to show the sustained rate.
+        for R, C in ((8192, 768), (65536, 1600)):
+            for dtype, dname in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+                for op, oname in ((0, "sum"), (1, "mean"), (2, "amax")):
+                    name = f"reduce {oname} {dname} {R}x{C}"
+                    if not keep(name):
+                        continue
+                    s = 2 if dtype == torch.bfloat16 else 4
+                    nbytes = R * C * s
+                    make = lambda i, dtype=dtype, R=R, C=C: (randn((R, C), dtype),)
+                    us, rot = time_case(make, lambda t, op=op: ops.reduce(t[0], op), nbytes, args.iters, use_graph)
+                    report(name, us, rot, nbytes=nbytes)
 
     if "embedding" in wanted:
         # token + positional embeddings of a GPT-2 XL batch: bf16 tables, fp32 residual stream out

@@ -385,85 +385,141 @@ struct RowMask {
   float fill;
 };
 
-// One warp per row, the row in registers. Values are moved to the base-2 exponent domain when
-// they are loaded (x * scale * log2(e)), so each element costs one subtract and one ex2 between
-// the two reductions; masking is decided per 16-byte chunk and only chunks that straddle the
-// causal limit (or rows that carry an explicit mask) look at single elements. A masked element is
-// -inf, which the exponential turns into an exact 0; a row with nothing visible gives NaN like
+// 16 raw bytes of a row (N elements of Tin) -> N fp32 values.
+template <typename Tin, int N>
+__device__ __forceinline__ void unpack_raw(const uint4& t, float (&v)[N]) {
+  if constexpr (sizeof(Tin) == 2) {
+    static_assert(sizeof(Tin) != 2 || N == 8, "16 bytes of bf16");
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+    static_assert(sizeof(Tin) != 4 || N == 4, "16 bytes of fp32");
+    v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y);
+    v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
+  }
+}
+
+// One warp per row, the row in registers; a warp walks rows with a grid stride and issues the
+// 16-byte loads of its NEXT row before it reduces the current one, so every resident warp keeps a
+// row of loads in flight through its arithmetic and store phases (without that the kernel waits
+// on memory latency at half the copy bandwidth). Values are moved to the base-2 exponent domain
+// when they are unpacked (x * scale * log2(e)), so each element costs one subtract and one ex2
+// between the two reductions; masking is decided per 16-byte chunk and only chunks that straddle
+// the causal limit (or rows that carry an explicit mask) look at single elements. A masked element
+// is -inf, which the exponential turns into an exact 0; a row with nothing visible gives NaN like
 // torch.
-template <typename Tin, typename Tout, int N, int MAXC>
-__global__ void __launch_bounds__(kRowThreads)
+// Registers that hold row data: the fp32 row, the raw next row and its mask bytes. The launch bound
+// asks for as many resident CTAs as leave those plus ~30 working registers per thread.
+constexpr int softmax_min_ctas(int n, int maxc, bool has_mask) {
+  const int live = maxc * n + maxc * 4 + (has_mask ? maxc * 2 : 0);
+  return live < 56 ? 6 : (live <= 72 ? 5 : 3);
+}
+
+template <typename Tin, typename Tout, int N, int MAXC, bool HAS_MASK>
+__global__ void __launch_bounds__(kRowThreads, softmax_min_ctas(N, MAXC, HAS_MASK))
 softmax_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t rows, int cols,
                     int64_t x_row_stride, float scale, int causal, int64_t q_len, RowMask mask) {
+  static_assert(N * sizeof(Tin) == 16, "one chunk is one 16-byte load");
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  const int64_t stride = (int64_t)gridDim.x * kWarpsPerCta;
+  int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int nchunks = cols / N;
-  int allowed = cols;
-  if (causal) {
-    const int64_t a = row % q_len + 1;
-    allowed = a < cols ? (int)a : cols;
-  }
-  const Tin* xr = x + row * x_row_stride;
-  const uint8_t* mr = mask.ptr != nullptr ? mask.ptr + (row % mask.rows) * mask.stride : nullptr;
   constexpr float kLog2e = 1.4426950408889634f;
   const float sl = scale * kLog2e;
   const float fill2 = mask.fill * kLog2e;
+  constexpr bool has_mask = HAS_MASK;
 
-  float v[MAXC][N];
-  float m = -INFINITY;
+  uint4 raw[MAXC];
+  uint64_t mraw[HAS_MASK ? MAXC : 1];
+  auto limit_of = [&](int64_t r) {
+    if (!causal) return cols;
+    const int64_t a = r % q_len + 1;
+    return a < cols ? (int)a : cols;
+  };
+  // Chunks entirely past the causal limit are never read.
+  auto fetch = [&](int64_t r, int allowed) {
+    const Tin* xr = x + r * x_row_stride;
+    const uint8_t* mr = has_mask ? mask.ptr + (r % mask.rows) * mask.stride : nullptr;
 #pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
-    const int c = lane + 32 * i;
-    // Chunks entirely past the causal limit are never read.
-    if (c < nchunks && c * N < allowed) {
-      Chunk<Tin, N>::load(xr + c * N, v[i]);
-#pragma unroll
-      for (int j = 0; j < N; ++j) v[i][j] *= sl;
-      if (c * N + N > allowed) {  // the chunk that straddles the limit
-#pragma unroll
-        for (int j = 0; j < N; ++j)
-          if (c * N + j >= allowed) v[i][j] = -INFINITY;
-      }
-      if (mr != nullptr) {
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunks && c * N < allowed) {
+        raw[i] = __ldcs(reinterpret_cast<const uint4*>(xr + c * N));
         // N mask bytes of this chunk (the launcher guarantees N-byte alignment of every chunk)
-        const uint64_t mbits = N == 8 ? *reinterpret_cast<const uint64_t*>(mr + c * N)
-                                      : (uint64_t) * reinterpret_cast<const uint32_t*>(mr + c * N);
-#pragma unroll
-        for (int j = 0; j < N; ++j)
-          if ((((mbits >> (8 * j)) & 0xffu) != 0) != (mask.invert != 0)) v[i][j] = fill2;
+        if constexpr (has_mask)
+          mraw[i] = N == 8 ? *reinterpret_cast<const uint64_t*>(mr + c * N)
+                           : (uint64_t) * reinterpret_cast<const uint32_t*>(mr + c * N);
       }
-#pragma unroll
-      for (int j = 0; j < N; ++j) m = nan_max(m, v[i][j]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < N; ++j) v[i][j] = -INFINITY;
     }
-  }
-  m = warp_max(m);
-  float s = 0.0f;
+  };
+
+  int allowed = limit_of(row);
+  fetch(row, allowed);
+  while (true) {
+    float v[MAXC][N];
+    float m = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunks && c * N < allowed) {
+        unpack_raw<Tin, N>(raw[i], v[i]);
 #pragma unroll
-    for (int j = 0; j < N; ++j) {
-      float e;
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v[i][j] - m));
-      v[i][j] = e;
-      s += e;
+        for (int j = 0; j < N; ++j) v[i][j] *= sl;
+        if (c * N + N > allowed) {  // the chunk that straddles the limit
+#pragma unroll
+          for (int j = 0; j < N; ++j)
+            if (c * N + j >= allowed) v[i][j] = -INFINITY;
+        }
+        if constexpr (has_mask) {
+          const uint64_t mbits = mraw[i];
+#pragma unroll
+          for (int j = 0; j < N; ++j)
+            if ((((mbits >> (8 * j)) & 0xffu) != 0) != (mask.invert != 0)) v[i][j] = fill2;
+        }
+#pragma unroll
+        for (int j = 0; j < N; ++j) m = nan_max(m, v[i][j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[i][j] = -INFINITY;
+      }
     }
-  }
-  s = warp_sum(s);
-  const float inv = 1.0f / s;
-  Tout* yr = y + row * (int64_t)cols;
+    const int64_t next = row + stride;
+    const int next_allowed = next < rows ? limit_of(next) : 0;
+    if (next < rows) fetch(next, next_allowed);
+
+    m = warp_max(m);
+    float s = 0.0f;
 #pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
-    const int c = lane + 32 * i;
-    if (c < nchunks) {
-      float o[N];
+    for (int i = 0; i < MAXC; ++i) {
 #pragma unroll
-      for (int j = 0; j < N; ++j) o[j] = v[i][j] * inv;
-      Chunk<Tout, N>::store(yr + c * N, o);
+      for (int j = 0; j < N; ++j) {
+        float e;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v[i][j] - m));
+        v[i][j] = e;
+        s += e;
+      }
     }
+    s = warp_sum(s);
+    const float inv = 1.0f / s;
+    Tout* yr = y + row * (int64_t)cols;
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunks) {
+        float o[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = v[i][j] * inv;
+        Chunk<Tout, N>::store(yr + c * N, o);
+      }
+    }
+    if (next >= rows) break;
+    row = next;
+    allowed = next_allowed;
   }
 }
 
@@ -498,6 +554,15 @@ __global__ void softmax_block_kernel(const Tin* __restrict__ x, Tout* __restrict
   }
 }
 
+int softmax_rows_per_warp() {
+  static const int r = [] {
+    const char* e = std::getenv("B200_SOFTMAX_ROWS_PER_WARP");
+    const int v = e != nullptr ? std::atoi(e) : 0;
+    return v >= 1 && v <= 64 ? v : 4;
+  }();
+  return r;
+}
+
 template <typename Tin, typename Tout>
 int32_t launch_softmax(const void* x, void* y, int64_t rows, int64_t cols, int64_t x_row_stride,
                        float scale, int causal, int64_t q_len, RowMask mask, cudaStream_t stream) {
@@ -511,10 +576,21 @@ int32_t launch_softmax(const void* x, void* y, int64_t rows, int64_t cols, int64
                       (mask.ptr == nullptr || (aligned_to(mask.ptr, N) && mask.stride % N == 0));
   if (vec_ok) {
     const int per_lane = (int)((cols / N + 31) / 32);
-    const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
-#define SM_LAUNCH(MAXC)                                                              \
-  softmax_warp_kernel<Tin, Tout, N, MAXC><<<grid, kRowThreads, 0, stream>>>(           \
-      xp, yp, rows, (int)cols, x_row_stride, scale, causal, q_len, mask)
+    // Rows per warp: one while that fills the GPU less than four times over, then up to
+    // kSoftmaxRowsPerWarp so that the prefetch of the next row has something to overlap.
+    const int64_t ctas_1 = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int64_t ctas_r = (ctas_1 + softmax_rows_per_warp() - 1) / softmax_rows_per_warp();
+    const int64_t floor_ctas = (int64_t)sm_count() * 32;
+    const unsigned grid = (unsigned)(ctas_1 <= floor_ctas ? ctas_1 : (ctas_r > floor_ctas ? ctas_r : floor_ctas));
+#define SM_LAUNCH(MAXC)                                                                      \
+  do {                                                                                       \
+    if (mask.ptr != nullptr)                                                                 \
+      softmax_warp_kernel<Tin, Tout, N, MAXC, true><<<grid, kRowThreads, 0, stream>>>(       \
+          xp, yp, rows, (int)cols, x_row_stride, scale, causal, q_len, mask);                \
+    else                                                                                     \
+      softmax_warp_kernel<Tin, Tout, N, MAXC, false><<<grid, kRowThreads, 0, stream>>>(      \
+          xp, yp, rows, (int)cols, x_row_stride, scale, causal, q_len, mask);                \
+  } while (0)
     if (per_lane <= 1) SM_LAUNCH(1);
     else if (per_lane <= 2) SM_LAUNCH(2);
     else if (per_lane <= 4) SM_LAUNCH(4);
@@ -555,6 +631,36 @@ __device__ __forceinline__ float gelu_tanh_mufu(float x) {
   return x * r;
 }
 
+// erf form for two bf16-bound values at once: 0.5 x (1 + erf(x / sqrt 2)) = x * (x < 0 ? h : 1 - h) with
+//   h = 0.5 erfc(|x| / sqrt 2) = t Q(t) exp(-x^2 / 2),   t = 1 / (1 + |x| / (2 sqrt 2)),
+// Q a degree-7 minimax fit (relative error of h 3.1e-6, a hundredth of a bf16 rounding step; over all
+// 65536 bf16 inputs the rounded result equals the correctly rounded one wherever the exact result is
+// a normal number). Two MUFU operations and packed two-wide FMAs per element in place of erff's two
+// polynomial branches, which is what lets the bf16 kernel run at memory speed. Because h keeps its
+// relative accuracy in the left tail, x < -5.6 gives the tiny true value where the fp32 formula's
+// 1 + erf cancels to -0. +inf -> +inf (inf * 1), -inf -> NaN (-inf * 0), NaN -> NaN, +-0 -> +-0.
+__device__ __forceinline__ float2 gelu_erf_pair(float2 x) {
+  const float kHalfInvSqrt2 = 0.35355339059327373f;
+  float2 t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.x) : "f"(fmaf(fabsf(x.x), kHalfInvSqrt2, 1.0f)));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.y) : "f"(fmaf(fabsf(x.y), kHalfInvSqrt2, 1.0f)));
+  constexpr float q[8] = {1.410478354e-01f, 1.409928650e-01f, 1.244906485e-01f, 8.064989746e-02f,
+                          6.382267177e-02f, -2.228422835e-02f, -5.376151577e-02f, 2.504315786e-02f};
+  float2 acc = make_float2(q[7], q[7]);
+#pragma unroll
+  for (int i = 6; i >= 0; --i) acc = __ffma2_rn(acc, t, make_float2(q[i], q[i]));
+  const float kNegHalfLog2e = -0.7213475204444817f;
+  const float2 arg = __fmul2_rn(__fmul2_rn(x, x), make_float2(kNegHalfLog2e, kNegHalfLog2e));
+  float2 e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(arg.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(arg.y));
+  const float2 h = __fmul2_rn(__fmul2_rn(t, acc), e);
+  float2 w = __ffma2_rn(h, make_float2(-1.0f, -1.0f), make_float2(1.0f, 1.0f));
+  w.x = x.x < 0.0f ? h.x : w.x;
+  w.y = x.y < 0.0f ? h.y : w.y;
+  return __fmul2_rn(x, w);
+}
+
 template <typename T>
 __device__ __forceinline__ float gelu_tanh_for(float x) {
   return sizeof(T) == 2 ? gelu_tanh_mufu(x) : gelu_tanh_fast(x);
@@ -579,8 +685,17 @@ gelu_vec_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nvec) {
   for (int u = 0; u < kGeluUnroll; ++u) {
     const int64_t i = base + (int64_t)u * kGeluThreads;
     if (i < nvec) {
+      if constexpr (!kTanh && sizeof(T) == 2) {
 #pragma unroll
-      for (int j = 0; j < N; ++j) v[u][j] = kTanh ? gelu_tanh_for<T>(v[u][j]) : gelu_erf_f32(v[u][j]);
+        for (int j = 0; j < N; j += 2) {
+          const float2 r = gelu_erf_pair(make_float2(v[u][j], v[u][j + 1]));
+          v[u][j] = r.x;
+          v[u][j + 1] = r.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[u][j] = kTanh ? gelu_tanh_for<T>(v[u][j]) : gelu_erf_f32(v[u][j]);
+      }
       store16_stream(y + i * N, v[u]);
     }
   }
@@ -592,7 +707,10 @@ __global__ void gelu_scalar_kernel(const T* __restrict__ x, T* __restrict__ y, i
   const int64_t i = start + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < numel) {
     const float v = Elem<T>::to_f32(x[i]);
-    y[i] = Elem<T>::from_f32(kTanh ? gelu_tanh_for<T>(v) : gelu_erf_f32(v));
+    float r;
+    if constexpr (!kTanh && sizeof(T) == 2) r = gelu_erf_pair(make_float2(v, v)).x;
+    else r = kTanh ? gelu_tanh_for<T>(v) : gelu_erf_f32(v);
+    y[i] = Elem<T>::from_f32(r);
   }
 }
 
@@ -642,23 +760,24 @@ reduce_warp_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int64_t rows
   if (row >= rows) return;
   const int nchunks = cols / N;
   const Tin* xr = x + row * x_row_stride;
-  // Four independent accumulators keep four 16-byte loads in flight per lane.
+  // Four independent accumulators and four predicated 16-byte loads per lane and step: a short row
+  // (fewer than 128 chunks) still has all of its loads in flight at once.
   float acc[4] = {red_init<OP>(), red_init<OP>(), red_init<OP>(), red_init<OP>()};
-  int c = lane;
-  for (; c + 96 < nchunks; c += 128) {
+  for (int c = lane; c < nchunks; c += 128) {
     float v[4][N];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) load16_stream(xr + (c + 32 * u) * N, v[u]);
+    for (int u = 0; u < 4; ++u) {
+      if (c + 32 * u < nchunks) {
+        load16_stream(xr + (c + 32 * u) * N, v[u]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[u][j] = red_init<OP>();
+      }
+    }
 #pragma unroll
     for (int u = 0; u < 4; ++u)
 #pragma unroll
       for (int j = 0; j < N; ++j) acc[u] = red_step<OP>(acc[u], v[u][j]);
-  }
-  for (; c < nchunks; c += 32) {
-    float v[N];
-    load16_stream(xr + c * N, v);
-#pragma unroll
-    for (int j = 0; j < N; ++j) acc[0] = red_step<OP>(acc[0], v[j]);
   }
   float r = red_step<OP>(red_step<OP>(acc[0], acc[1]), red_step<OP>(acc[2], acc[3]));
   r = OP == B200_REDUCE_AMAX ? warp_max(r) : warp_sum(r);
