@@ -135,6 +135,53 @@ B200_API int32_t b200_reduce_lastdim(const void* x, void* y, int64_t rows, int64
                             int64_t x_row_stride, int32_t op, int32_t in_dtype,
                             int32_t out_dtype, b200_stream_t stream);
 
+/* ---- backward of the row kernels (HBM bound) ------------------------------------------- */
+
+/* dx = dy * gelu'(x) over numel contiguous elements, erf or tanh form; one dtype for all three.
+ * Replaces: aten_gelu_backward (torch_mojo_backend/aten_functions.py:2070-2102) and
+ * _gelu_backward_{exact,tanh}[_bf16]
+ * (torch_mojo_backend/eager_kernels/activation_backward_ops.mojo:60-130). */
+B200_API int32_t b200_gelu_backward(const void* dy, const void* x, void* dx, int64_t numel,
+                           int32_t approximate_tanh, int32_t dtype, b200_stream_t stream);
+
+/* dx[rows, cols] = scale * y * (dy - sum_j dy_j y_j) along the last dim: the backward of a row
+ * softmax whose input had been multiplied by scale (aten._softmax_backward_data has scale 1).
+ * dy and y have unit column stride and the given row strides; dx is contiguous.
+ * Replaces: the softmax backward of the reference's decomposed attention
+ * (torch_mojo_backend/eager_kernels/sdpa_backward_ops.mojo:28-78). */
+B200_API int32_t b200_softmax_backward(const void* dy, const void* y, void* dx, int64_t rows,
+                              int64_t cols, int64_t dy_row_stride, int64_t y_row_stride,
+                              float scale, int32_t in_dtype, int32_t out_dtype,
+                              b200_stream_t stream);
+
+/* LayerNorm backward over x[rows, cols] with the forward's mean and rstd (fp32 [rows]):
+ *   dx = rstd (g - mean_j g - xhat mean_j(g xhat)),  xhat = (x - mean) rstd,  g = dy gamma,
+ *   dgamma = sum_rows dy xhat,  dbeta = sum_rows dy   (fp32 sums in a fixed order).
+ * gamma may be NULL (ones); dgamma / dbeta may be NULL (not wanted) and are written in
+ * param_dtype; dx is contiguous and has the dtype of dy. The workspace holds the per-CTA column
+ * sums (b200_layer_norm_backward_workspace_bytes, 16-byte aligned).
+ * Replaces: the decomposition of aten.native_layer_norm_backward
+ * (torch_mojo_backend/aten_functions.py:2871) and the reference's eager kernels
+ * _dx_warp_rows (torch_mojo_backend/eager_kernels/normalization_backward_dx.mojo:66-175) and
+ * _partial_kernel / _final_kernel
+ * (torch_mojo_backend/eager_kernels/normalization_backward_params.mojo:75-180). */
+B200_API size_t b200_layer_norm_backward_workspace_bytes(int64_t rows, int64_t cols);
+B200_API int32_t b200_layer_norm_backward(const void* dy, const void* x, const float* mean,
+                                 const float* rstd, const void* gamma, void* dx, void* dgamma,
+                                 void* dbeta, void* workspace, size_t workspace_bytes,
+                                 int64_t rows, int64_t cols, int64_t dy_row_stride,
+                                 int64_t x_row_stride, int32_t x_dtype, int32_t dy_dtype,
+                                 int32_t param_dtype, int32_t dx_dtype, b200_stream_t stream);
+
+/* y[cols] = sum over the rows of x[rows, cols] (unit column stride): the bias gradient of a linear
+ * layer, aten.sum(dy, [0]). fp32 accumulation in a fixed order; workspace as above.
+ * Replaces: aten_sum over a leading dim (torch_mojo_backend/aten_functions.py:3310-3346) and the
+ * bias sum of aten_linear_backward (torch_mojo_backend/aten_functions.py:2323-2380). */
+B200_API size_t b200_sum_rows_workspace_bytes(int64_t rows, int64_t cols, int32_t in_dtype);
+B200_API int32_t b200_sum_rows(const void* x, void* y, void* workspace, size_t workspace_bytes,
+                      int64_t rows, int64_t cols, int64_t x_row_stride, int32_t in_dtype,
+                      int32_t out_dtype, b200_stream_t stream);
+
 /* ---- index-driven row kernels (HBM bound) ---------------------------------------------- */
 
 /* out[r, :] = table_a[idx_a[r], :] (+ table_b[idx_b[r % idx_b_len], :]) for r < rows: an embedding

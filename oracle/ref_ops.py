@@ -119,6 +119,72 @@ def gelu(x, approximate="none"):
     return _out(y, x.dtype)
 
 
+def gelu_backward(dy, x, approximate="none"):
+    """dy * gelu'(x), formulas of the reference's kernels
+    (torch_mojo_backend/eager_kernels/activation_backward_ops.mojo:44-72: exact
+    Phi(x) + x phi(x); tanh 0.5 (1 + t) + 0.5 x (1 - t^2) beta (1 + 3 kappa x^2))."""
+    a, g = _np(x), _np(dy)
+    with np.errstate(invalid="ignore", over="ignore"):
+        if approximate == "tanh":
+            beta, kappa = math.sqrt(2.0 / math.pi), 0.044715
+            t = np.tanh(beta * (a + kappa * a * a * a))
+            d = 0.5 * (1.0 + t) + 0.5 * a * (1.0 - t * t) * beta * (1.0 + 3.0 * kappa * a * a)
+        else:
+            d = 0.5 * (1.0 + _erf(a / math.sqrt(2.0))) + a * np.exp(-0.5 * a * a) / math.sqrt(2.0 * math.pi)
+    return _out(g * d, x.dtype)
+
+
+# ---- backward of the row kernels ----------------------------------------------------------------
+def softmax_backward(dy, y, scale=1.0, out_dtype=None):
+    """scale * y * (dy - sum_j dy_j y_j) over the last dim: aten._softmax_backward_data (scale 1), and
+    with the score scale folded in, the softmax backward of the reference's decomposed attention
+    (torch_mojo_backend/eager_kernels/sdpa_backward_ops.mojo:28-78)."""
+    g, p = _np(dy), _np(y)
+    return _out(scale * p * (g - (g * p).sum(-1, keepdims=True)), out_dtype or y.dtype)
+
+
+def layer_norm_backward(dy, x, mean, rstd, weight):
+    """(dx, dgamma, dbeta) from the forward's statistics
+    (torch_mojo_backend/eager_kernels/normalization_backward_dx.mojo:66-175 for dx,
+    normalization_backward_params.mojo:75-180 for the parameter sums):
+    xhat = (x - mean) rstd, g = dy gamma, dx = rstd (g - mean(g) - xhat mean(g xhat)),
+    dgamma = sum_rows dy xhat, dbeta = sum_rows dy."""
+    cols = x.shape[-1]
+    a, g = _np(x).reshape(-1, cols), _np(dy).reshape(-1, cols)
+    mu, rs = _np(mean).reshape(-1, 1), _np(rstd).reshape(-1, 1)
+    xh = (a - mu) * rs
+    gg = g * (_np(weight) if weight is not None else 1.0)
+    dx = rs * (gg - gg.mean(-1, keepdims=True) - xh * (gg * xh).mean(-1, keepdims=True))
+    pd = weight.dtype if weight is not None else x.dtype
+    return _out(dx.reshape(x.shape), dy.dtype), _out((g * xh).sum(0), pd), _out(g.sum(0), pd)
+
+
+def sum_rows(x, out_dtype=None):
+    """Sum over every dim but the last (a bias gradient; torch_mojo_backend/aten_functions.py:2323-2380)."""
+    return _out(_np(x).reshape(-1, x.shape[-1]).sum(0), out_dtype or x.dtype)
+
+
+def sdpa_backward(d_out, q, k, v, causal=False, scale=None):
+    """(dq, dk, dv) of softmax(scale q k^T [+ causal mask]) v in float64: P recomputed, dV = P^T dO,
+    dP = dO V^T, dS = scale P (dP - rowsum(dP P)), dQ = dS K, dK = dS^T Q (the math of
+    torch_mojo_backend/eager_flash_attention/fa4_bwd_kernel.mojo)."""
+    Q, K, V, dO = _np(q), _np(k), _np(v), _np(d_out)
+    T, S, D = Q.shape[-2], K.shape[-2], Q.shape[-1]
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+    s = np.einsum("...td,...sd->...ts", Q, K) * scale
+    if causal:
+        s = np.where(np.tril(np.ones((T, S), dtype=bool)), s, -np.inf)
+    s = s - s.max(-1, keepdims=True)
+    p = np.exp(s)
+    p = p / p.sum(-1, keepdims=True)
+    dv = np.einsum("...ts,...td->...sd", p, dO)
+    dp = np.einsum("...td,...sd->...ts", dO, V)
+    ds = scale * p * (dp - (dp * p).sum(-1, keepdims=True))
+    dq = np.einsum("...ts,...sd->...td", ds, K)
+    dk = np.einsum("...ts,...td->...sd", ds, Q)
+    return _out(dq, q.dtype), _out(dk, k.dtype), _out(dv, v.dtype)
+
+
 # ---- reductions -------------------------------------------------------------------------------
 def reduce(x, op, dim=None, keepdim=False, out_dtype=None):
     """sum / mean / amax over `dim` (list, int or None = all dims).

@@ -1,0 +1,206 @@
+"""GPU parity of the backward kernels (GELU, row softmax, LayerNorm, bias sum), of the GEMM layouts
+a weight gradient needs (A stored transposed), of the attention backward built from them, and of a
+compiled training step, against the CPU oracle / CPU eager autograd."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+from conftest import assert_parity
+
+from oracle import ref_ops
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def gen(shape, dtype, seed=0, mean=0.0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std + mean).to(dtype)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from torch_mojo_backend import ops as _ops
+
+    return _ops
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("approximate", ["none", "tanh"])
+@pytest.mark.parametrize("shape", [(8192, 3072), (257,), (3, 5, 7), (1,)])
+def test_gelu_backward(ops, dtype, approximate, shape):
+    x = gen(shape, dtype, 41, std=2.0)
+    dy = gen(shape, dtype, 42)
+    dx = ops.gelu_backward(dy.cuda(), x.cuda(), approximate)
+    assert dx.dtype == dtype and dx.shape == x.shape
+    if x.numel() > 100000:
+        want = torch.ops.aten.gelu_backward(dy.float(), x.float(), approximate=approximate).to(dtype)
+    else:
+        want = ref_ops.gelu_backward(dy, x, approximate)
+    assert_parity(dx, want, bf16=dtype == torch.bfloat16)
+
+
+def test_gelu_backward_unaligned_offset_and_special_values(ops):
+    base_x, base_g = gen((1000,), torch.float32, 43).cuda(), gen((1000,), torch.float32, 44).cuda()
+    x, dy = base_x[3:900], base_g[3:900]  # 12-byte offset: the vector path must not be taken blindly
+    assert_parity(ops.gelu_backward(dy, x, "tanh"), ref_ops.gelu_backward(dy.cpu(), x.cpu(), "tanh"), bf16=False)
+    x = torch.tensor([0.0, -0.0, 30.0, -30.0, float("inf"), float("-inf"), float("nan")]).cuda()
+    dy = torch.ones_like(x)
+    for approximate in ("none", "tanh"):
+        got = ops.gelu_backward(dy, x, approximate).cpu()
+        assert got[0] == 0.5 and got[1] == 0.5 and got[2] == 1.0 and abs(float(got[3])) < 1e-6
+        assert torch.isnan(got[6])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(96, 1024, 1024), (33, 65), (4, 6, 9), (2, 9000), (600, 4)])
+def test_softmax_backward(ops, dtype, shape):
+    if shape[0] == 96:
+        g = torch.Generator(device="cuda").manual_seed(45)
+        y = torch.softmax(torch.randn(shape, generator=g, device="cuda"), -1).to(dtype)
+        dy = torch.randn(shape, generator=g, device="cuda").to(dtype)
+        dx = ops.softmax_backward(dy, y, 0.125)
+        sl = (slice(5, 6), slice(100, 164))
+        assert_parity(dx[sl], ref_ops.softmax_backward(dy[sl].cpu(), y[sl].cpu(), 0.125), bf16=dtype == torch.bfloat16)
+        # every row of the full-size result sums to (almost) zero: sum_j y_j (dy_j - dot) = dot - dot
+        assert float(dx.float().sum(-1).abs().max()) < (2e-2 if dtype == torch.bfloat16 else 1e-5)
+        return
+    y = torch.softmax(gen(shape, torch.float32, 46), -1).to(dtype)
+    dy = gen(shape, dtype, 47)
+    dx = ops.softmax_backward(dy.cuda(), y.cuda())
+    assert dx.dtype == dtype
+    assert_parity(dx, ref_ops.softmax_backward(dy, y), bf16=dtype == torch.bfloat16)
+
+
+def test_softmax_backward_mixed_dtypes_and_strided_rows(ops):
+    y = torch.softmax(gen((64, 256), torch.float32, 48), -1)
+    dy = gen((64, 256), torch.float32, 49)
+    dx = ops.softmax_backward(dy.cuda(), y.cuda(), 0.5, torch.bfloat16)  # fp32 operands, bf16 result
+    assert dx.dtype == torch.bfloat16
+    assert_parity(dx, ref_ops.softmax_backward(dy, y, 0.5, torch.bfloat16), bf16=True)
+    big_y, big_g = torch.softmax(gen((64, 1024), torch.float32, 50), -1).cuda(), gen((64, 1024), torch.float32, 51).cuda()
+    ys, gs = big_y[:, 128:384], big_g[:, 256:512]  # row stride 1024, 256 columns
+    ys = ys / ys.sum(-1, keepdim=True)
+    assert_parity(ops.softmax_backward(gs, ys), ref_ops.softmax_backward(gs.cpu(), ys.cpu()), bf16=False)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(8192, 768), (8192, 1600), (33, 40), (5, 7), (3, 5000), (2, 3, 64), (1, 8), (700, 4096)])
+def test_layer_norm_backward(ops, dtype, shape):
+    cols = shape[-1]
+    x = gen(shape, dtype, 52)
+    dy = gen(shape, dtype, 53)
+    w = gen((cols,), dtype, 54, mean=1.0, std=0.2)
+    _, mean, rstd = ref_ops.layer_norm(x, [cols], w, None, 1e-5)
+    dx, dgamma, dbeta = ops.layer_norm_backward(dy.cuda(), x.cuda(), mean.cuda(), rstd.cuda(), w.cuda())
+    rdx, rdgamma, rdbeta = ref_ops.layer_norm_backward(dy, x, mean, rstd, w)
+    assert dx.dtype == dtype and dgamma.dtype == dtype and dx.shape == x.shape and dgamma.shape == (cols,)
+    bf = dtype == torch.bfloat16
+    assert_parity(dx, rdx, bf16=bf, what="dx")
+    assert_parity(dgamma, rdgamma, bf16=bf, what="dgamma")
+    assert_parity(dbeta, rdbeta, bf16=bf, what="dbeta")
+
+
+def test_layer_norm_backward_mixed_dtypes_no_weight_and_determinism(ops):
+    x = gen((4096, 1600), torch.float32, 55)      # fp32 residual stream
+    dy = gen((4096, 1600), torch.bfloat16, 56)    # bf16 gradient of the GEMM operand
+    w = gen((1600,), torch.float32, 57, mean=1.0, std=0.2)
+    _, mean, rstd = ref_ops.layer_norm(x, [1600], w, None, 1e-5)
+    args = (dy.cuda(), x.cuda(), mean.cuda(), rstd.cuda(), w.cuda())
+    dx, dgamma, dbeta = ops.layer_norm_backward(*args)
+    assert dx.dtype == torch.bfloat16 and dgamma.dtype == torch.float32
+    rdx, rdgamma, rdbeta = ref_ops.layer_norm_backward(dy, x, mean, rstd, w)
+    assert_parity(dx, rdx, bf16=True)
+    assert_parity(dgamma, rdgamma, bf16=False)
+    assert_parity(dbeta, rdbeta, bf16=False)
+    again = ops.layer_norm_backward(*args)
+    assert torch.equal(again[1], dgamma) and torch.equal(again[2], dbeta), "fixed-order sums: bit-identical reruns"
+    dx2, dg2, db2 = ops.layer_norm_backward(args[0], args[1], args[2], args[3], None, False, False)
+    assert dg2 is None and db2 is None
+    assert_parity(dx2, ref_ops.layer_norm_backward(dy, x, mean, rstd, None)[0], bf16=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(65536, 1600), (8192, 6400), (33, 65), (5, 4), (1, 8), (300, 5000)])
+def test_sum_rows(ops, dtype, shape):
+    x = gen(shape, dtype, 58)
+    y = ops.sum_rows(x.cuda(), torch.float32)
+    assert y.shape == (shape[-1],) and y.dtype == torch.float32
+    assert_parity(y, x.double().sum(0).float(), bf16=False, scale=float(shape[0]) ** 0.5 * 4)
+    assert torch.equal(ops.sum_rows(x.cuda(), torch.float32), y)
+
+
+@pytest.mark.parametrize("b_layout", ["kn", "nk"])
+@pytest.mark.parametrize("m,n,k", [(768, 2304, 8192), (1600, 6400, 4096), (200, 136, 520), (64, 768, 4096), (130, 72, 64)])
+def test_gemm_with_transposed_a(ops, b_layout, m, n, k):
+    """A weight gradient dW = X^T dY: A is the [m, k] view of a [k, m] tensor (m contiguous)."""
+    from torch_mojo_backend import native
+
+    at = gen((k, m), torch.bfloat16, 59)          # stored transposed
+    b = gen((k, n), torch.bfloat16, 60) if b_layout == "kn" else gen((n, k), torch.bfloat16, 60).t()
+    want = at.t().double() @ b.double()
+    if m % 8 == 0:  # a 16-byte column pitch: the tensor-core kernel takes A as it lies
+        got = ops.gemm(at.cuda().t(), b.cuda(), None, None, 1.0, 1.0, 0, torch.float32, native.ROUTE_TCGEN05)
+        assert_parity(got, want.float(), bf16=False, scale=float(want.abs().max()) * 20)  # bf16 operands, fp32 sums
+    auto = ops.gemm(at.cuda().t(), b.cuda(), None, None, 1.0, 1.0, 0, torch.float32)
+    assert_parity(auto, want.float(), bf16=False, scale=float(want.abs().max()) * 20)
+
+
+def test_batched_gemm_with_transposed_a(ops):
+    at = gen((6, 256, 192), torch.bfloat16, 61)   # [batch, k, m]
+    b = gen((6, 256, 64), torch.bfloat16, 62)     # [batch, k, n]
+    got = ops.gemm(at.cuda().transpose(1, 2), b.cuda(), None, None, 1.0, 1.0, 0, torch.float32)
+    want = at.transpose(1, 2).double() @ b.double()
+    assert_parity(got, want.float(), bf16=False, scale=float(want.abs().max()) * 20)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_backward(dtype, causal):
+    from torch_mojo_backend import aten_functions as af
+
+    B, H, T, D = 2, 3, 256, 64
+    q, k, v, d_out = (gen((B, H, T, D), dtype, 63 + i, std=0.7) for i in range(4))
+    dq, dk, dv, _ = af._sdpa_backward(d_out.cuda(), q.cuda(), k.cuda(), v.cuda(), None, causal, None)
+    want = ref_ops.sdpa_backward(d_out, q, k, v, causal)
+    for got, ref, name in zip((dq, dk, dv), want, "qkv"):
+        assert got.dtype == dtype and got.shape == ref.shape
+        assert_parity(got, ref, bf16=dtype == torch.bfloat16, what=f"d{name}")
+
+
+@pytest.mark.parametrize("attention", ["sdpa", "masked_softmax"])
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_compiled_training_step_matches_cpu_autograd(attention, precision, reset_compiler):
+    """Loss and every parameter gradient of a GPT-2 training step compiled with the backend against
+    fp32 CPU eager autograd of the same model; the backward graph must run the library's kernels."""
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+    from torch_mojo_backend import mojo_backend, native
+
+    cfg = GPTConfig(vocab_size=512, block_size=128, n_layer=2, n_head=4, n_embd=256)
+    ref = GPT2(cfg, attention).init_weights(0).train()
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 512, (4, 128), generator=g)
+    targets = torch.randint(0, 512, (4, 128), generator=g)
+    F.cross_entropy(ref(ids).reshape(-1, 512).float(), targets.reshape(-1)).backward()
+    want = {n: p.grad.clone() for n, p in ref.named_parameters()}
+
+    model = GPT2(cfg, attention).init_weights(0).train().cuda().set_precision(precision)
+    compiled = torch.compile(model, backend=mojo_backend)
+    before = native.launch_count
+    loss = F.cross_entropy(compiled(ids.cuda()).reshape(-1, 512).float(), targets.cuda().reshape(-1))
+    loss.backward()
+    assert native.launch_count - before > 40, "forward and backward ran on the library's kernels"
+    ref_loss = F.cross_entropy(ref(ids).reshape(-1, 512).float(), targets.reshape(-1))
+    bf = precision == "bf16"
+    torch.testing.assert_close(loss.cpu(), ref_loss, rtol=2e-2 if bf else 1e-4, atol=2e-2 if bf else 1e-4)
+    got = {n: p.grad for n, p in model.named_parameters()}
+    assert got.keys() == want.keys()
+    for name in want:
+        assert got[name] is not None, name
+        # gradients of a bf16 model are judged against the scale of the tensor (the parity bar of
+        # the forward, applied to the gradient); fp32 against the fp32 bar times the depth of the chain
+        scale = float(want[name].abs().max())
+        tol = (6e-2 if bf else 2e-3) * max(scale, 1e-8)
+        err = float((got[name].float().cpu() - want[name]).abs().max())
+        assert err <= tol, f"{name}: max error {err:.3e} against scale {scale:.3e}"

@@ -147,3 +147,33 @@ def test_gpt2_tiny_golden(golden, attention):
     assert next(model.h[0].attn.c_attn.parameters()).dtype == torch.bfloat16  # oracle left the model alone
     rel = (ref - t(golden[f"gpt_logits_{attention}"])).norm() / t(golden[f"gpt_logits_{attention}"]).norm()
     assert rel < 2e-2
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_backward_oracle_matches_torch_autograd(seed):
+    """The backward restatements against PyTorch CPU autograd of the forward ops (the reference pins
+    its backward kernels the same way, tests/test_eager_kernels.py: gradients vs torch eager)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(13, 40, generator=g, requires_grad=True)
+    dy = torch.randn(13, 40, generator=g)
+    for approximate in ("none", "tanh"):
+        (want,) = torch.autograd.grad(F.gelu(x, approximate=approximate), x, dy)
+        close(ref_ops.gelu_backward(dy, x.detach(), approximate), want, atol=2e-6)
+    y = torch.softmax(x * 0.3, -1)
+    (want,) = torch.autograd.grad(y, x, dy)
+    close(ref_ops.softmax_backward(dy, y.detach(), 0.3), want, atol=1e-6)
+    w = torch.randn(40, generator=g, requires_grad=True)
+    b = torch.randn(40, generator=g, requires_grad=True)
+    out, mean, rstd = torch.native_layer_norm(x, (40,), w, b, 1e-5)
+    want = torch.autograd.grad(out, (x, w, b), dy)
+    got = ref_ops.layer_norm_backward(dy, x.detach(), mean.detach(), rstd.detach(), w.detach())
+    for a, e in zip(got, want):
+        close(a, e, atol=2e-5)
+    close(ref_ops.sum_rows(dy), dy.sum(0), atol=1e-5)
+    q, k, v = (torch.randn(2, 3, 9, 8, generator=g, requires_grad=True) for _ in range(3))
+    d_out = torch.randn(2, 3, 9, 8, generator=g)
+    for causal in (False, True):
+        want = torch.autograd.grad(F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=0.4), (q, k, v), d_out)
+        got = ref_ops.sdpa_backward(d_out, q.detach(), k.detach(), v.detach(), causal, 0.4)
+        for a, e in zip(got, want):
+            close(a, e, atol=2e-6)

@@ -1,0 +1,138 @@
+"""A training step (forward + backward) through the backend on a CPU-only box. The kernel ops are
+replaced by torch stand-ins (installed by the test, never shipped), which checks the wiring of the
+backward lowerings -- which aten nodes stay whole, operand order, dtypes, shapes, transposed GEMM
+operands -- against plain eager autograd."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from test_fusion_cpu import _StandIns
+from torch_mojo_backend import aten_functions as af
+from torch_mojo_backend import mojo_backend
+
+
+class _TrainingStandIns(_StandIns):
+    @staticmethod
+    def layer_norm(x, w, b, eps, out_dtype=None):
+        xf = x.float()
+        mean = xf.mean(-1)
+        rstd = torch.rsqrt(xf.var(-1, unbiased=False) + eps)
+        y = (xf - mean[..., None]) * rstd[..., None]
+        if w is not None:
+            y = y * w.float()
+        if b is not None:
+            y = y + b.float()
+        return y.to(out_dtype or x.dtype), mean, rstd
+
+    @staticmethod
+    def softmax(x, scale=1.0, causal=False, q_len=0, out_dtype=None):
+        out_dtype = out_dtype or x.dtype
+        x = x.float() * scale
+        if causal:  # the kernel's fused flag: column j of row r is visible when j <= r % q_len
+            x = x.masked_fill(~torch.ones(x.shape[-2], x.shape[-1], dtype=torch.bool).tril(), float("-inf"))
+        return torch.softmax(x, -1).to(out_dtype)
+
+    @staticmethod
+    def gelu_backward(dy, x, approximate="none"):
+        _StandIns._record(x, ("gelu_backward", approximate))
+        return torch.ops.aten.gelu_backward(dy, x, approximate=approximate)
+
+    @staticmethod
+    def softmax_backward(dy, y, scale=1.0, out_dtype=None):
+        _StandIns._record(y, ("softmax_backward", scale))
+        yf, gf = y.float(), dy.float()
+        return (scale * yf * (gf - (gf * yf).sum(-1, keepdim=True))).to(out_dtype or y.dtype)
+
+    @staticmethod
+    def layer_norm_backward(dy, x, mean, rstd, weight, want_weight=True, want_bias=True):
+        _StandIns._record(x, ("layer_norm_backward", want_weight, want_bias))
+        cols = x.shape[-1]
+        xf, gf = x.float().reshape(-1, cols), dy.float().reshape(-1, cols)
+        xh = (xf - mean.reshape(-1, 1).float()) * rstd.reshape(-1, 1).float()
+        g = gf * (weight.float() if weight is not None else 1.0)
+        dx = rstd.reshape(-1, 1).float() * (g - g.mean(-1, keepdim=True) - xh * (g * xh).mean(-1, keepdim=True))
+        pd = weight.dtype if weight is not None else x.dtype
+        return (
+            dx.reshape(x.shape).to(dy.dtype),
+            (gf * xh).sum(0).to(pd) if want_weight else None,
+            gf.sum(0).to(pd) if want_bias else None,
+        )
+
+    @staticmethod
+    def sum_rows(x, out_dtype=None):
+        _StandIns._record(x, ("sum_rows",))
+        return x.float().reshape(-1, x.shape[-1]).sum(0).to(out_dtype or x.dtype)
+
+
+@pytest.fixture()
+def training_stand_ins(monkeypatch, reset_compiler):
+    _StandIns.calls = []
+    monkeypatch.setattr(af, "ops", _TrainingStandIns)
+    return _TrainingStandIns
+
+
+def _grads(model):
+    return {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+
+
+@pytest.mark.parametrize("attention", ["masked_softmax", "sdpa"])
+def test_gpt2_training_step_matches_eager_autograd(training_stand_ins, attention):
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+
+    cfg = GPTConfig(vocab_size=97, block_size=16, n_layer=2, n_head=2, n_embd=32)
+    model = GPT2(cfg, attention).init_weights(0).train()
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 97, (2, 16), generator=g)
+    targets = torch.randint(0, 97, (2, 16), generator=g)
+
+    def loss_of(m):
+        return F.cross_entropy(m(ids).reshape(-1, 97).float(), targets.reshape(-1))
+
+    want_loss = loss_of(model)
+    want_loss.backward()
+    want = _grads(model)
+    model.zero_grad()
+
+    before = {f: f.call_count for f in (af.aten_gelu_backward, af.aten_native_layer_norm_backward)}
+    got_loss = loss_of(torch.compile(model, backend=mojo_backend))
+    got_loss.backward()
+    got = _grads(model)
+
+    torch.testing.assert_close(got_loss, want_loss, rtol=1e-5, atol=1e-6)
+    assert got.keys() == want.keys() and len(got) > 10
+    for name in want:
+        torch.testing.assert_close(got[name], want[name], rtol=1e-4, atol=1e-5, msg=lambda m: f"{name}: {m}")
+    # the backward graph kept these ops whole and they went through the lowerings (and the stand-ins)
+    assert af.aten_gelu_backward.call_count > before[af.aten_gelu_backward]
+    assert af.aten_native_layer_norm_backward.call_count > before[af.aten_native_layer_norm_backward]
+    kinds = {c[0] for c in training_stand_ins.calls}
+    assert {"gelu_backward", "layer_norm_backward", "sum_rows"} <= kinds
+    if attention == "masked_softmax":
+        assert "softmax_backward" in kinds
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_attention_backward_composition_matches_autograd(training_stand_ins, causal, with_bias):
+    g = torch.Generator().manual_seed(2)
+    B, H, T, D = 2, 3, 8, 4
+    q, k, v = (torch.randn(B, H, T, D, generator=g, requires_grad=True) for _ in range(3))
+    bias = torch.randn(1, H, T, T, generator=g, requires_grad=True) if with_bias else None
+    d_out = torch.randn(B, H, T, D, generator=g)
+    scale = 0.37
+    scores = (q @ k.transpose(-1, -2)) * scale
+    if bias is not None:
+        scores = scores + bias
+    if causal:
+        scores = scores.masked_fill(~torch.ones(T, T, dtype=torch.bool).tril(), float("-inf"))
+    out = torch.softmax(scores, -1) @ v
+    want = torch.autograd.grad(out, [q, k, v] + ([bias] if with_bias else []), d_out)
+
+    dq, dk, dv, dbias = af._sdpa_backward(
+        d_out, q.detach(), k.detach(), v.detach(), None if bias is None else bias.detach(), causal, scale, with_bias
+    )
+    for got, ref in zip((dq, dk, dv), want[:3]):
+        torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)
+    if with_bias:
+        torch.testing.assert_close(dbias, want[3], rtol=1e-4, atol=1e-5)

@@ -80,7 +80,7 @@ def time_case(make_inputs, run, bytes_per_copy, iters, use_graph):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ops", default="gemm,gemm_fused,gemm_fp32_routes,layer_norm,softmax,gelu,reduce,embedding,argmax,sdpa,sdpa_decode")
+    ap.add_argument("--ops", default="gemm,gemm_fused,gemm_fp32_routes,layer_norm,softmax,gelu,reduce,embedding,argmax,sdpa,sdpa_decode,backward")
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--only", default="", help="substring filter on the case name")
     ap.add_argument("--no-graph", action="store_true", help="plain launches (what an ncu capture wants)")
@@ -262,6 +262,70 @@ def main():
                     make = lambda i, dtype=dtype, R=R, C=C: (randn((R, C), dtype),)
                     us, rot = time_case(make, lambda t, op=op: ops.reduce(t[0], op), nbytes, args.iters, use_graph)
                     report(name, us, rot, nbytes=nbytes)
+
+    if "backward" in wanted:
+        # The backward kernels on the shapes of a GPT-2 XL training step over 8 x 1024 tokens
+        # (and LayerNorm / bias sums also on the benchmark's 64 x 1024).
+        bf, f32 = torch.bfloat16, torch.float32
+        for approx in ("tanh", "none"):
+            name = f"gelu_backward bf16 {approx} 8192x6400"
+            if keep(name):
+                nbytes = 3 * 8192 * 6400 * 2
+                make = lambda i: (randn((8192, 6400), bf), randn((8192, 6400), bf))
+                us, rot = time_case(make, lambda t, approx=approx: ops.gelu_backward(t[0], t[1], approx), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+        name = "gelu_backward fp32 tanh 8192x3072"
+        if keep(name):
+            nbytes = 3 * 8192 * 3072 * 4
+            make = lambda i: (randn((8192, 3072), f32), randn((8192, 3072), f32))
+            us, rot = time_case(make, lambda t: ops.gelu_backward(t[0], t[1], "tanh"), nbytes, args.iters, use_graph)
+            report(name, us, rot, nbytes=nbytes)
+        for dtype, dname in ((bf, "bf16"), (f32, "fp32")):
+            name = f"softmax_backward {dname} 96x1024x1024"
+            if keep(name):
+                s_ = 2 if dtype == bf else 4
+                nbytes = 3 * 96 * 1024 * 1024 * s_
+                make = lambda i, dtype=dtype: (randn((96, 1024, 1024), dtype), torch.softmax(randn((96, 1024, 1024), f32), -1).to(dtype))
+                us, rot = time_case(make, lambda t: ops.softmax_backward(t[0], t[1], 0.125), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+        for rows in (8192, 65536):
+            # x fp32 (residual stream), dy bf16 (gradient of the GEMM operand), dx bf16
+            name = f"layer_norm_backward x fp32, dy bf16 {rows}x1600"
+            if keep(name):
+                nbytes = rows * 1600 * (4 + 2 + 2) + 8 * rows
+                make = lambda i, rows=rows: (randn((rows, 1600), bf), randn((rows, 1600), f32), randn((rows,), f32),
+                                             randn((rows,), f32).abs() + 0.5, randn((1600,), f32, 0.02, 1.0))
+                us, rot = time_case(make, lambda t: ops.layer_norm_backward(t[0], t[1], t[2], t[3], t[4]), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+            name = f"layer_norm_backward fp32 {rows}x1600"
+            if keep(name):
+                nbytes = rows * 1600 * 12 + 8 * rows
+                make = lambda i, rows=rows: (randn((rows, 1600), f32), randn((rows, 1600), f32), randn((rows,), f32),
+                                             randn((rows,), f32).abs() + 0.5, randn((1600,), f32, 0.02, 1.0))
+                us, rot = time_case(make, lambda t: ops.layer_norm_backward(t[0], t[1], t[2], t[3], t[4]), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+        for rows, cols in ((8192, 6400), (65536, 1600)):
+            name = f"sum_rows bf16 {rows}x{cols}"
+            if keep(name):
+                nbytes = rows * cols * 2
+                make = lambda i, rows=rows, cols=cols: (randn((rows, cols), bf),)
+                us, rot = time_case(make, lambda t: ops.sum_rows(t[0], f32), nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+        # weight gradients dW = X^T dY (A stored transposed, K = tokens) and data gradients dX = dY W
+        m_tok, d = 8192, 1600
+        for label, kin, nout in (("fc", d, 4 * d), ("out", 4 * d, d)):
+            name = f"gemm wgrad xl {label} {kin}x{nout}x{m_tok} (A transposed)"
+            if keep(name):
+                nbytes = 2 * (m_tok * kin + m_tok * nout) + 4 * kin * nout
+                make = lambda i, kin=kin, nout=nout: (randn((m_tok, kin), bf), randn((m_tok, nout), bf))
+                us, rot = time_case(make, lambda t: ops.gemm(t[0].t(), t[1], None, None, 1.0, 1.0, 0, f32), nbytes, args.iters, use_graph)
+                report(name, us, rot, 2.0 * m_tok * kin * nout, nbytes, "tensor")
+            name = f"gemm dgrad xl {label} {m_tok}x{nout}x{kin}"
+            if keep(name):
+                nbytes = 2 * (m_tok * nout + kin * nout + m_tok * kin)
+                make = lambda i, kin=kin, nout=nout: (randn((m_tok, nout), bf), randn((nout, kin), bf, 0.02))
+                us, rot = time_case(make, lambda t: ops.gemm(t[0], t[1]), nbytes, args.iters, use_graph)
+                report(name, us, rot, 2.0 * m_tok * kin * nout, nbytes, "tensor")
 
     if "embedding" in wanted:
         # token + positional embeddings of a GPT-2 XL batch: bf16 tables, fp32 residual stream out

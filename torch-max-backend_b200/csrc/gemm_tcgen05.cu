@@ -80,6 +80,9 @@ struct Params {
   // stored as [hi | lo] halves are the split-precision product a_hi b_lo + a_lo b_hi + a_hi b_hi.
   int32_t k_parts;
   int32_t a_part_off[3], b_part_off[3];
+  // A is stored [K, M] with M contiguous (the transposed operand of a weight-gradient GEMM): its tile
+  // arrives as two boxes of 64(m) x 64(k) and the MMA reads it through the MN-major descriptor.
+  int32_t a_mn_major;
 };
 
 __device__ __forceinline__ float act(float v, int32_t epilogue) {
@@ -259,7 +262,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // complete until the pending arrival below has happened.)
             const uint32_t bar = ptx::mapa(full_bar(s), 0);
             if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + C_::B_STAGE_BYTES));
-            ptx::tma_load_3d_pair(a_base + s * A_STAGE_BYTES, &tmap_a, bar, k0, m0, (int32_t)b);
+            if (!p.a_mn_major) {
+              ptx::tma_load_3d_pair(a_base + s * A_STAGE_BYTES, &tmap_a, bar, k0, m0, (int32_t)b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                ptx::tma_load_3d_pair(a_base + s * A_STAGE_BYTES + j * (64 * BK * 2), &tmap_a, bar, m0 + j * 64, k0,
+                                      (int32_t)b);
+            }
             if (!B_MN_MAJOR) {
               ptx::tma_load_3d_pair(b_base + s * C_::B_STAGE_BYTES, &tmap_b, bar, k0b, n0, (int32_t)b);
             } else {
@@ -273,7 +283,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             continue;
           }
           ptx::mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + C_::B_STAGE_BYTES);
-          ptx::tma_load_3d(a_base + s * A_STAGE_BYTES, &tmap_a, full_bar(s), k0, m0, (int32_t)b);
+          if (!p.a_mn_major) {
+            ptx::tma_load_3d(a_base + s * A_STAGE_BYTES, &tmap_a, full_bar(s), k0, m0, (int32_t)b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              ptx::tma_load_3d(a_base + s * A_STAGE_BYTES + j * (64 * BK * 2), &tmap_a, full_bar(s), m0 + j * 64, k0,
+                               (int32_t)b);
+          }
           if (!B_MN_MAJOR) {
             ptx::tma_load_3d(b_base + s * C_::B_STAGE_BYTES, &tmap_b, full_bar(s), k0b, n0, (int32_t)b);
           } else {
@@ -293,7 +310,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // values) and one elected lane issues the MMAs and commits; tcgen05.commit tracks the MMAs of
     // the thread that executes it, and the election returns the same lane every time.
     if (rank == 0) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(kTileM, BN, 0, B_MN_MAJOR ? 1 : 0);
+      const uint32_t idesc = p.a_mn_major ? ptx::idesc_bf16_f32(kTileM, BN, 1, B_MN_MAJOR ? 1 : 0)
+                                          : ptx::idesc_bf16_f32(kTileM, BN, 0, B_MN_MAJOR ? 1 : 0);
+      const bool a_mn = p.a_mn_major != 0;
       int s = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -311,7 +330,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (ptx::elect_one()) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t a_desc = ptx::smem_desc_sw128(a_addr + k * (UMMA_K * 2), 0, 1024);
+              const uint64_t a_desc = a_mn ? ptx::smem_desc_sw128(a_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                           : ptx::smem_desc_sw128(a_addr + k * (UMMA_K * 2), 0, 1024);
               const uint64_t b_desc =
                   B_MN_MAJOR ? ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024)
                              : ptx::smem_desc_sw128(b_addr + k * (UMMA_K * 2), 0, 1024);
@@ -562,6 +582,7 @@ int32_t fill_params(const b200_gemm_args& g, Params& p, int tile_m, int tile_n, 
   p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * g.batch;
   p.k_parts = 1;
   for (int i = 0; i < 3; ++i) { p.a_part_off[i] = 0; p.b_part_off[i] = 0; }
+  p.a_mn_major = 0;
   p.status = device_status_ptr();
   B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "gemm(tcgen05): device status word unavailable");
   {
@@ -583,17 +604,32 @@ void apply_k_parts(Params& p, const GemmKParts* kp) {
   for (int i = 0; i < 3; ++i) { p.a_part_off[i] = kp->a_off[i]; p.b_part_off[i] = kp->b_off[i]; }
 }
 
+bool a_is_m_major(const b200_gemm_args& g) { return g.a_col_stride != 1 && g.a_row_stride == 1; }
+
+// A as [m, k] with k contiguous (boxes of 64 k x 128 rows), or as [k, m] with m contiguous (boxes of
+// 64 m x 64 k, two per tile).
+int32_t encode_a_map(CUtensorMap* map, const b200_gemm_args& g, uint64_t k_extent) {
+  if (!a_is_m_major(g)) {
+    const uint64_t dims[3] = {k_extent, (uint64_t)g.m, (uint64_t)g.batch};
+    const uint64_t strides[2] = {(uint64_t)g.a_row_stride * 2,
+                                 (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_row_stride * g.m) * 2};
+    const uint32_t box[3] = {BK, BM, 1};
+    return encode_tensor_map(map, B200_BF16, 3, g.a, dims, strides, box, true);
+  }
+  const uint64_t dims[3] = {(uint64_t)g.m, k_extent, (uint64_t)g.batch};
+  const uint64_t strides[2] = {(uint64_t)g.a_col_stride * 2,
+                               (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_col_stride * (int64_t)k_extent) * 2};
+  const uint32_t box[3] = {64, BK, 1};
+  return encode_tensor_map(map, B200_BF16, 3, g.a, dims, strides, box, true);
+}
+
 template <int BN, bool B_MN_MAJOR, typename Tout>
 int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream, const GemmKParts* kp) {
   using C_ = Cfg<BN>;
   CUtensorMap tmap_a, tmap_b;
   const uint64_t k_extent = kp != nullptr ? (uint64_t)kp->k_storage : (uint64_t)g.k;  // K extent of the stored operands
   {
-    const uint64_t dims[3] = {k_extent, (uint64_t)g.m, (uint64_t)g.batch};
-    const uint64_t strides[2] = {(uint64_t)g.a_row_stride * 2,
-                                 (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_row_stride * g.m) * 2};
-    const uint32_t box[3] = {BK, BM, 1};
-    int32_t st = encode_tensor_map(&tmap_a, B200_BF16, 3, g.a, dims, strides, box, true);
+    int32_t st = encode_a_map(&tmap_a, g, k_extent);
     if (st != B200_OK) return st;
   }
   if (!B_MN_MAJOR) {
@@ -618,6 +654,7 @@ int32_t launch_cfg(const b200_gemm_args& g, cudaStream_t stream, const GemmKPart
     int32_t st = fill_params(g, p, BM, BN, sizeof(Tout));
     if (st != B200_OK) return st;
     apply_k_parts(p, kp);
+    p.a_mn_major = a_is_m_major(g) ? 1 : 0;
   }
 
   auto kernel = gemm_tcgen05_kernel<BN, B_MN_MAJOR, Tout>;
@@ -645,11 +682,7 @@ int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream, const Gemm
   CUtensorMap tmap_a, tmap_b;
   const uint64_t k_extent = kp != nullptr ? (uint64_t)kp->k_storage : (uint64_t)g.k;
   {
-    const uint64_t dims[3] = {k_extent, (uint64_t)g.m, (uint64_t)g.batch};
-    const uint64_t strides[2] = {(uint64_t)g.a_row_stride * 2,
-                                 (uint64_t)(g.batch > 1 ? g.a_batch_stride : g.a_row_stride * g.m) * 2};
-    const uint32_t box[3] = {BK, BM, 1};
-    int32_t st = encode_tensor_map(&tmap_a, B200_BF16, 3, g.a, dims, strides, box, true);
+    int32_t st = encode_a_map(&tmap_a, g, k_extent);
     if (st != B200_OK) return st;
   }
   if (!B_MN_MAJOR) {
@@ -672,6 +705,7 @@ int32_t launch_pair_cfg(const b200_gemm_args& g, cudaStream_t stream, const Gemm
   int32_t st = fill_params(g, p, 2 * BM, BN, sizeof(Tout));
   if (st != B200_OK) return st;
   apply_k_parts(p, kp);
+  p.a_mn_major = a_is_m_major(g) ? 1 : 0;
 
   auto kernel = gemm_tcgen05_kernel<BN, B_MN_MAJOR, Tout, true>;
   static thread_local bool attr_set[64] = {false};
@@ -778,10 +812,14 @@ int pick_bn(const b200_gemm_args& g) {
 const char* gemm_tcgen05_ineligible(const b200_gemm_args& g) {
   if (g.in_dtype != B200_BF16) return "operands are not bf16";
   if (g.k <= 0) return "k is zero";
-  if (g.a_col_stride != 1) return "A is not K-contiguous";
+  if (g.a_col_stride != 1 && g.a_row_stride != 1) return "A has no unit stride";
   if (!b_is_k_major(g) && !b_is_n_major(g)) return "B has no unit stride";
   if (!aligned_to(g.a, 16) || !aligned_to(g.b, 16)) return "operand pointer not 16-byte aligned";
-  if (g.a_row_stride % 8 != 0 || g.a_row_stride < g.k) return "A row pitch not a multiple of 16 bytes";
+  if (a_is_m_major(g)) {
+    if (g.a_col_stride % 8 != 0 || g.a_col_stride < g.m) return "A column pitch not a multiple of 16 bytes";
+  } else if (g.a_row_stride % 8 != 0 || g.a_row_stride < g.k) {
+    return "A row pitch not a multiple of 16 bytes";
+  }
   if (g.batch > 1 && (g.a_batch_stride % 8 != 0 || g.b_batch_stride % 8 != 0))
     return "batch stride not a multiple of 16 bytes";
   if (b_is_n_major(g)) {

@@ -239,6 +239,59 @@ def aten_gelu(input, approximate="none"):
     return ops.gelu(input, approximate)
 
 
+# gelu_backward(Tensor grad_output, Tensor self, *, str approximate='none') -> Tensor
+@map_to(aten.gelu_backward)
+def aten_gelu_backward(grad_output, input, *, approximate="none"):
+    """reference: aten_functions.py:2070-2102"""
+    if approximate not in ("none", "tanh"):
+        raise ValueError(
+            f"Invalid approximate argument '{approximate}'. Supported values are 'none' (exact, erf) and 'tanh'."
+        )
+    _require_kernel_dtype("aten.gelu_backward", grad_output, input)
+    if grad_output.dtype != input.dtype:
+        grad_output = grad_output.to(input.dtype)
+    return ops.gelu_backward(grad_output, input, approximate)
+
+
+# _softmax_backward_data(Tensor grad_output, Tensor output, int dim, ScalarType input_dtype) -> Tensor
+@map_to(aten._softmax_backward_data)
+def aten__softmax_backward_data(grad_output, output, dim, input_dtype):
+    _require_kernel_dtype("aten._softmax_backward_data", grad_output, output)
+    if grad_output.dtype != output.dtype:
+        grad_output = grad_output.to(output.dtype)
+    g, _ = _move_dim_last(grad_output, dim)
+    y, moved = _move_dim_last(output, dim)
+    dx = ops.softmax_backward(g, y, 1.0, input_dtype if native.supported_dtype(input_dtype) else None)
+    return dx if moved is None else dx.movedim(-1, moved)
+
+
+# native_layer_norm_backward(Tensor grad_out, Tensor input, SymInt[] normalized_shape, Tensor mean,
+#   Tensor rstd, Tensor? weight, Tensor? bias, bool[3] output_mask) -> (Tensor, Tensor, Tensor)
+@map_to(aten.native_layer_norm_backward)
+def aten_native_layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask):
+    _require_kernel_dtype("aten.native_layer_norm_backward", grad_out, input, weight)
+    norm = 1
+    for d in normalized_shape:
+        norm *= int(d)
+    if weight is not None and weight.numel() != norm:
+        raise ValueError(f"native_layer_norm_backward: weight of {weight.numel()} elements for {norm} normalised elements")
+    w = weight
+    if w is None and norm != input.shape[-1]:
+        # no weight to carry the normalised extent: flatten the normalised dims ourselves
+        input = input.reshape(*input.shape[: input.dim() - len(normalized_shape)], norm)
+        grad_out = grad_out.reshape(input.shape)
+    dx, dgamma, dbeta = ops.layer_norm_backward(
+        grad_out, input, mean, rstd, w, bool(output_mask[1]) and weight is not None,
+        bool(output_mask[2]) and bias is not None,
+    )
+    if dx.dtype != input.dtype:
+        dx = dx.to(input.dtype)
+    dx = dx.reshape(grad_out.shape) if output_mask[0] else None
+    if dbeta is not None and bias is not None:
+        dbeta = dbeta.reshape(bias.shape)
+    return dx, dgamma, dbeta
+
+
 def _reduce_dims(input, dim, keepdim, op, dtype):
     """sum/mean/amax over `dim` (list, int or None): the reduced dims are moved to the end and
     flattened so that one trailing-dim kernel launch covers any dim list."""
@@ -254,6 +307,11 @@ def _reduce_dims(input, dim, keepdim, op, dtype):
         out = ops.reduce(x, op, dtype)
         return out
     kept = [d for d in range(nd) if d not in dims]
+    if op == native.REDUCE_SUM and kept == [nd - 1] and nd >= 2 and input.stride(-1) == 1:
+        # Every dim but the last is summed (a bias gradient): the column-sum kernel reads the rows
+        # as they lie instead of transposing them first.
+        out = ops.sum_rows(input.reshape(-1, input.shape[-1]), dtype)
+        return out.reshape([1] * (nd - 1) + [input.shape[-1]]) if keepdim else out
     x = input.permute(*kept, *dims) if kept + dims != list(range(nd)) else input
     lead = [input.shape[d] for d in kept]
     x = x.reshape(*lead, -1)
@@ -506,6 +564,128 @@ def aten_scaled_dot_product_attention(
 # ==============================================================================================
 
 
+# ---- attention backward -----------------------------------------------------------------------
+# The gradient of softmax(scale Q K^T + bias) V from the library's own GEMM and row kernels: the
+# probabilities are recomputed (S = Q K^T, P = softmax), dV = P^T dO, dP = dO V^T,
+# dS = scale P (dP - rowsum(dP P)), dQ = dS K, dK = dS^T Q. The T x S matrices exist for a bounded
+# number of (batch, head) pairs at a time. (The reference's fused form is
+# eager_flash_attention/fa4_bwd_kernel.mojo; its decomposed form is eager_kernels/sdpa_backward_ops.mojo.)
+_SDPA_BACKWARD_SCORE_BYTES = 1 << 30
+
+
+def _sdpa_backward(grad_out, query, key, value, attn_bias, is_causal, scale, want_bias_grad=False):
+    _require_kernel_dtype("scaled_dot_product_attention backward", grad_out, query, key, value)
+    if key.shape[1] != query.shape[1]:
+        raise NotImplementedError("attention backward with grouped-query heads is not supported by the b200 kernels")
+    B, H, T, D = query.shape
+    S = key.shape[2]
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+    dtype = query.dtype
+    q = query.reshape(B * H, T, D)
+    k = key.reshape(B * H, S, D)
+    v = value.reshape(B * H, S, value.shape[3])
+    do = grad_out.to(dtype).reshape(B * H, T, value.shape[3])
+    bias = None
+    if attn_bias is not None:
+        bias = attn_bias
+        if bias.dtype == torch.bool:
+            bias = torch.zeros(bias.shape, dtype=torch.float32, device=bias.device).masked_fill_(~bias, float("-inf"))
+        bias = bias.to(torch.float32).expand(B, H, T, S).reshape(B * H, T, S)
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    dbias = torch.empty((B * H, T, S), dtype=torch.float32, device=q.device) if want_bias_grad else None
+    chunk = max(1, _SDPA_BACKWARD_SCORE_BYTES // (16 * T * S))
+    for lo in range(0, B * H, chunk):
+        hi = min(B * H, lo + chunk)
+        qc, kc, vc, doc = q[lo:hi], k[lo:hi], v[lo:hi], do[lo:hi]
+        scores = ops.gemm(qc, kc.transpose(1, 2), None, None, 1.0, 1.0, 0, torch.float32)
+        if bias is None:
+            p = ops.softmax(scores, scale, bool(is_causal), T)
+            fold = scale
+        else:
+            scores = scores * scale + bias[lo:hi]
+            p = ops.softmax(scores, 1.0, bool(is_causal), T)
+            fold = 1.0
+        del scores
+        p_lo = p if dtype == torch.float32 else p.to(dtype)
+        dv[lo:hi] = ops.gemm(p_lo.transpose(1, 2), doc)
+        dp = ops.gemm(doc, vc.transpose(1, 2), None, None, 1.0, 1.0, 0, torch.float32)
+        if dbias is not None:
+            ds32 = ops.softmax_backward(dp, p, 1.0)
+            dbias[lo:hi] = ds32
+            ds = (ds32 * scale).to(dtype)
+        else:
+            ds = ops.softmax_backward(dp, p, fold if bias is None else scale, dtype)
+        del dp, p, p_lo
+        dq[lo:hi] = ops.gemm(ds, kc)
+        dk[lo:hi] = ops.gemm(ds.transpose(1, 2), qc)
+    shape_q, shape_k, shape_v = query.shape, key.shape, value.shape
+    if dbias is not None:
+        dbias = dbias.reshape(B, H, T, S)
+        # sum over the dims the bias was broadcast along
+        for d in range(4):
+            if attn_bias.dim() == 4 and attn_bias.shape[d] == 1 and dbias.shape[d] != 1:
+                dbias = dbias.sum(d, keepdim=True)
+        dbias = dbias.to(attn_bias.dtype) if attn_bias.dtype.is_floating_point else None
+    return dq.reshape(shape_q), dk.reshape(shape_k), dv.reshape(shape_v), dbias
+
+
+# _scaled_dot_product_flash_attention_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value,
+#   Tensor out, Tensor logsumexp, Tensor cum_seq_q, Tensor cum_seq_k, SymInt max_q, SymInt max_k,
+#   float dropout_p, bool is_causal, Tensor philox_seed, Tensor philox_offset, *, float? scale=None)
+#   -> (Tensor, Tensor, Tensor)
+@map_to(aten._scaled_dot_product_flash_attention_backward)
+def aten__scaled_dot_product_flash_attention_backward(
+    grad_out, query, key, value, out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, dropout_p, is_causal,
+    philox_seed, philox_offset, *, scale=None,
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention backward with dropout is not supported by the b200 kernels")
+    return _sdpa_backward(grad_out, query, key, value, None, is_causal, scale)[:3]
+
+
+# _scaled_dot_product_efficient_attention_backward(Tensor grad_out_, Tensor query, Tensor key, Tensor value,
+#   Tensor attn_bias, Tensor out, Tensor logsumexp, Tensor philox_seed, Tensor philox_offset, float dropout_p,
+#   bool[4] grad_input_mask, bool is_causal=False, *, float? scale=None) -> (Tensor, Tensor, Tensor, Tensor)
+@map_to(aten._scaled_dot_product_efficient_attention_backward)
+def aten__scaled_dot_product_efficient_attention_backward(
+    grad_out_, query, key, value, attn_bias, out, logsumexp, philox_seed, philox_offset, dropout_p,
+    grad_input_mask, is_causal=False, *, scale=None,
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention backward with dropout is not supported by the b200 kernels")
+    want_bias = bool(grad_input_mask[3]) and attn_bias is not None
+    return _sdpa_backward(grad_out_, query, key, value, attn_bias, is_causal, scale, want_bias)
+
+
+# _scaled_dot_product_cudnn_attention_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value,
+#   Tensor out, Tensor logsumexp, Tensor philox_seed, Tensor philox_offset, Tensor attn_bias,
+#   Tensor cum_seq_q, Tensor cum_seq_k, SymInt max_q, SymInt max_k, float dropout_p, bool is_causal,
+#   *, float? scale=None) -> (Tensor, Tensor, Tensor)
+@map_to(aten._scaled_dot_product_cudnn_attention_backward)
+def aten__scaled_dot_product_cudnn_attention_backward(
+    grad_out, query, key, value, out, logsumexp, philox_seed, philox_offset, attn_bias, cum_seq_q, cum_seq_k,
+    max_q, max_k, dropout_p, is_causal, *, scale=None,
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention backward with dropout is not supported by the b200 kernels")
+    return _sdpa_backward(grad_out, query, key, value, attn_bias, is_causal, scale)[:3]
+
+
+# _scaled_dot_product_flash_attention_for_cpu_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value,
+#   Tensor out, Tensor logsumexp, float dropout_p, bool is_causal, *, Tensor? attn_mask=None, float? scale=None)
+#   -> (Tensor, Tensor, Tensor)
+# (what the backward of a graph traced on CPU tensors holds: the forward op is decomposed, this one is not)
+@map_to(aten._scaled_dot_product_flash_attention_for_cpu_backward)
+def aten__scaled_dot_product_flash_attention_for_cpu_backward(
+    grad_out, query, key, value, out, logsumexp, dropout_p, is_causal, *, attn_mask=None, scale=None
+):
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention backward with dropout is not supported by the b200 kernels")
+    return _sdpa_backward(grad_out, query, key, value, attn_mask, is_causal, scale)[:3]
+
+
 def _count_calls(fn):
     if not torch_mojo_backend.is_running_tests.IS_RUNNING_TESTS:
         return fn
@@ -673,6 +853,9 @@ _GLUE_OPS = [
     aten.any, aten.index, aten.index_select, aten.gather, aten.sym_size, aten.sym_numel,
     aten.lift_fresh_copy, aten.copy, aten.repeat, aten.flip, aten.unbind, aten.max, aten.min,
     aten.amin, aten.topk, aten.sort, aten.squeeze_copy, aten.native_dropout, aten._local_scalar_dense,
+    # loss and embedding gradients of a training step
+    aten._log_softmax, aten._log_softmax_backward_data, aten.nll_loss_forward, aten.nll_loss_backward,
+    aten.scatter, aten.scatter_add, aten.index_put, aten.embedding_dense_backward, aten.new_zeros,
 ]
 
 for _packet in _GLUE_OPS:

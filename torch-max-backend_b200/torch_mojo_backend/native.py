@@ -61,6 +61,12 @@ EXPORTED_SYMBOLS = (
     "b200_softmax_masked",
     "b200_gelu",
     "b200_reduce_lastdim",
+    "b200_gelu_backward",
+    "b200_softmax_backward",
+    "b200_layer_norm_backward_workspace_bytes",
+    "b200_layer_norm_backward",
+    "b200_sum_rows_workspace_bytes",
+    "b200_sum_rows",
     "b200_embedding_sum",
     "b200_argmax_lastdim",
     "b200_copy_rows",
@@ -204,6 +210,20 @@ def _declare(dll: ctypes.CDLL) -> None:
     dll.b200_gelu.argtypes = [vp, vp, i64, i32, i32, vp]
     dll.b200_reduce_lastdim.restype = i32
     dll.b200_reduce_lastdim.argtypes = [vp, vp, i64, i64, i64, i32, i32, i32, vp]
+    dll.b200_gelu_backward.restype = i32
+    dll.b200_gelu_backward.argtypes = [vp, vp, vp, i64, i32, i32, vp]
+    dll.b200_softmax_backward.restype = i32
+    dll.b200_softmax_backward.argtypes = [vp, vp, vp, i64, i64, i64, i64, ctypes.c_float, i32, i32, vp]
+    dll.b200_layer_norm_backward_workspace_bytes.restype = ctypes.c_size_t
+    dll.b200_layer_norm_backward_workspace_bytes.argtypes = [i64, i64]
+    dll.b200_layer_norm_backward.restype = i32
+    dll.b200_layer_norm_backward.argtypes = [
+        vp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, i64, i64, i64, i64, i32, i32, i32, i32, vp,
+    ]
+    dll.b200_sum_rows_workspace_bytes.restype = ctypes.c_size_t
+    dll.b200_sum_rows_workspace_bytes.argtypes = [i64, i64, i32]
+    dll.b200_sum_rows.restype = i32
+    dll.b200_sum_rows.argtypes = [vp, vp, vp, ctypes.c_size_t, i64, i64, i64, i32, i32, vp]
     dll.b200_embedding_sum.restype = i32
     dll.b200_embedding_sum.argtypes = [vp, vp, i64, i64, vp, vp, i64, i64, i64, vp, i64, i64, i32, i32, vp]
     dll.b200_argmax_lastdim.restype = i32

@@ -46,6 +46,13 @@ _lib.define(
     "embedding_sum(Tensor table, Tensor indices, Tensor? table2=None, Tensor? indices2=None,"
     " ScalarType? out_dtype=None) -> Tensor"
 )
+_lib.define("gelu_backward(Tensor dy, Tensor x, str approximate='none') -> Tensor")
+_lib.define("softmax_backward(Tensor dy, Tensor y, float scale=1.0, ScalarType? out_dtype=None) -> Tensor")
+_lib.define(
+    "layer_norm_backward(Tensor dy, Tensor x, Tensor mean, Tensor rstd, Tensor? weight, bool want_weight=True,"
+    " bool want_bias=True) -> (Tensor, Tensor?, Tensor?)"
+)
+_lib.define("sum_rows(Tensor x, ScalarType? out_dtype=None) -> Tensor")
 _lib.define("argmax(Tensor x) -> Tensor")
 _lib.define("cat(Tensor[] tensors, int dim=0) -> Tensor")
 _lib.define("kv_append(Tensor(a!) cache, Tensor new, int position) -> ()")
@@ -235,6 +242,130 @@ def _reduce_cuda(x, op, out_dtype=None):
 
 def _reduce_meta(x, op, out_dtype=None):
     return torch.empty(x.shape[:-1], dtype=out_dtype or x.dtype, device=x.device)
+
+
+# ---- backward of the row kernels --------------------------------------------------------------
+
+
+def _gelu_backward_cuda(dy, x, approximate="none"):
+    device = native.require_cuda("gelu_backward", dy, x)
+    if approximate not in ("none", "tanh"):
+        raise ValueError(f"gelu_backward: approximate must be 'none' or 'tanh', got {approximate!r}")
+    if dy.shape != x.shape or dy.dtype != x.dtype:
+        raise RuntimeError(f"gelu_backward: dy {tuple(dy.shape)} {dy.dtype} and x {tuple(x.shape)} {x.dtype} differ")
+    gc = dy if dy.is_contiguous() else dy.contiguous()
+    xc = x if x.is_contiguous() else x.contiguous()
+    dx = torch.empty(x.shape, dtype=x.dtype, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_gelu_backward(
+            gc.data_ptr(), xc.data_ptr(), dx.data_ptr(), xc.numel(), int(approximate == "tanh"),
+            native.dtype_enum(x.dtype), native.current_stream(device),
+        )
+    native.check("gelu_backward", status)
+    _launched(device, start, "gelu_backward", 0.0, _nbytes(gc, xc, dx))
+    return dx
+
+
+def _gelu_backward_meta(dy, x, approximate="none"):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+def _softmax_backward_cuda(dy, y, scale=1.0, out_dtype=None):
+    device = native.require_cuda("softmax_backward", dy, y)
+    if dy.shape != y.shape or dy.dtype != y.dtype:
+        raise RuntimeError(f"softmax_backward: dy {tuple(dy.shape)} {dy.dtype} and y {tuple(y.shape)} {y.dtype} differ")
+    out_dtype = out_dtype or y.dtype
+    gr, rows, cols, g_stride = _as_rows(dy)
+    yr, _, _, y_stride = _as_rows(y)
+    dx = torch.empty(y.shape, dtype=out_dtype, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = native.lib().b200_softmax_backward(
+            gr.data_ptr(), yr.data_ptr(), dx.data_ptr(), rows, cols, g_stride, y_stride, float(scale),
+            native.dtype_enum(y.dtype), native.dtype_enum(out_dtype), native.current_stream(device),
+        )
+    native.check("softmax_backward", status)
+    _launched(device, start, "softmax_backward", 0.0, _nbytes(gr, yr, dx))
+    return dx
+
+
+def _softmax_backward_meta(dy, y, scale=1.0, out_dtype=None):
+    return torch.empty(y.shape, dtype=out_dtype or y.dtype, device=y.device)
+
+
+def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_bias=True):
+    device = native.require_cuda("layer_norm_backward", dy, x, mean, rstd, weight)
+    if dy.shape != x.shape:
+        raise RuntimeError(f"layer_norm_backward: dy {tuple(dy.shape)} and x {tuple(x.shape)} differ")
+    cols = weight.numel() if weight is not None else x.shape[-1]
+    if cols == 0 or x.numel() % cols != 0:
+        raise RuntimeError(f"layer_norm_backward: {tuple(x.shape)} is not rows of {cols} normalised elements")
+    rows = x.numel() // cols
+    x2 = x.reshape(rows, cols)
+    g2 = dy.reshape(rows, cols)
+    x2 = x2 if x2.stride(1) == 1 and (x2.stride(0) >= cols or rows <= 1) else x2.contiguous()
+    g2 = g2 if g2.stride(1) == 1 and (g2.stride(0) >= cols or rows <= 1) else g2.contiguous()
+    mean_c = mean.reshape(-1).float().contiguous()
+    rstd_c = rstd.reshape(-1).float().contiguous()
+    if mean_c.numel() != rows or rstd_c.numel() != rows:
+        raise RuntimeError(f"layer_norm_backward: mean / rstd have {mean_c.numel()} / {rstd_c.numel()} entries for {rows} rows")
+    param_dtype = weight.dtype if weight is not None else x.dtype
+    wc = None if weight is None else weight.reshape(-1).contiguous()
+    dx = torch.empty(x.shape, dtype=dy.dtype, device=device)
+    dgamma = torch.empty(cols, dtype=param_dtype, device=device) if want_weight else None
+    dbeta = torch.empty(cols, dtype=param_dtype, device=device) if want_bias else None
+    lib = native.lib()
+    ws_bytes = lib.b200_layer_norm_backward_workspace_bytes(rows, cols)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = lib.b200_layer_norm_backward(
+            g2.data_ptr(), x2.data_ptr(), mean_c.data_ptr(), rstd_c.data_ptr(), _ptr(wc), dx.data_ptr(),
+            _ptr(dgamma), _ptr(dbeta), ws.data_ptr(), ws_bytes, rows, cols, g2.stride(0) if rows > 1 else cols,
+            x2.stride(0) if rows > 1 else cols, native.dtype_enum(x.dtype), native.dtype_enum(dy.dtype),
+            native.dtype_enum(param_dtype), native.dtype_enum(dy.dtype), native.current_stream(device),
+        )
+    native.check("layer_norm_backward", status)
+    _launched(device, start, "layer_norm_backward", 0.0, _nbytes(g2, x2, dx))
+    if weight is not None and dgamma is not None:
+        dgamma = dgamma.reshape(weight.shape)
+        dbeta = dbeta.reshape(weight.shape) if dbeta is not None else None
+    return dx, dgamma, dbeta
+
+
+def _layer_norm_backward_meta(dy, x, mean, rstd, weight, want_weight=True, want_bias=True):
+    cols = weight.numel() if weight is not None else x.shape[-1]
+    shape = weight.shape if weight is not None else (cols,)
+    param_dtype = weight.dtype if weight is not None else x.dtype
+    return (
+        torch.empty(x.shape, dtype=dy.dtype, device=x.device),
+        torch.empty(shape, dtype=param_dtype, device=x.device) if want_weight else None,
+        torch.empty(shape, dtype=param_dtype, device=x.device) if want_bias else None,
+    )
+
+
+def _sum_rows_cuda(x, out_dtype=None):
+    device = native.require_cuda("sum_rows", x)
+    out_dtype = out_dtype or x.dtype
+    xr, rows, cols, row_stride = _as_rows(x)
+    y = torch.empty(cols, dtype=out_dtype, device=device)
+    lib = native.lib()
+    ws_bytes = lib.b200_sum_rows_workspace_bytes(rows, cols, native.dtype_enum(x.dtype))
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = lib.b200_sum_rows(
+            xr.data_ptr(), y.data_ptr(), ws.data_ptr(), ws_bytes, rows, cols, row_stride,
+            native.dtype_enum(x.dtype), native.dtype_enum(out_dtype), native.current_stream(device),
+        )
+    native.check("sum_rows", status)
+    _launched(device, start, "sum_rows", 0.0, _nbytes(xr, y))
+    return y
+
+
+def _sum_rows_meta(x, out_dtype=None):
+    return torch.empty(x.shape[-1] if x.dim() > 0 else 1, dtype=out_dtype or x.dtype, device=x.device)
 
 
 # ---- gemm -----------------------------------------------------------------------------------
@@ -567,6 +698,10 @@ for _name, _cuda, _meta in (
     ("softmax_masked", _softmax_masked_cuda, _softmax_masked_meta),
     ("gelu", _gelu_cuda, _gelu_meta),
     ("reduce", _reduce_cuda, _reduce_meta),
+    ("gelu_backward", _gelu_backward_cuda, _gelu_backward_meta),
+    ("softmax_backward", _softmax_backward_cuda, _softmax_backward_meta),
+    ("layer_norm_backward", _layer_norm_backward_cuda, _layer_norm_backward_meta),
+    ("sum_rows", _sum_rows_cuda, _sum_rows_meta),
     ("gemm", _gemm_cuda, _gemm_meta),
     ("sdpa", _sdpa_cuda, _sdpa_meta),
     ("embedding_sum", _embedding_sum_cuda, _embedding_sum_meta),
@@ -583,6 +718,10 @@ softmax = torch.ops.b200.softmax
 softmax_masked = torch.ops.b200.softmax_masked
 gelu = torch.ops.b200.gelu
 reduce = torch.ops.b200.reduce
+gelu_backward = torch.ops.b200.gelu_backward
+softmax_backward = torch.ops.b200.softmax_backward
+layer_norm_backward = torch.ops.b200.layer_norm_backward
+sum_rows = torch.ops.b200.sum_rows
 gemm = torch.ops.b200.gemm
 sdpa = torch.ops.b200.sdpa
 embedding_sum = torch.ops.b200.embedding_sum
