@@ -356,7 +356,10 @@ def test_auto_route_choices(ops):
     assert route(torch.empty((256, 64), device="cuda"), torch.empty((64, 256), device="cuda")) == ROUTE_SIMT
     # K-contiguity / 16-byte pitch rules of the TMA route
     assert route(torch.empty((256, 60), dtype=bf, device="cuda"), torch.empty((60, 256), dtype=bf, device="cuda")) == ROUTE_SIMT
-    assert route(torch.empty((64, 256), dtype=bf, device="cuda").t(), torch.empty((64, 256), dtype=bf, device="cuda")) == ROUTE_SIMT
+    # a transposed A (m contiguous, the operand of a weight gradient) is taken as it lies when its pitch is 16-byte
+    assert route(torch.empty((64, 256), dtype=bf, device="cuda").t(), torch.empty((64, 256), dtype=bf, device="cuda")) == ROUTE_TC
+    assert route(torch.empty((64, 252), dtype=bf, device="cuda").t(), torch.empty((64, 256), dtype=bf, device="cuda")) == ROUTE_SIMT
+    assert route(torch.empty((64, 512), dtype=bf, device="cuda")[:, ::2].t(), torch.empty((64, 256), dtype=bf, device="cuda")) == ROUTE_SIMT
 
 
 def test_forced_route_refused_loudly(ops):

@@ -243,33 +243,91 @@ int32_t launch_softmax_backward(const void* dy, const void* y, void* dx, int64_t
 // LayerNorm backward and the sum over rows (bias gradient)
 // =========================================================================================
 
-// out[c] = sum over the partial rows, in row order; one thread per column.
+// out[c] = sum over the partial rows of part[nparts, cols], for up to two arrays at once
+// (blockIdx.y). A CTA of 32 x 32 threads takes 32 columns: thread (cx, ry) adds rows ry, ry + 32, ...
+// of column cx, then the 32 row sums of a column are added in ry order: a fixed order whatever the
+// launch, and short dependent chains instead of one thread walking every partial row.
+struct PartialSums {
+  const float* part[2];
+  void* out[2];
+};
+
 template <typename Tout>
-__global__ void sum_partials_kernel(const float* __restrict__ part, Tout* __restrict__ out, int64_t nparts, int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  int64_t r = 0;
-  for (; r + 4 <= nparts; r += 4) {
-#pragma unroll
-    for (int u = 0; u < 4; ++u) s[u] += part[(r + u) * cols + c];
+__global__ void __launch_bounds__(1024)
+sum_partials_kernel(PartialSums ps, int64_t nparts, int cols) {
+  __shared__ float tile[32][33];
+  const float* part = ps.part[blockIdx.y];
+  Tout* out = static_cast<Tout*>(ps.out[blockIdx.y]);
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s0 = 0.0f, s1 = 0.0f;
+  if (c < cols) {
+    int64_t r = ry;
+    for (; r + 32 < nparts; r += 64) {
+      s0 += part[r * cols + c];
+      s1 += part[(r + 32) * cols + c];
+    }
+    if (r < nparts) s0 += part[r * cols + c];
   }
-  for (; r < nparts; ++r) s[0] += part[r * cols + c];
-  out[c] = Elem<Tout>::from_f32((s[0] + s[1]) + (s[2] + s[3]));
+  tile[ry][cx] = s0 + s1;
+  __syncthreads();
+  if (ry == 0 && c < cols) {
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) s += tile[i][cx];
+    out[c] = Elem<Tout>::from_f32(s);
+  }
+}
+
+template <typename Tout>
+int32_t launch_sum_partials(const float* part_a, void* out_a, const float* part_b, void* out_b, int64_t nparts,
+                            int64_t cols, cudaStream_t stream, const char* what) {
+  PartialSums ps;
+  int n = 0;
+  if (out_a != nullptr) { ps.part[n] = part_a; ps.out[n] = out_a; ++n; }
+  if (out_b != nullptr) { ps.part[n] = part_b; ps.out[n] = out_b; ++n; }
+  if (n == 0) return B200_OK;
+  if (n == 1) { ps.part[1] = ps.part[0]; ps.out[1] = ps.out[0]; }
+  sum_partials_kernel<Tout><<<dim3((unsigned)((cols + 31) / 32), (unsigned)n), 1024, 0, stream>>>(ps, nparts, (int)cols);
+  B200_CHECK_LAUNCH(what);
+  return B200_OK;
 }
 
 constexpr int kLnbWarps = 4;      // warps per CTA
-constexpr int kLnbCtasPerSm = 3;  // 12 warps per SM, each with a whole row of loads in flight
+constexpr int kLnbCtasPerSm = 2;  // two rows of up to 2048 columns in registers per lane: 8 warps per SM
+
+// Four consecutive elements as loaded (fp32: 16 bytes, bf16: 8 bytes), widened on use.
+template <typename T>
+struct Raw4;
+template <>
+struct Raw4<float> {
+  float4 v;
+  __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void load_stream(const float* p) { v = __ldcs(reinterpret_cast<const float4*>(p)); }
+  __device__ __forceinline__ void unpack(float (&o)[4]) const { o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+};
+template <>
+struct Raw4<__nv_bfloat16> {
+  uint2 v;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint2*>(p); }
+  __device__ __forceinline__ void load_stream(const __nv_bfloat16* p) { v = __ldcs(reinterpret_cast<const uint2*>(p)); }
+  __device__ __forceinline__ void unpack(float (&o)[4]) const {
+    o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+    o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+  }
+};
 constexpr int kLnbMaxChunks = 16; // 128-column chunks a lane can keep column sums for (2048 columns)
 
 // LayerNorm backward, one WARP per row and no CTA-wide synchronisation while rows stream. A warp
 // walks rows (warp, warp + total, ...); lane l owns columns {128 i + 4 l .. + 3}. With
 // xhat = (x - mean) rstd and g = dy gamma:
 //   dx = rstd (g - mean_j(g) - xhat mean_j(g xhat)),  dgamma = sum_rows dy xhat,  dbeta = sum_rows dy.
-// Pass 1 over a row issues all of its loads at once, takes the two row sums and adds the row into
-// the warp's own column sums (a private strip of shared memory, row order: the row's operands fill
-// the registers); pass 2 re-reads the row -- it is a few KB and sits in L1 -- and writes dx, so HBM
-// sees every operand once. At the end the warps of a CTA add their column sums in warp order and
+// A row is worked on out of registers: pass 1 takes the two row sums and adds the row into the
+// warp's own column sums (a private strip of shared memory, row order), pass 2 writes dx. The
+// warp's NEXT row is loaded into a second register set meanwhile (all loads issued at once), so
+// HBM sees every operand once and every warp always has a row of loads in flight. (Measured
+// against it and no faster: twice the warps with one register set each; a second pass over L1
+// instead of the second register set.) At the end the warps of a CTA add their column sums in warp order and
 // the CTA leaves one partial row in part_g / part_b [grid, cols]; a second kernel adds the CTAs up.
 template <typename Tx, typename Tg, typename Tp, typename Td, int MAXC>
 __global__ void __launch_bounds__(kLnbWarps * 32, kLnbCtasPerSm)
@@ -292,77 +350,98 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
   }
   const float inv_cols = 1.0f / (float)cols;
 
-  for (int64_t row = (int64_t)blockIdx.x * kLnbWarps + warp; row < rows; row += total_warps) {
-    const Tx* xr = x + row * x_rs;
-    const Tg* gr = dy + row * dy_rs;
-    const float mu = mean[row], rs = rstd[row];
-    float s1 = 0.0f, s2 = 0.0f;
-    {
-      // plain loads: the lines are wanted again by the second pass
-      float xv[MAXC][4], gv[MAXC][4];
+  // gamma of the lane's columns, four at a time
+  auto gamma4 = [&](int c, float (&w)[4]) {
+    if (gamma == nullptr) {
+      w[0] = w[1] = w[2] = w[3] = 1.0f;
+    } else {
+      Raw4<Tp> t;
+      t.load(gamma + c);
+      t.unpack(w);
+    }
+  };
+  // Two register sets hold two rows (as loaded: fp32 or bf16): while one row is worked on, the
+  // loads of the warp's next row -- all issued at once -- are in flight into the other.
+  Raw4<Tx> xa[MAXC], xb[MAXC];
+  Raw4<Tg> ga[MAXC], gb[MAXC];
+  auto fetch = [&](int64_t row, Raw4<Tx> (&xr)[MAXC], Raw4<Tg> (&gr)[MAXC]) {
 #pragma unroll
-      for (int i = 0; i < MAXC; ++i) {
-        const int c = 128 * i + 4 * lane;
-        if (c < cols) {
-          if (sizeof(Tx) == 4) {
-            const float4 t = *reinterpret_cast<const float4*>(xr + c);
-            xv[i][0] = t.x; xv[i][1] = t.y; xv[i][2] = t.z; xv[i][3] = t.w;
-          } else {
-            const uint2 t = *reinterpret_cast<const uint2*>(xr + c);
-            xv[i][0] = __uint_as_float(t.x << 16); xv[i][1] = __uint_as_float(t.x & 0xffff0000u);
-            xv[i][2] = __uint_as_float(t.y << 16); xv[i][3] = __uint_as_float(t.y & 0xffff0000u);
-          }
-          if (sizeof(Tg) == 4) {
-            const float4 t = *reinterpret_cast<const float4*>(gr + c);
-            gv[i][0] = t.x; gv[i][1] = t.y; gv[i][2] = t.z; gv[i][3] = t.w;
-          } else {
-            const uint2 t = *reinterpret_cast<const uint2*>(gr + c);
-            gv[i][0] = __uint_as_float(t.x << 16); gv[i][1] = __uint_as_float(t.x & 0xffff0000u);
-            gv[i][2] = __uint_as_float(t.y << 16); gv[i][3] = __uint_as_float(t.y & 0xffff0000u);
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < MAXC; ++i) {
-        const int c = 128 * i + 4 * lane;
-        if (c < cols) {
-          float4 ag = *reinterpret_cast<const float4*>(sm_g + c), ab = *reinterpret_cast<const float4*>(sm_b + c);
-          float* agp = reinterpret_cast<float*>(&ag);
-          float* abp = reinterpret_cast<float*>(&ab);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float xh = (xv[i][j] - mu) * rs;
-            const float gg = gv[i][j] * (gamma != nullptr ? Elem<Tp>::to_f32(gamma[c + j]) : 1.0f);
-            s1 += gg;
-            s2 = fmaf(gg, xh, s2);
-            agp[j] = fmaf(gv[i][j], xh, agp[j]);
-            abp[j] += gv[i][j];
-          }
-          *reinterpret_cast<float4*>(sm_g + c) = ag;
-          *reinterpret_cast<float4*>(sm_b + c) = ab;
-        }
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = 128 * i + 4 * lane;
+      if (c < cols) {
+        xr[i].load_stream(x + row * x_rs + c);
+        gr[i].load_stream(dy + row * dy_rs + c);
       }
     }
-    s1 = warp_sum(s1);
-    s2 = warp_sum(s2);
-    const float c1 = s1 * inv_cols, c2 = s2 * inv_cols;
+  };
+  // The arithmetic is arranged for the packed two-wide FMA pipe and few operations per element:
+  //   xhat = x rs - mu rs,  t = dy xhat,  s1 += dy w,  s2 += t w,  dgamma += t,  dbeta += dy   (pass 1)
+  //   dx = dy (w rs) + x A + B  with  A = -rs^2 c2,  B = rs^2 c2 mu - rs c1                       (pass 2)
+  auto process = [&](int64_t row, const Raw4<Tx> (&xr)[MAXC], const Raw4<Tg> (&gr)[MAXC]) {
+    const float mu = mean[row], rs = rstd[row];
+    const float2 rs2 = make_float2(rs, rs), nmurs2 = make_float2(-mu * rs, -mu * rs);
+    float2 s1 = make_float2(0.0f, 0.0f), s2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = 128 * i + 4 * lane;
+      if (c < cols) {
+        float xv[4], gv[4], w[4];
+        xr[i].unpack(xv);
+        gr[i].unpack(gv);
+        gamma4(c, w);
+        float4 ag = *reinterpret_cast<const float4*>(sm_g + c), ab = *reinterpret_cast<const float4*>(sm_b + c);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float2 x2 = make_float2(xv[2 * h], xv[2 * h + 1]), g2 = make_float2(gv[2 * h], gv[2 * h + 1]);
+          const float2 w2 = make_float2(w[2 * h], w[2 * h + 1]);
+          const float2 xh = __ffma2_rn(x2, rs2, nmurs2);
+          const float2 t = __fmul2_rn(g2, xh);
+          s1 = __ffma2_rn(g2, w2, s1);
+          s2 = __ffma2_rn(t, w2, s2);
+          float2* agp = reinterpret_cast<float2*>(&ag) + h;
+          float2* abp = reinterpret_cast<float2*>(&ab) + h;
+          *agp = __fadd2_rn(*agp, t);
+          *abp = __fadd2_rn(*abp, g2);
+        }
+        *reinterpret_cast<float4*>(sm_g + c) = ag;
+        *reinterpret_cast<float4*>(sm_b + c) = ab;
+      }
+    }
+    const float c1 = warp_sum(s1.x + s1.y) * inv_cols, c2 = warp_sum(s2.x + s2.y) * inv_cols;
+    const float a = -rs * rs * c2, b = rs * rs * c2 * mu - rs * c1;
+    const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
     Td* dr = dx + row * (int64_t)cols;
 #pragma unroll
     for (int i = 0; i < MAXC; ++i) {
       const int c = 128 * i + 4 * lane;
       if (c < cols) {
-        float xv[4], gv[4], o[4];
-        load_vec<Tx, 4>(xr + c, xv);
-        load_vec<Tg, 4>(gr + c, gv);
+        float xv[4], gv[4], w[4], o[4];
+        xr[i].unpack(xv);
+        gr[i].unpack(gv);
+        gamma4(c, w);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float xh = (xv[j] - mu) * rs;
-          const float gg = gv[j] * (gamma != nullptr ? Elem<Tp>::to_f32(gamma[c + j]) : 1.0f);
-          o[j] = rs * (gg - c1 - xh * c2);
+        for (int h = 0; h < 2; ++h) {
+          const float2 x2 = make_float2(xv[2 * h], xv[2 * h + 1]), g2 = make_float2(gv[2 * h], gv[2 * h + 1]);
+          const float2 wr = __fmul2_rn(make_float2(w[2 * h], w[2 * h + 1]), rs2);
+          const float2 r = __ffma2_rn(g2, wr, __ffma2_rn(x2, a2, b2));
+          o[2 * h] = r.x;
+          o[2 * h + 1] = r.y;
         }
         store_vec4<Td>(dr + c, o);
       }
     }
+  };
+
+  int64_t row = (int64_t)blockIdx.x * kLnbWarps + warp;
+  if (row < rows) fetch(row, xa, ga);
+  while (row < rows) {
+    const int64_t row_b = row + total_warps;
+    if (row_b < rows) fetch(row_b, xb, gb);
+    process(row, xa, ga);
+    if (row_b >= rows) break;
+    row = row_b + total_warps;
+    if (row < rows) fetch(row, xa, ga);
+    process(row_b, xb, gb);
   }
 
   // column sums of the CTA: warp order, then one partial row per CTA
@@ -547,16 +626,7 @@ int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* m
         gp, xp, mean, rstd, part_g, part_b, rows, cols, dy_rs, x_rs, per_slab);
     B200_CHECK_LAUNCH("layer_norm_backward(params)");
   }
-  const unsigned fgrid = (unsigned)((cols + 255) / 256);
-  if (dgamma != nullptr) {
-    sum_partials_kernel<Tp><<<fgrid, 256, 0, stream>>>(part_g, static_cast<Tp*>(dgamma), nparts, (int)cols);
-    B200_CHECK_LAUNCH("layer_norm_backward(dgamma)");
-  }
-  if (dbeta != nullptr) {
-    sum_partials_kernel<Tp><<<fgrid, 256, 0, stream>>>(part_b, static_cast<Tp*>(dbeta), nparts, (int)cols);
-    B200_CHECK_LAUNCH("layer_norm_backward(dbeta)");
-  }
-  return B200_OK;
+  return launch_sum_partials<Tp>(part_g, dgamma, part_b, dbeta, nparts, cols, stream, "layer_norm_backward(sums)");
 }
 
 // ---- sum over rows: which form, how many partial rows ----
@@ -595,10 +665,7 @@ int32_t launch_sum_rows(const void* x, void* y, float* ws, int64_t rows, int64_t
                                                                                        per_slab);
   }
   B200_CHECK_LAUNCH("sum_rows");
-  sum_partials_kernel<Tout><<<(unsigned)((cols + 255) / 256), 256, 0, stream>>>(ws, static_cast<Tout*>(y), nparts,
-                                                                               (int)cols);
-  B200_CHECK_LAUNCH("sum_rows(final)");
-  return B200_OK;
+  return launch_sum_partials<Tout>(ws, y, nullptr, nullptr, nparts, cols, stream, "sum_rows(final)");
 }
 
 }  // namespace
