@@ -364,7 +364,9 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
   // loads of the warp's next row -- all issued at once -- are in flight into the other.
   Raw4<Tx> xa[MAXC], xb[MAXC];
   Raw4<Tg> ga[MAXC], gb[MAXC];
-  auto fetch = [&](int64_t row, Raw4<Tx> (&xr)[MAXC], Raw4<Tg> (&gr)[MAXC]) {
+  float2 stat_a, stat_b;  // (mean, rstd) of the row, fetched with it
+  auto fetch = [&](int64_t row, Raw4<Tx> (&xr)[MAXC], Raw4<Tg> (&gr)[MAXC], float2& stat) {
+    stat = make_float2(mean[row], rstd[row]);
 #pragma unroll
     for (int i = 0; i < MAXC; ++i) {
       const int c = 128 * i + 4 * lane;
@@ -377,8 +379,8 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
   // The arithmetic is arranged for the packed two-wide FMA pipe and few operations per element:
   //   xhat = x rs - mu rs,  t = dy xhat,  s1 += dy w,  s2 += t w,  dgamma += t,  dbeta += dy   (pass 1)
   //   dx = dy (w rs) + x A + B  with  A = -rs^2 c2,  B = rs^2 c2 mu - rs c1                       (pass 2)
-  auto process = [&](int64_t row, const Raw4<Tx> (&xr)[MAXC], const Raw4<Tg> (&gr)[MAXC]) {
-    const float mu = mean[row], rs = rstd[row];
+  auto process = [&](int64_t row, const Raw4<Tx> (&xr)[MAXC], const Raw4<Tg> (&gr)[MAXC], float2 stat) {
+    const float mu = stat.x, rs = stat.y;
     const float2 rs2 = make_float2(rs, rs), nmurs2 = make_float2(-mu * rs, -mu * rs);
     float2 s1 = make_float2(0.0f, 0.0f), s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
@@ -433,15 +435,15 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
   };
 
   int64_t row = (int64_t)blockIdx.x * kLnbWarps + warp;
-  if (row < rows) fetch(row, xa, ga);
+  if (row < rows) fetch(row, xa, ga, stat_a);
   while (row < rows) {
     const int64_t row_b = row + total_warps;
-    if (row_b < rows) fetch(row_b, xb, gb);
-    process(row, xa, ga);
+    if (row_b < rows) fetch(row_b, xb, gb, stat_b);
+    process(row, xa, ga, stat_a);
     if (row_b >= rows) break;
     row = row_b + total_warps;
-    if (row < rows) fetch(row, xa, ga);
-    process(row_b, xb, gb);
+    if (row < rows) fetch(row, xa, ga, stat_a);
+    process(row_b, xb, gb, stat_b);
   }
 
   // column sums of the CTA: warp order, then one partial row per CTA
@@ -598,11 +600,17 @@ int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* m
 #define LNB(MAXC)                                                                                              \
   do {                                                                                                         \
     auto kernel = layer_norm_backward_kernel<Tx, Tg, Tp, Td, MAXC>;                                            \
-    if (smem > 48 * 1024) {                                                                                    \
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    /* opt in once per kernel and device to the most this kernel can ask for (2048 columns) */                 \
+    static thread_local bool attr_set[64] = {false};                                                           \
+    int dev = 0;                                                                                               \
+    cudaGetDevice(&dev);                                                                                       \
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {                                                              \
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                                           kLnbWarps * 2 * 128 * kLnbMaxChunks * (int)sizeof(float));          \
       if (e != cudaSuccess)                                                                                    \
-        B200_FAIL(B200_ERR_CUDA, "layer_norm_backward: cannot opt in to %zu bytes of shared memory: %s", smem, \
+        B200_FAIL(B200_ERR_CUDA, "layer_norm_backward: cannot opt in to shared memory: %s",                    \
                   cudaGetErrorString(e));                                                                      \
+      attr_set[dev] = true;                                                                                    \
     }                                                                                                          \
     kernel<<<(unsigned)nparts, kLnbWarps * 32, smem, stream>>>(gp, xp, mean, rstd, wp, op, part_g, part_b, rows, \
                                                                (int)cols, dy_rs, x_rs);                        \

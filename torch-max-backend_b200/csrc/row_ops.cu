@@ -100,20 +100,60 @@ __device__ float block_max(float v, float* smem) {
 // LayerNorm
 // =========================================================================================
 
+// 16 raw bytes of a row (N elements of Tin) -> N fp32 values.
+template <typename Tin, int N>
+__device__ __forceinline__ void unpack_raw(const uint4& t, float (&v)[N]) {
+  if constexpr (sizeof(Tin) == 2) {
+    static_assert(sizeof(Tin) != 2 || N == 8, "16 bytes of bf16");
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+    static_assert(sizeof(Tin) != 4 || N == 4, "16 bytes of fp32");
+    v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y);
+    v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
+  }
+}
+
+// CTAs of a warp-per-row kernel whose warps walk rows with a grid stride and prefetch their next
+// row: one row per warp while that fills the GPU less than 32 CTAs per SM deep, then up to
+// rows_per_warp rows per warp so that the prefetch has something to overlap.
+unsigned prefetching_grid(int64_t rows, int rows_per_warp) {
+  const int64_t ctas_1 = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int64_t ctas_r = (ctas_1 + rows_per_warp - 1) / rows_per_warp;
+  const int64_t floor_ctas = (int64_t)sm_count() * 32;
+  return (unsigned)(ctas_1 <= floor_ctas ? ctas_1 : (ctas_r > floor_ctas ? ctas_r : floor_ctas));
+}
+
 // One warp per row; the row lives in registers between the three uses (mean, variance,
-// normalise). N = elements per chunk (16 bytes of Tin), MAXC = chunks per lane.
+// normalise). N = elements per chunk (16 bytes of Tin), MAXC = chunks per lane. A warp walks rows
+// with a grid stride and issues the 16-byte loads of its NEXT row as soon as the current one is
+// unpacked, so the loads overlap the two reductions and the stores.
 template <typename Tin, typename Tp, typename Tout, int N, int MAXC>
 __global__ void __launch_bounds__(kRowThreads)
 layer_norm_warp_kernel(const Tin* __restrict__ x, const Tp* __restrict__ gamma,
                        const Tp* __restrict__ beta, Tout* __restrict__ y,
                        float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t rows,
                        int cols, int64_t x_row_stride, float eps) {
+  static_assert(N * sizeof(Tin) == 16, "one chunk is one 16-byte load");
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  const int64_t stride = (int64_t)gridDim.x * kWarpsPerCta;
+  int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int nchunks = cols / N;
-  const Tin* xr = x + row * x_row_stride;
-
+  uint4 raw[MAXC];
+  auto fetch = [&](int64_t r) {
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunks) raw[i] = __ldcs(reinterpret_cast<const uint4*>(x + r * x_row_stride + c * N));
+    }
+  };
+  fetch(row);
+  while (true) {
   // The three uses of the row run on packed fp32 instructions (two elements per add / mul /
   // fma): at power-capped clocks the narrow-type variants are bound by instruction issue, not HBM.
   float v[MAXC][N];
@@ -122,11 +162,13 @@ layer_norm_warp_kernel(const Tin* __restrict__ x, const Tp* __restrict__ gamma,
   for (int i = 0; i < MAXC; ++i) {
     const int c = lane + 32 * i;
     if (c < nchunks) {
-      Chunk<Tin, N>::load(xr + c * N, v[i]);
+      unpack_raw<Tin, N>(raw[i], v[i]);
 #pragma unroll
       for (int j = 0; j < N; j += 2) sum2 = __fadd2_rn(sum2, make_float2(v[i][j], v[i][j + 1]));
     }
   }
+  const int64_t next = row + stride;
+  if (next < rows) fetch(next);
   const float mean = warp_sum(sum2.x + sum2.y) / (float)cols;
   const float2 neg_mean2 = make_float2(-mean, -mean);
   float2 sq2 = make_float2(0.0f, 0.0f);
@@ -178,6 +220,9 @@ layer_norm_warp_kernel(const Tin* __restrict__ x, const Tp* __restrict__ gamma,
   if (lane == 0) {
     if (mean_out != nullptr) mean_out[row] = mean;
     if (rstd_out != nullptr) rstd_out[row] = rstd;
+  }
+  if (next >= rows) break;
+  row = next;
   }
 }
 
@@ -351,7 +396,7 @@ int32_t launch_layer_norm(const void* x, const void* gamma, const void* beta, vo
       B200_CHECK_LAUNCH("layer_norm");
       return B200_OK;
     }
-    const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+    const unsigned grid = prefetching_grid(rows, 4);
 #define LN_LAUNCH(MAXC)                                                                   \
   layer_norm_warp_kernel<Tin, Tp, Tout, N, MAXC><<<grid, kRowThreads, 0, stream>>>(         \
       xp, gp, bp, yp, mean, rstd, rows, (int)cols, x_row_stride, eps)
@@ -384,24 +429,6 @@ struct RowMask {
   int invert;
   float fill;
 };
-
-// 16 raw bytes of a row (N elements of Tin) -> N fp32 values.
-template <typename Tin, int N>
-__device__ __forceinline__ void unpack_raw(const uint4& t, float (&v)[N]) {
-  if constexpr (sizeof(Tin) == 2) {
-    static_assert(sizeof(Tin) != 2 || N == 8, "16 bytes of bf16");
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-  } else {
-    static_assert(sizeof(Tin) != 4 || N == 4, "16 bytes of fp32");
-    v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y);
-    v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
-  }
-}
 
 // One warp per row, the row in registers; a warp walks rows with a grid stride and issues the
 // 16-byte loads of its NEXT row before it reduces the current one, so every resident warp keeps a
@@ -576,12 +603,7 @@ int32_t launch_softmax(const void* x, void* y, int64_t rows, int64_t cols, int64
                       (mask.ptr == nullptr || (aligned_to(mask.ptr, N) && mask.stride % N == 0));
   if (vec_ok) {
     const int per_lane = (int)((cols / N + 31) / 32);
-    // Rows per warp: one while that fills the GPU less than four times over, then up to
-    // kSoftmaxRowsPerWarp so that the prefetch of the next row has something to overlap.
-    const int64_t ctas_1 = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
-    const int64_t ctas_r = (ctas_1 + softmax_rows_per_warp() - 1) / softmax_rows_per_warp();
-    const int64_t floor_ctas = (int64_t)sm_count() * 32;
-    const unsigned grid = (unsigned)(ctas_1 <= floor_ctas ? ctas_1 : (ctas_r > floor_ctas ? ctas_r : floor_ctas));
+    const unsigned grid = prefetching_grid(rows, softmax_rows_per_warp());
 #define SM_LAUNCH(MAXC)                                                                      \
   do {                                                                                       \
     if (mask.ptr != nullptr)                                                                 \
