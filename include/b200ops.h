@@ -311,6 +311,41 @@ typedef struct b200_sdpa_args {
 B200_API int32_t b200_sdpa_route(const b200_sdpa_args* args);
 B200_API int32_t b200_sdpa_fwd(const b200_sdpa_args* args, b200_stream_t stream);
 
+/* Gradients of b200_sdpa_fwd: dq, dk, dv (contiguous [batch, heads, len, head_dim], dtype of q) from
+ * d_out, the forward's output o and its natural-log LSE (fp32 [batch, heads, q_len], contiguous).
+ * bf16 with head_dim 64 only (the tensor-core kernel); anything else is B200_ERR_UNSUPPORTED and the
+ * caller composes the gradient from b200_gemm / b200_softmax_backward. Per 128-key tile one CTA keeps
+ * dK and dV in tensor memory and walks the query tiles; the shares of dQ are written per key tile
+ * to the workspace (b200_sdpa_bwd_workspace_bytes, 256-byte aligned) and added in tile order, so
+ * the result does not depend on scheduling.
+ * Replaces: aten._scaled_dot_product_flash_attention_backward through the FA4 backward bridge
+ * (torch_mojo_backend/eager_flash_attention/fa4_bwd_kernel.mojo, fa4_bwd_launch.mojo). */
+typedef struct b200_sdpa_bwd_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_out;
+  const float* lse;
+  void* dq;
+  void* dk;
+  void* dv;
+  void* workspace;
+  size_t workspace_bytes;
+  int64_t batch, heads, q_len, kv_len, head_dim;
+  int64_t q_strides[3]; /* batch, head, position */
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t o_strides[3];
+  int64_t d_out_strides[3];
+  float scale;
+  int32_t causal;
+  int32_t dtype;
+} b200_sdpa_bwd_args;
+
+B200_API size_t b200_sdpa_bwd_workspace_bytes(const b200_sdpa_bwd_args* args);
+B200_API int32_t b200_sdpa_bwd(const b200_sdpa_bwd_args* args, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -84,6 +84,10 @@ class _StandIns:
         return torch.cat(list(tensors), dim)
 
     @staticmethod
+    def sdpa_backward_supported(q, k, v):
+        return False
+
+    @staticmethod
     def sdpa(q, k, v, causal=False, scale=None, route=0):
         out = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
         return out, torch.zeros(q.shape[:3])

@@ -147,6 +147,30 @@ def test_gemm_with_transposed_a(ops, b_layout, m, n, k):
     assert_parity(auto, want.float(), bf16=False, scale=float(want.abs().max()) * 20)
 
 
+def test_gemm_operands_with_unaligned_pitch_stay_on_the_tensor_cores(ops):
+    """The gradient of the logits is [tokens, 50257] bf16 with a 50257-element pitch: both LM-head gradient
+    GEMMs (dX = dL W, dW = dL^T X) must not fall to the CUDA-core kernel (they are re-pitched once)."""
+    import time
+
+    tokens, vocab, d = 2048, 50257, 256
+    dl = gen((tokens, vocab), torch.bfloat16, 76, std=0.05).cuda()
+    w = gen((vocab, d), torch.bfloat16, 77, std=0.05).cuda()
+    x = gen((tokens, d), torch.bfloat16, 78).cuda()
+    assert dl.stride(0) % 8 != 0
+    dx = ops.gemm(dl, w, None, None, 1.0, 1.0, 0, torch.float32)
+    dw = ops.gemm(dl.t(), x, None, None, 1.0, 1.0, 0, torch.float32)
+    want_dx = dl.double() @ w.double()
+    want_dw = dl.double().t() @ x.double()
+    assert_parity(dx, want_dx.float(), bf16=False, scale=float(want_dx.abs().max()) * 20)
+    assert_parity(dw, want_dw.float(), bf16=False, scale=float(want_dw.abs().max()) * 20)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        ops.gemm(dl, w, None, None, 1.0, 1.0, 0, torch.float32)
+    torch.cuda.synchronize()
+    assert (time.perf_counter() - t0) / 3 < 5e-3, "52 GFLOP must take well under the CUDA-core kernel's ~15 ms"
+
+
 def test_batched_gemm_with_transposed_a(ops):
     at = gen((6, 256, 192), torch.bfloat16, 61)   # [batch, k, m]
     b = gen((6, 256, 64), torch.bfloat16, 62)     # [batch, k, n]
@@ -167,6 +191,42 @@ def test_attention_backward(dtype, causal):
     for got, ref, name in zip((dq, dk, dv), want, "qkv"):
         assert got.dtype == dtype and got.shape == ref.shape
         assert_parity(got, ref, bf16=dtype == torch.bfloat16, what=f"d{name}")
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,H,T,S", [(1, 1, 128, 128), (2, 3, 256, 256), (1, 2, 300, 300), (2, 2, 1024, 1024),
+                                     (1, 2, 200, 333), (1, 1, 384, 130)])
+def test_fused_attention_backward(ops, causal, B, H, T, S):
+    """b200_sdpa_bwd (tensor cores, bf16, head_dim 64) against the float64 oracle, with the forward's own
+    output and LSE as its inputs; ragged lengths, more keys than queries and the reverse."""
+    if causal and T != S:
+        pytest.skip("causal attention is exercised with equal lengths")
+    q = gen((B, H, T, 64), torch.bfloat16, 70, std=0.8)
+    k = gen((B, H, S, 64), torch.bfloat16, 71, std=0.8)
+    v = gen((B, H, S, 64), torch.bfloat16, 72, std=0.8)
+    d_out = gen((B, H, T, 64), torch.bfloat16, 73, std=0.8)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    o, lse = ops.sdpa(qc, kc, vc, causal)
+    dq, dk, dv = ops.sdpa_backward(d_out.cuda(), qc, kc, vc, o, lse, causal)
+    want = ref_ops.sdpa_backward(d_out, q, k, v, causal)
+    for got, ref, name in zip((dq, dk, dv), want, "qkv"):
+        assert got.dtype == torch.bfloat16 and got.shape == ref.shape
+        assert_parity(got, ref, bf16=True, what=f"d{name}")
+    again = ops.sdpa_backward(d_out.cuda(), qc, kc, vc, o, lse, causal)
+    assert all(torch.equal(a, b) for a, b in zip(again, (dq, dk, dv))), "fixed-order sums: bit-identical reruns"
+
+
+def test_fused_attention_backward_on_fused_qkv_views(ops):
+    """q, k, v as strided views of one [B, T, 3 H 64] projection (no copies), d_out in the forward's layout."""
+    B, H, T = 2, 4, 512
+    qkv = gen((B, T, 3 * H * 64), torch.bfloat16, 74, std=0.8)
+    q, k, v = (t.view(B, T, H, 64).transpose(1, 2) for t in qkv.split(H * 64, dim=2))
+    d_out = gen((B, T, H, 64), torch.bfloat16, 75, std=0.8).transpose(1, 2)
+    qc, kc, vc = (t.view(B, T, H, 64).transpose(1, 2) for t in qkv.cuda().split(H * 64, dim=2))
+    o, lse = ops.sdpa(qc, kc, vc, True)
+    dq, dk, dv = ops.sdpa_backward(d_out.cuda(), qc, kc, vc, o, lse, True)
+    for got, ref, name in zip((dq, dk, dv), ref_ops.sdpa_backward(d_out, q, k, v, True), "qkv"):
+        assert_parity(got, ref, bf16=True, what=f"d{name}")
 
 
 @pytest.mark.parametrize("attention", ["sdpa", "masked_softmax"])

@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--by-shape", action="store_true", help="break the GEMM time of the profiled step down by shape")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("bench_training.py needs a CUDA device: the b200 kernels have no CPU fallback")
@@ -67,6 +68,7 @@ def main():
     launches = (native.launch_count - before) // args.steps
 
     native.profiler = native.KernelProfiler()
+    native.profiler.by_shape = args.by_shape
     step()
     per_op = native.profiler.summary()
     native.profiler = None

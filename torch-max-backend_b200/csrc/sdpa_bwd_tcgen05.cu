@@ -1,0 +1,583 @@
+// Attention backward on the 5th-generation tensor cores for head_dim 64, bf16.
+//
+// One work item is a 128-key tile (K_i, V_i) of one (batch, head); the CTA that owns it keeps dK_i and
+// dV_i in tensor memory and walks the 128-row query tiles j that attend to it (all of them, or
+// j >= i under a causal mask). Per (i, j), with the forward's LSE and delta = rowsum(dO * O):
+//   S  = Q_j K_i^T            dP = dO_j V_i^T                       (two MMAs into tensor memory)
+//   P  = exp2(S scale log2e - LSE log2e),  dS = scale P (dP - delta) (one thread per query row)
+//   dV_i += P^T dO_j          dK_i += dS^T Q_j      dQ_j(i) = dS K_i (three MMAs)
+// P and dS go to shared memory as bf16 in the [query row][key] layout with the 128-byte swizzle of
+// the TMA tiles; that one layout is the K-major A operand of dS K and, read through the MN-major
+// descriptor, the transposed A operand of P^T dO and dS^T Q. K, V, Q and dO tiles are [row][64]
+// TMA tiles exactly as in the forward kernel, used K-major for S and dP and MN-major (as B) for the
+// three products that contract over rows.
+// dQ_j gets a contribution from every key tile; tile i writes its own to a partial buffer
+// [batch*heads, key tile, row, 64] (fp32) and a second kernel adds the tiles up in tile order, so
+// the gradient does not depend on which CTA ran first (no atomics).
+//   warp 0      TMA producer: K_i, V_i per item; Q_j, dO_j into a two-deep ring.
+//   warp 1      MMA issuer (converged warp, one elected lane).
+//   warps 2-5   one thread per query row: P and dS, the dQ partial, and at the end of the item dK, dV.
+// Tensor memory: S 128 columns, dP 128, dV 64, dK 64, dQ 64. Items are ordered by key tile, so
+// the tiles with the most query tiles (the first ones under a causal mask) start first.
+// Every wait is bounded (ptx::mbar_wait); a CTA that gives up raises its abort flag, sets the
+// device status bit and leaves through the normal teardown.
+#include "ptx.cuh"
+#include "sdpa_internal.cuh"
+#include "tma.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;  // query rows per tile
+constexpr int BN = 128;  // keys per tile
+constexpr int D = 64;
+constexpr int kThreads = 6 * 32;
+constexpr int TILE_BYTES = 128 * D * 2;  // 16 KiB: a [128][64] bf16 tile; also one 64-key half of P / dS
+constexpr int kTmemCols = 512;
+constexpr int TMEM_S = 0, TMEM_DP = 128, TMEM_DV = 256, TMEM_DK = 320, TMEM_DQ = 384;
+
+constexpr int SMEM_K = 0;
+constexpr int SMEM_V = SMEM_K + TILE_BYTES;
+constexpr int SMEM_Q = SMEM_V + TILE_BYTES;         // two stages
+constexpr int SMEM_DO = SMEM_Q + 2 * TILE_BYTES;    // two stages
+constexpr int SMEM_P = SMEM_DO + 2 * TILE_BYTES;    // [2 key halves][128 rows][64 keys]
+constexpr int SMEM_DS = SMEM_P + 2 * TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_DS + 2 * TILE_BYTES;
+constexpr int kNumBars = 14;
+constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
+constexpr int SMEM_BYTES = SMEM_MISC + 16 + 1024;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM exceeded");
+
+struct Params {
+  const float* lse;    // [bh, q_len] natural log
+  const float* delta;  // [bh, q_len]
+  float* dq_part;      // [bh, kv_tiles, q_len, 64]
+  __nv_bfloat16* dk;   // [bh, kv_len, 64]
+  __nv_bfloat16* dv;
+  uint32_t heads, bh;
+  int32_t q_len, kv_len, q_tiles, kv_tiles;
+  float scale, scale_log2;
+  int causal;
+  uint32_t num_items;  // kv_tiles * bh
+  int q_heads_inner, k_heads_inner, v_heads_inner, do_heads_inner;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 16 bytes (eight bf16) of row r, 16-byte unit u of a [rows][64] tile with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz(uint32_t tile, int r, int u) {
+  return tile + (uint32_t)r * 128u + (uint32_t)((u ^ (r & 7)) << 4);
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                        Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t base = ptx::smem_u32(smem);
+  const uint32_t k_smem = base + SMEM_K, v_smem = base + SMEM_V, q_smem = base + SMEM_Q, do_smem = base + SMEM_DO;
+  const uint32_t p_smem = base + SMEM_P, ds_smem = base + SMEM_DS;
+  const uint32_t bar = base + SMEM_BAR;
+  // Each barrier is used once per item or once per (i, j) step by one producer and one consumer
+  // side, in strict alternation, so use n is waited for with parity n & 1.
+  const uint32_t kv_full = bar, kv_empty = bar + 8;                  // per item
+  auto qd_full = [&](int s) { return bar + 8u * (2 + s); };         // per step, two stages
+  auto qd_empty = [&](int s) { return bar + 8u * (4 + s); };
+  const uint32_t sdp_full = bar + 8 * 6;    // S and dP are in tensor memory
+  const uint32_t sdp_free = bar + 8 * 7;    // the row threads have read them (4 warps)
+  const uint32_t pds_full = bar + 8 * 8;    // P and dS are in shared memory (4 warps)
+  const uint32_t pds_free = bar + 8 * 9;    // the three MMAs that read them have completed
+  const uint32_t dq_full = bar + 8 * 10;    // dQ_j(i) is in tensor memory
+  const uint32_t dq_free = bar + 8 * 11;    // the row threads have read it (4 warps)
+  const uint32_t acc_full = bar + 8 * 12;   // dK_i, dV_i complete (per item)
+  const uint32_t acc_free = bar + 8 * 13;   // the row threads have read them (4 warps)
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + SMEM_MISC);
+  volatile uint32_t* tmem_holder = misc;
+  volatile uint32_t* abort_flag = misc + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(kv_full, 1);
+    ptx::mbar_init(kv_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(qd_full(s), 1);
+      ptx::mbar_init(qd_empty(s), 1);
+    }
+    ptx::mbar_init(sdp_full, 1);
+    ptx::mbar_init(sdp_free, 4);
+    ptx::mbar_init(pds_full, 4);
+    ptx::mbar_init(pds_free, 1);
+    ptx::mbar_init(dq_full, 1);
+    ptx::mbar_init(dq_free, 4);
+    ptx::mbar_init(acc_full, 1);
+    ptx::mbar_init(acc_free, 4);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tmap_q);
+    ptx::prefetch_tensormap(&tmap_k);
+    ptx::prefetch_tensormap(&tmap_v);
+    ptx::prefetch_tensormap(&tmap_do);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem = *tmem_holder;
+
+  // item w -> (key tile i, batch*head index): key tiles outermost, so the longest items start first
+  auto item_tile = [&](uint32_t w) { return (int)(w / p.bh); };
+  auto item_bh = [&](uint32_t w) { return w - (w / p.bh) * p.bh; };
+  auto first_q_tile = [&](int i) { return p.causal ? i : 0; };  // rows of tile j >= i see keys of tile i
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t items = 0, steps = 0;
+      bool ok = true;
+      for (uint32_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
+        const int i = item_tile(w);
+        const uint32_t bh = item_bh(w);
+        const int32_t b = (int32_t)(bh / p.heads), h = (int32_t)(bh - (uint32_t)b * p.heads);
+        if (!ptx::mbar_wait_relaxed(kv_empty, (items & 1) ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+        if (p.k_heads_inner) ptx::tma_load_4d(k_smem, &tmap_k, kv_full, 0, h, i * BN, b);
+        else ptx::tma_load_4d(k_smem, &tmap_k, kv_full, 0, i * BN, h, b);
+        if (p.v_heads_inner) ptx::tma_load_4d(v_smem, &tmap_v, kv_full, 0, h, i * BN, b);
+        else ptx::tma_load_4d(v_smem, &tmap_v, kv_full, 0, i * BN, h, b);
+        for (int j = first_q_tile(i); j < p.q_tiles; ++j, ++steps) {
+          const int s = steps & 1;
+          if (!ptx::mbar_wait_relaxed(qd_empty(s), ((steps >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(qd_full(s), 2 * TILE_BYTES);
+          if (p.q_heads_inner) ptx::tma_load_4d(q_smem + s * TILE_BYTES, &tmap_q, qd_full(s), 0, h, j * BM, b);
+          else ptx::tma_load_4d(q_smem + s * TILE_BYTES, &tmap_q, qd_full(s), 0, j * BM, h, b);
+          if (p.do_heads_inner) ptx::tma_load_4d(do_smem + s * TILE_BYTES, &tmap_do, qd_full(s), 0, h, j * BM, b);
+          else ptx::tma_load_4d(do_smem + s * TILE_BYTES, &tmap_do, qd_full(s), 0, j * BM, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc_s = ptx::idesc_bf16_f32(BM, BN, 0, 0);   // S, dP: both operands K-major
+    constexpr uint32_t idesc_t = ptx::idesc_bf16_f32(BN, D, 1, 1);    // dV, dK: A read transposed, B = [row][d]
+    constexpr uint32_t idesc_q = ptx::idesc_bf16_f32(BM, D, 0, 1);    // dQ: A = dS K-major, B = K_i [key][d]
+    uint32_t items = 0, steps = 0, accs = 0;  // accs: items that had query tiles (the ones that use dK / dV)
+    bool ok = true;
+    for (uint32_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
+      const int i = item_tile(w);
+      const int j0 = first_q_tile(i);
+      if (j0 >= p.q_tiles) {
+        // no query row attends to this key tile: nothing to accumulate; free K/V for the next item
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(kv_full, items & 1, abort_flag))) break;
+        if (ptx::elect_one()) ptx::tc_commit(kv_empty);
+        __syncwarp();
+        continue;
+      }
+      bool go = ptx::mbar_wait(kv_full, items & 1, abort_flag);
+      // dK / dV restart with this item: the row threads must have read the previous item's
+      if (accs > 0) go = go && ptx::mbar_wait(acc_free, (accs - 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, go)) break;
+      ++accs;
+      for (int j = j0; j < p.q_tiles; ++j, ++steps) {
+        const int s = steps & 1;
+        go = ptx::mbar_wait(qd_full(s), (steps >> 1) & 1, abort_flag);
+        if (steps > 0) go = go && ptx::mbar_wait(sdp_free, (steps - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t qs = q_smem + s * TILE_BYTES, dos = do_smem + s * TILE_BYTES;
+        if (ptx::elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_S, ptx::smem_desc_sw128(qs + kk * 32, 0, 1024),
+                            ptx::smem_desc_sw128(k_smem + kk * 32, 0, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_DP, ptx::smem_desc_sw128(dos + kk * 32, 0, 1024),
+                            ptx::smem_desc_sw128(v_smem + kk * 32, 0, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(sdp_full);
+        }
+        __syncwarp();
+        go = ptx::mbar_wait(pds_full, steps & 1, abort_flag);
+        if (steps > 0) go = go && ptx::mbar_wait(dq_free, (steps - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        if (ptx::elect_one()) {
+          const uint32_t acc = j > j0 ? 1u : 0u;
+          // contraction over the 128 query rows: eight steps of 16 rows; A = P^T / dS^T through the
+          // MN-major descriptor (two 64-key halves 16 KiB apart, 8-row groups 1 KiB apart)
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_DV, ptx::smem_desc_sw128(p_smem + kk * 2048, TILE_BYTES, 1024),
+                            ptx::smem_desc_sw128(dos + kk * 2048, 0, 1024), idesc_t, (acc | (kk > 0)) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_DK, ptx::smem_desc_sw128(ds_smem + kk * 2048, TILE_BYTES, 1024),
+                            ptx::smem_desc_sw128(qs + kk * 2048, 0, 1024), idesc_t, (acc | (kk > 0)) ? 1u : 0u);
+          }
+          // contraction over the 128 keys: A = dS K-major (16 keys = 32 bytes inside a 64-key half)
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_DQ,
+                            ptx::smem_desc_sw128(ds_smem + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024),
+                            ptx::smem_desc_sw128(k_smem + kk * 2048, 0, 1024), idesc_q, kk > 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(dq_full);
+          ptx::tc_commit(pds_free);
+          ptx::tc_commit(qd_empty(s));
+          if (j + 1 == p.q_tiles) {
+            ptx::tc_commit(acc_full);
+            ptx::tc_commit(kv_empty);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---------------- row threads: warps 2-5 ----------------
+    const int quad = warp & 3;       // TMEM lane quadrant this warp may access
+    const int r = quad * 32 + lane;  // row of the tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    uint32_t items = 0, steps = 0, accs = 0;
+    bool ok = true;
+    for (uint32_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
+      const int i = item_tile(w);
+      const uint32_t bh = item_bh(w);
+      const int j0 = first_q_tile(i);
+      const int32_t kv0 = i * BN;
+      const int32_t key = kv0 + r;  // the key this thread owns in the dK / dV epilogue
+      __nv_bfloat16* dk_row = p.dk + ((int64_t)bh * p.kv_len + key) * D;
+      __nv_bfloat16* dv_row = p.dv + ((int64_t)bh * p.kv_len + key) * D;
+      if (j0 >= p.q_tiles) {
+        if (key < p.kv_len) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            reinterpret_cast<uint4*>(dk_row)[c] = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<uint4*>(dv_row)[c] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
+      for (int j = j0; j < p.q_tiles; ++j, ++steps) {
+        const int32_t row = j * BM + r;
+        const bool live = row < p.q_len;
+        const float lse2 = live ? p.lse[(int64_t)bh * p.q_len + row] * 1.4426950408889634f : 0.0f;
+        const float delta = live ? p.delta[(int64_t)bh * p.q_len + row] : 0.0f;
+        bool go = ptx::mbar_wait(sdp_full, steps & 1, abort_flag);
+        if (steps > 0) go = go && ptx::mbar_wait(pds_free, (steps - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        // keys [kv0, kv0 + visible) of the tile are visible to this row
+        int32_t visible = p.kv_len - kv0;
+        if (p.causal && row - kv0 + 1 < visible) visible = row - kv0 + 1;
+        if (!live) visible = 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t sv[32], dpv[32];
+          ptx::tmem_ld_32x32b_x32(tmem + TMEM_S + c * 32 + lane_addr, sv);
+          ptx::tmem_ld_32x32b_x32(tmem + TMEM_DP + c * 32 + lane_addr, dpv);
+          ptx::tmem_ld_wait();
+          uint32_t pp[16], dd[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float p0 = ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
+            float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -lse2));
+            if (c * 32 + e >= visible) p0 = 0.0f;
+            if (c * 32 + e + 1 >= visible) p1 = 0.0f;
+            const float d0 = p.scale * p0 * (__uint_as_float(dpv[e]) - delta);
+            const float d1 = p.scale * p1 * (__uint_as_float(dpv[e + 1]) - delta);
+            pp[e >> 1] = pack_bf16x2(p0, p1);
+            dd[e >> 1] = pack_bf16x2(d0, d1);
+          }
+          // 32 keys = four 16-byte units of this row in the 64-key half (c >> 1)
+          const uint32_t half_p = p_smem + (c >> 1) * TILE_BYTES, half_d = ds_smem + (c >> 1) * TILE_BYTES;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int unit = (c & 1) * 4 + u;
+            st_shared_v4(swz(half_p, r, unit), pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+            st_shared_v4(swz(half_d, r, unit), dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+          }
+        }
+        // S / dP have been read; P / dS are written: make them visible to the tensor core's proxy
+        ptx::tc_fence_before_sync();
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(sdp_free);
+          ptx::mbar_arrive(pds_full);
+        }
+        // this key tile's share of dQ_j
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(dq_full, steps & 1, abort_flag))) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        float* part = p.dq_part + (((int64_t)bh * p.kv_tiles + i) * p.q_len + row) * D;
+#pragma unroll
+        for (int hcol = 0; hcol < 2; ++hcol) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32b_x32(tmem + TMEM_DQ + hcol * 32 + lane_addr, o);
+          ptx::tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              reinterpret_cast<uint4*>(part)[hcol * 8 + c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(dq_free);
+      }
+      if (!ok) break;
+      // ---- end of the item: dK_i and dV_i, one key per thread
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(acc_full, accs & 1, abort_flag))) { ok = false; break; }
+      ++accs;
+      ptx::tc_fence_after_sync();
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* out = which ? dv_row : dk_row;
+#pragma unroll
+        for (int hcol = 0; hcol < 2; ++hcol) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32b_x32(tmem + (which ? TMEM_DV : TMEM_DK) + hcol * 32 + lane_addr, o);
+          ptx::tmem_ld_wait();
+          if (key < p.kv_len) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 t;
+              t.x = pack_bf16x2(__uint_as_float(o[8 * c + 0]), __uint_as_float(o[8 * c + 1]));
+              t.y = pack_bf16x2(__uint_as_float(o[8 * c + 2]), __uint_as_float(o[8 * c + 3]));
+              t.z = pack_bf16x2(__uint_as_float(o[8 * c + 4]), __uint_as_float(o[8 * c + 5]));
+              t.w = pack_bf16x2(__uint_as_float(o[8 * c + 6]), __uint_as_float(o[8 * c + 7]));
+              reinterpret_cast<uint4*>(out)[hcol * 4 + c] = t;
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(acc_free);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    if (threadIdx.x == 0) atomicOr(p.status, STATUS_SDPA_TIMEOUT);
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// delta[bh, row] = sum_d dO * O: one thread per row, 16-byte loads.
+__global__ void sdpa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_out,
+                                  float* __restrict__ delta, int64_t rows, int64_t heads, int64_t q_len,
+                                  int64_t os_b, int64_t os_h, int64_t os_t, int64_t ds_b, int64_t ds_h,
+                                  int64_t ds_t) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows) return;
+  const int64_t t = idx % q_len, bh = idx / q_len;
+  const int64_t b = bh / heads, h = bh - b * heads;
+  const __nv_bfloat16* op = o + b * os_b + h * os_h + t * os_t;
+  const __nv_bfloat16* dp = d_out + b * ds_b + h * ds_h + t * ds_t;
+  float acc = 0.0f;
+#pragma unroll
+  for (int c = 0; c < D / 8; ++c) {
+    float a[8], g[8];
+    load16(op + 8 * c, a);
+    load16(dp + 8 * c, g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc = fmaf(a[e], g[e], acc);
+  }
+  delta[idx] = acc;
+}
+
+// dq[bh, row, :] = sum over the key tiles that row attends to, in tile order; one thread per 4 columns.
+__global__ void sdpa_dq_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dq, int64_t bh_count,
+                                      int32_t q_len, int32_t kv_tiles, int causal) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // over bh * q_len * 16
+  const int64_t total = bh_count * q_len * (D / 4);
+  if (idx >= total) return;
+  const int c4 = (int)(idx % (D / 4));
+  const int64_t rowi = idx / (D / 4);
+  const int32_t row = (int32_t)(rowi % q_len);
+  const int64_t bh = rowi / q_len;
+  int last = kv_tiles - 1;
+  if (causal && row / BM < last) last = row / BM;
+  float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int i = 0; i <= last; ++i) {
+    const float4 t = __ldcs(reinterpret_cast<const float4*>(part + ((bh * kv_tiles + i) * q_len + row) * D) + c4);
+    s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+  }
+  uint2 o;
+  o.x = pack_bf16x2(s.x, s.y);
+  o.y = pack_bf16x2(s.z, s.w);
+  reinterpret_cast<uint2*>(dq + rowi * D)[c4] = o;
+}
+
+// Byte strides of the (position, head, batch) dims with legal stand-ins for size-1 dims.
+void byte_strides(const int64_t* s, int64_t batch, int64_t heads, int64_t len, uint64_t* st, uint64_t* sh,
+                  uint64_t* sb) {
+  *st = (uint64_t)(len > 1 ? s[2] : D) * 2;
+  *sh = heads > 1 ? (uint64_t)s[1] * 2 : *st * (uint64_t)(len > 0 ? len : 1);
+  const uint64_t big = (*st * (uint64_t)len > *sh * (uint64_t)heads) ? *st * (uint64_t)len : *sh * (uint64_t)heads;
+  *sb = batch > 1 ? (uint64_t)s[0] * 2 : big;
+}
+
+// Tensor map over [batch, heads, len, 64] with boxes of 128 positions; dims innermost first with
+// ascending strides ((d, pos, head, batch) or (d, head, pos, batch)); *heads_inner says which.
+int32_t make_map(CUtensorMap* map, const void* ptr, int64_t batch, int64_t heads, int64_t len,
+                 const int64_t* strides, int* heads_inner) {
+  uint64_t st, sh, sb;
+  byte_strides(strides, batch, heads, len, &st, &sh, &sb);
+  *heads_inner = sh < st ? 1 : 0;
+  if (*heads_inner) {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)heads, (uint64_t)len, (uint64_t)batch};
+    const uint64_t str[3] = {sh, st, sb};
+    const uint32_t box[4] = {(uint32_t)D, 1, 128, 1};
+    return encode_tensor_map(map, B200_BF16, 4, ptr, dims, str, box, true);
+  }
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)len, (uint64_t)heads, (uint64_t)batch};
+  const uint64_t str[3] = {st, sh, sb};
+  const uint32_t box[4] = {(uint32_t)D, 128, 1, 1};
+  return encode_tensor_map(map, B200_BF16, 4, ptr, dims, str, box, true);
+}
+
+bool strides_ok(const int64_t* s, int64_t batch, int64_t heads, int64_t len) {
+  if (len > 1 && (s[2] % 8 != 0 || s[2] < D)) return false;
+  if (heads > 1 && (s[1] % 8 != 0 || s[1] < D)) return false;
+  if (batch > 1 && (s[0] % 8 != 0 || s[0] < D)) return false;
+  uint64_t st, sh, sb;
+  byte_strides(s, batch, heads, len, &st, &sh, &sb);
+  return sb >= st && sb >= sh;  // batch must be the outermost dim
+}
+
+size_t align256(size_t n) { return (n + 255) / 256 * 256; }
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+namespace {
+const char* sdpa_bwd_ineligible(const b200_sdpa_bwd_args& a) {
+  if (a.dtype != B200_BF16) return "tensors are not bf16";
+  if (a.head_dim != D) return "head_dim is not 64";
+  if (a.q_len <= 0 || a.kv_len <= 0) return "empty sequence";
+  if (!(a.scale > 0.0f)) return "scale is not positive";
+  if (!aligned_to(a.q, 16) || !aligned_to(a.k, 16) || !aligned_to(a.v, 16) || !aligned_to(a.o, 16) ||
+      !aligned_to(a.d_out, 16) || !aligned_to(a.dq, 16) || !aligned_to(a.dk, 16) || !aligned_to(a.dv, 16))
+    return "pointer not 16-byte aligned";
+  if (!strides_ok(a.q_strides, a.batch, a.heads, a.q_len) || !strides_ok(a.k_strides, a.batch, a.heads, a.kv_len) ||
+      !strides_ok(a.v_strides, a.batch, a.heads, a.kv_len) || !strides_ok(a.d_out_strides, a.batch, a.heads, a.q_len))
+    return "stride not a multiple of 16 bytes";
+  if (a.o_strides[0] % 8 != 0 || a.o_strides[1] % 8 != 0 || a.o_strides[2] % 8 != 0) return "output stride not a multiple of 16 bytes";
+  if (a.q_len > INT32_MAX - 512 || a.kv_len > INT32_MAX - 512) return "sequence too long";
+  if (a.batch * a.heads > (1ll << 24) || (a.batch * a.heads) * ((a.kv_len + BN - 1) / BN) > (1ll << 30))
+    return "too many (batch, head, key tile) work items";
+  return nullptr;
+}
+}  // namespace
+
+extern "C" B200_API size_t b200_sdpa_bwd_workspace_bytes(const b200_sdpa_bwd_args* a) {
+  if (a == nullptr || a->batch <= 0 || a->heads <= 0 || a->q_len <= 0 || a->kv_len <= 0) return 0;
+  const size_t bh = (size_t)a->batch * (size_t)a->heads;
+  const size_t kv_tiles = (size_t)((a->kv_len + BN - 1) / BN);
+  return align256(bh * (size_t)a->q_len * sizeof(float)) + bh * kv_tiles * (size_t)a->q_len * D * sizeof(float);
+}
+
+extern "C" B200_API int32_t b200_sdpa_bwd(const b200_sdpa_bwd_args* args, b200_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(args != nullptr, B200_ERR_INVALID_ARG, "sdpa_bwd: null args");
+  const b200_sdpa_bwd_args& a = *args;
+  B200_REQUIRE(a.batch >= 0 && a.heads >= 0 && a.q_len >= 0 && a.kv_len >= 0, B200_ERR_INVALID_ARG,
+               "sdpa_bwd: negative size");
+  B200_REQUIRE(valid_dtype(a.dtype), B200_ERR_INVALID_ARG, "sdpa_bwd: bad dtype enum");
+  if (a.batch == 0 || a.heads == 0) return B200_OK;
+  B200_REQUIRE(a.q != nullptr && a.k != nullptr && a.v != nullptr && a.o != nullptr && a.d_out != nullptr &&
+                   a.lse != nullptr && a.dq != nullptr && a.dk != nullptr && a.dv != nullptr,
+               B200_ERR_INVALID_ARG, "sdpa_bwd: null pointer");
+  const char* why = sdpa_bwd_ineligible(a);
+  B200_REQUIRE(why == nullptr, B200_ERR_UNSUPPORTED, "sdpa_bwd: %s", why);
+  const size_t need = b200_sdpa_bwd_workspace_bytes(args);
+  B200_REQUIRE(a.workspace != nullptr && a.workspace_bytes >= need, B200_ERR_WORKSPACE,
+               "sdpa_bwd: workspace of %zu bytes needed, %zu given", need, a.workspace_bytes);
+  B200_REQUIRE(aligned_to(a.workspace, 256), B200_ERR_ALIGNMENT, "sdpa_bwd: workspace not 256-byte aligned");
+
+  const int64_t bh = a.batch * a.heads;
+  float* delta = static_cast<float*>(a.workspace);
+  float* dq_part = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) +
+                                            align256((size_t)bh * (size_t)a.q_len * sizeof(float)));
+  {
+    const int64_t rows = bh * a.q_len;
+    sdpa_delta_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(a.o), static_cast<const __nv_bfloat16*>(a.d_out), delta, rows, a.heads,
+        a.q_len, a.o_strides[0], a.o_strides[1], a.o_strides[2], a.d_out_strides[0], a.d_out_strides[1],
+        a.d_out_strides[2]);
+    B200_CHECK_LAUNCH("sdpa_bwd(delta)");
+  }
+  CUtensorMap mq, mk, mv, mdo;
+  Params p;
+  int32_t st = make_map(&mq, a.q, a.batch, a.heads, a.q_len, a.q_strides, &p.q_heads_inner);
+  if (st != B200_OK) return st;
+  st = make_map(&mk, a.k, a.batch, a.heads, a.kv_len, a.k_strides, &p.k_heads_inner);
+  if (st != B200_OK) return st;
+  st = make_map(&mv, a.v, a.batch, a.heads, a.kv_len, a.v_strides, &p.v_heads_inner);
+  if (st != B200_OK) return st;
+  st = make_map(&mdo, a.d_out, a.batch, a.heads, a.q_len, a.d_out_strides, &p.do_heads_inner);
+  if (st != B200_OK) return st;
+  p.lse = a.lse;
+  p.delta = delta;
+  p.dq_part = dq_part;
+  p.dk = static_cast<__nv_bfloat16*>(a.dk);
+  p.dv = static_cast<__nv_bfloat16*>(a.dv);
+  p.heads = (uint32_t)a.heads;
+  p.bh = (uint32_t)bh;
+  p.q_len = (int32_t)a.q_len;
+  p.kv_len = (int32_t)a.kv_len;
+  p.q_tiles = (int32_t)((a.q_len + BM - 1) / BM);
+  p.kv_tiles = (int32_t)((a.kv_len + BN - 1) / BN);
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.causal = a.causal;
+  p.num_items = (uint32_t)p.kv_tiles * p.bh;
+  p.status = device_status_ptr();
+  B200_REQUIRE(p.status != nullptr, B200_ERR_CUDA, "sdpa_bwd: device status word unavailable");
+
+  static thread_local bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(sdpa_bwd_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess)
+      B200_FAIL(B200_ERR_CUDA, "sdpa_bwd: cannot opt in to %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  const int64_t slots = sm_count();
+  const int64_t grid = (int64_t)p.num_items < slots ? (int64_t)p.num_items : slots;
+  sdpa_bwd_tcgen05_kernel<<<(unsigned)grid, kThreads, SMEM_BYTES, stream>>>(mq, mk, mv, mdo, p);
+  B200_CHECK_LAUNCH("sdpa_bwd");
+  {
+    const int64_t total = bh * a.q_len * (D / 4);
+    sdpa_dq_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+        dq_part, static_cast<__nv_bfloat16*>(a.dq), bh, p.q_len, p.kv_tiles, p.causal);
+    B200_CHECK_LAUNCH("sdpa_bwd(dq)");
+  }
+  return B200_OK;
+}

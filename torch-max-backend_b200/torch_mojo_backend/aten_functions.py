@@ -573,8 +573,15 @@ def aten_scaled_dot_product_attention(
 _SDPA_BACKWARD_SCORE_BYTES = 1 << 30
 
 
-def _sdpa_backward(grad_out, query, key, value, attn_bias, is_causal, scale, want_bias_grad=False):
+def _sdpa_backward(grad_out, query, key, value, attn_bias, is_causal, scale, want_bias_grad=False, out=None, lse=None):
     _require_kernel_dtype("scaled_dot_product_attention backward", grad_out, query, key, value)
+    if (
+        attn_bias is None and out is not None and lse is not None and ops.sdpa_backward_supported(query, key, value)
+        and out.dtype == query.dtype
+    ):
+        # the fused tensor-core kernel (bf16, head_dim 64): no T x S matrix is ever materialised
+        dq, dk, dv = ops.sdpa_backward(grad_out, query, key, value, out, lse, bool(is_causal), scale)
+        return dq, dk, dv, None
     if key.shape[1] != query.shape[1]:
         raise NotImplementedError("attention backward with grouped-query heads is not supported by the b200 kernels")
     B, H, T, D = query.shape
@@ -642,7 +649,7 @@ def aten__scaled_dot_product_flash_attention_backward(
 ):
     if dropout_p != 0.0:
         raise NotImplementedError("attention backward with dropout is not supported by the b200 kernels")
-    return _sdpa_backward(grad_out, query, key, value, None, is_causal, scale)[:3]
+    return _sdpa_backward(grad_out, query, key, value, None, is_causal, scale, out=out, lse=logsumexp)[:3]
 
 
 # _scaled_dot_product_efficient_attention_backward(Tensor grad_out_, Tensor query, Tensor key, Tensor value,
@@ -656,7 +663,7 @@ def aten__scaled_dot_product_efficient_attention_backward(
     if dropout_p != 0.0:
         raise NotImplementedError("attention backward with dropout is not supported by the b200 kernels")
     want_bias = bool(grad_input_mask[3]) and attn_bias is not None
-    return _sdpa_backward(grad_out_, query, key, value, attn_bias, is_causal, scale, want_bias)
+    return _sdpa_backward(grad_out_, query, key, value, attn_bias, is_causal, scale, want_bias, out=out, lse=logsumexp)
 
 
 # _scaled_dot_product_cudnn_attention_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value,
@@ -670,7 +677,7 @@ def aten__scaled_dot_product_cudnn_attention_backward(
 ):
     if dropout_p != 0.0:
         raise NotImplementedError("attention backward with dropout is not supported by the b200 kernels")
-    return _sdpa_backward(grad_out, query, key, value, attn_bias, is_causal, scale)[:3]
+    return _sdpa_backward(grad_out, query, key, value, attn_bias, is_causal, scale, out=out, lse=logsumexp)[:3]
 
 
 # _scaled_dot_product_flash_attention_for_cpu_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value,

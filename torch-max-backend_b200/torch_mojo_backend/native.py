@@ -76,6 +76,8 @@ EXPORTED_SYMBOLS = (
     "b200_gemm_small_m_static",
     "b200_sdpa_route",
     "b200_sdpa_fwd",
+    "b200_sdpa_bwd_workspace_bytes",
+    "b200_sdpa_bwd",
 )
 
 
@@ -145,6 +147,35 @@ class SdpaArgs(ctypes.Structure):
         ("causal", ctypes.c_int32),
         ("dtype", ctypes.c_int32),
         ("route", ctypes.c_int32),
+    ]
+
+
+class SdpaBwdArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p),
+        ("k", ctypes.c_void_p),
+        ("v", ctypes.c_void_p),
+        ("o", ctypes.c_void_p),
+        ("d_out", ctypes.c_void_p),
+        ("lse", ctypes.c_void_p),
+        ("dq", ctypes.c_void_p),
+        ("dk", ctypes.c_void_p),
+        ("dv", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+        ("batch", ctypes.c_int64),
+        ("heads", ctypes.c_int64),
+        ("q_len", ctypes.c_int64),
+        ("kv_len", ctypes.c_int64),
+        ("head_dim", ctypes.c_int64),
+        ("q_strides", ctypes.c_int64 * 3),
+        ("k_strides", ctypes.c_int64 * 3),
+        ("v_strides", ctypes.c_int64 * 3),
+        ("o_strides", ctypes.c_int64 * 3),
+        ("d_out_strides", ctypes.c_int64 * 3),
+        ("scale", ctypes.c_float),
+        ("causal", ctypes.c_int32),
+        ("dtype", ctypes.c_int32),
     ]
 
 
@@ -242,6 +273,10 @@ def _declare(dll: ctypes.CDLL) -> None:
     dll.b200_sdpa_route.argtypes = [ctypes.POINTER(SdpaArgs)]
     dll.b200_sdpa_fwd.restype = i32
     dll.b200_sdpa_fwd.argtypes = [ctypes.POINTER(SdpaArgs), vp]
+    dll.b200_sdpa_bwd_workspace_bytes.restype = ctypes.c_size_t
+    dll.b200_sdpa_bwd_workspace_bytes.argtypes = [ctypes.POINTER(SdpaBwdArgs)]
+    dll.b200_sdpa_bwd.restype = i32
+    dll.b200_sdpa_bwd.argtypes = [ctypes.POINTER(SdpaBwdArgs), vp]
 
 
 def lib() -> ctypes.CDLL:

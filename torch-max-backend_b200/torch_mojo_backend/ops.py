@@ -43,6 +43,10 @@ _lib.define(
     "sdpa(Tensor q, Tensor k, Tensor v, bool causal=False, float? scale=None, int route=0) -> (Tensor, Tensor)"
 )
 _lib.define(
+    "sdpa_backward(Tensor d_out, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, bool causal=False,"
+    " float? scale=None) -> (Tensor, Tensor, Tensor)"
+)
+_lib.define(
     "embedding_sum(Tensor table, Tensor indices, Tensor? table2=None, Tensor? indices2=None,"
     " ScalarType? out_dtype=None) -> Tensor"
 )
@@ -443,8 +447,26 @@ def _normalise_bias(bias, m, n):
     return full
 
 
+def _tma_pitch(t):
+    """A large 2-D bf16 operand whose rows (or, for a transposed view, columns) are contiguous but
+    whose pitch is not a multiple of 16 bytes (the 50257-column gradient of the logits) cannot be
+    read by TMA and would take the CUDA-core kernel, ~50x slower: copy it once into a buffer with
+    a padded pitch (one pass over the operand) and hand the GEMM the same view of that."""
+    if t.dim() != 2 or t.dtype != torch.bfloat16 or min(t.shape) < 64 or t.numel() < (1 << 22):
+        return t
+    if t.stride(1) == 1 and t.stride(0) % 8 != 0:
+        rows, cols = t.shape
+        padded = torch.empty((rows, (cols + 7) // 8 * 8), dtype=t.dtype, device=t.device)[:, :cols]
+        padded.copy_(t)
+        return padded
+    if t.stride(0) == 1 and t.stride(1) % 8 != 0:
+        return _tma_pitch(t.t()).t()
+    return t
+
+
 def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, out_dtype=None, route=0):
     device = native.require_cuda("gemm", a, b, bias, residual)
+    a, b = _tma_pitch(a), _tma_pitch(b)
     if a.dtype != b.dtype:
         raise RuntimeError(f"gemm: operand dtypes differ ({a.dtype} and {b.dtype})")
     out_shape = _gemm_out_shape(a, b)
@@ -472,7 +494,12 @@ def _gemm_cuda(a, b, bias=None, residual=None, alpha=1.0, beta=1.0, epilogue=0, 
     with torch.cuda.device(device):
         status = native.lib().b200_gemm(ctypes.byref(g), _ptr(workspace), workspace_bytes, native.current_stream(device))
     native.check("gemm", status)
-    _launched(device, start, "gemm", 2.0 * g.m * g.n * g.k * g.batch, _nbytes(a, b, c, bias, residual))
+    name = "gemm"
+    if start is not None and getattr(native.profiler, "by_shape", False):
+        # per-shape breakdown for bench_training.py --by-shape: operand layouts tell the three GEMMs of a layer apart
+        layout = ("T" if a.stride(-1) != 1 else "N") + ("T" if b.stride(-1) != 1 else "N")
+        name = f"gemm {g.m}x{g.k}x{g.n} {layout} {str(a.dtype).split('.')[-1]}->{str(c.dtype).split('.')[-1]}"
+    _launched(device, start, name, 2.0 * g.m * g.n * g.k * g.batch, _nbytes(a, b, c, bias, residual))
     return c
 
 
@@ -539,6 +566,55 @@ def _sdpa_meta(q, k, v, causal=False, scale=None, route=0):
     B, H, T, D = q.shape
     o = torch.empty((B, T, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
     return o, torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+
+
+def sdpa_backward_supported(q, k, v) -> bool:
+    """What b200_sdpa_bwd takes: bf16, head_dim 64, equal head counts."""
+    return (
+        q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+        and q.dim() == 4 and q.shape[-1] == 64 and v.shape[-1] == 64 and k.shape[1] == q.shape[1]
+        and q.shape[2] > 0 and k.shape[2] > 0
+    )
+
+
+def _sdpa_backward_cuda(d_out, q, k, v, o, lse, causal=False, scale=None):
+    device = native.require_cuda("sdpa_backward", d_out, q, k, v, o, lse)
+    if not sdpa_backward_supported(q, k, v):
+        raise RuntimeError("sdpa_backward: the kernel takes bf16 tensors with head_dim 64 and equal head counts")
+    B, H, T, D = q.shape
+    S = k.shape[2]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    q, k, v, o = _unit_last_stride(q), _unit_last_stride(k), _unit_last_stride(v), _unit_last_stride(o)
+    d_out = _unit_last_stride(d_out.to(q.dtype))
+    lse_c = lse.reshape(B, H, -1)[:, :, :T].float().contiguous()
+    dq = torch.empty((B, H, T, D), dtype=q.dtype, device=device)
+    dk = torch.empty((B, H, S, D), dtype=q.dtype, device=device)
+    dv = torch.empty((B, H, S, D), dtype=q.dtype, device=device)
+    a = native.SdpaBwdArgs()
+    a.q, a.k, a.v, a.o, a.d_out, a.lse = (t.data_ptr() for t in (q, k, v, o, d_out, lse_c))
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.batch, a.heads, a.q_len, a.kv_len, a.head_dim = B, H, T, S, D
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o), ("d_out_strides", d_out)):
+        arr = getattr(a, name)
+        arr[0], arr[1], arr[2] = t.stride(0), t.stride(1), t.stride(2)
+    a.scale, a.causal, a.dtype = float(scale), int(bool(causal)), native.dtype_enum(q.dtype)
+    lib = native.lib()
+    ws_bytes = lib.b200_sdpa_bwd_workspace_bytes(ctypes.byref(a))
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws_bytes
+    start = _prof_begin(device)
+    with torch.cuda.device(device):
+        status = lib.b200_sdpa_bwd(ctypes.byref(a), native.current_stream(device))
+    native.check("sdpa_backward", status)
+    flops = 10.0 * B * H * T * S * D * (0.5 if causal else 1.0)
+    _launched(device, start, "sdpa_backward", flops, _nbytes(q, k, v, o, d_out, dq, dk, dv))
+    return dq, dk, dv
+
+
+def _sdpa_backward_meta(d_out, q, k, v, o, lse, causal=False, scale=None):
+    return torch.empty_like(q, memory_format=torch.contiguous_format), torch.empty(
+        k.shape, dtype=k.dtype, device=k.device), torch.empty(v.shape, dtype=v.dtype, device=v.device)
 
 
 # ---- embedding (+ second table) ---------------------------------------------------------------
@@ -704,6 +780,7 @@ for _name, _cuda, _meta in (
     ("sum_rows", _sum_rows_cuda, _sum_rows_meta),
     ("gemm", _gemm_cuda, _gemm_meta),
     ("sdpa", _sdpa_cuda, _sdpa_meta),
+    ("sdpa_backward", _sdpa_backward_cuda, _sdpa_backward_meta),
     ("embedding_sum", _embedding_sum_cuda, _embedding_sum_meta),
     ("argmax", _argmax_cuda, _argmax_meta),
     ("cat", _cat_cuda, _cat_meta),
@@ -724,6 +801,7 @@ layer_norm_backward = torch.ops.b200.layer_norm_backward
 sum_rows = torch.ops.b200.sum_rows
 gemm = torch.ops.b200.gemm
 sdpa = torch.ops.b200.sdpa
+sdpa_backward = torch.ops.b200.sdpa_backward
 embedding_sum = torch.ops.b200.embedding_sum
 argmax = torch.ops.b200.argmax
 cat = torch.ops.b200.cat
