@@ -12,11 +12,19 @@
 // TMA tiles exactly as in the forward kernel, used K-major for S and dP and MN-major (as B) for the
 // three products that contract over rows.
 // dQ_j gets a contribution from every key tile; tile i writes its own to a partial buffer
-// [batch*heads, key tile, row, 64] (fp32) and a second kernel adds the tiles up in tile order, so
-// the gradient does not depend on which CTA ran first (no atomics).
+// [batch*heads, key tile, query tile, 64 columns, 128 rows] (fp32, rows innermost so that a warp's
+// stores are contiguous) and a second kernel adds the tiles up in tile order, so the gradient does
+// not depend on which CTA ran first (no atomics).
+// Steps overlap: P / dS have two shared-memory buffers, the score MMAs of step n + 1 are issued
+// BEFORE the three products of step n, and the row threads read dQ of step n after their
+// arithmetic for step n + 1 -- so the tensor core works on step n while the row threads are already
+// on step n + 1, and neither waits for the other inside an item.
 //   warp 0      TMA producer: K_i, V_i per item; Q_j, dO_j into a two-deep ring.
 //   warp 1      MMA issuer (converged warp, one elected lane).
-//   warps 2-5   one thread per query row: P and dS, the dQ partial, and at the end of the item dK, dV.
+//   warps 2-9   two threads per query row (warps w and w + 4 address the same 32 TMEM lanes): each
+//               takes 64 of the tile's 128 keys for P and dS -- with the LSE given, no value
+//               crosses between them --, 32 of the 64 columns of the dQ partial, and at the end
+//               of the item one of dK, dV.
 // Tensor memory: S 128 columns, dP 128, dV 64, dK 64, dQ 64. Items are ordered by key tile, so
 // the tiles with the most query tiles (the first ones under a causal mask) start first.
 // Every wait is bounded (ptx::mbar_wait); a CTA that gives up raises its abort flag, sets the
@@ -31,7 +39,8 @@ namespace {
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr int D = 64;
-constexpr int kThreads = 6 * 32;
+constexpr int kRowWarps = 8;
+constexpr int kThreads = (2 + kRowWarps) * 32;
 constexpr int TILE_BYTES = 128 * D * 2;  // 16 KiB: a [128][64] bf16 tile; also one 64-key half of P / dS
 constexpr int kTmemCols = 512;
 constexpr int TMEM_S = 0, TMEM_DP = 128, TMEM_DV = 256, TMEM_DK = 320, TMEM_DQ = 384;
@@ -40,10 +49,10 @@ constexpr int SMEM_K = 0;
 constexpr int SMEM_V = SMEM_K + TILE_BYTES;
 constexpr int SMEM_Q = SMEM_V + TILE_BYTES;         // two stages
 constexpr int SMEM_DO = SMEM_Q + 2 * TILE_BYTES;    // two stages
-constexpr int SMEM_P = SMEM_DO + 2 * TILE_BYTES;    // [2 key halves][128 rows][64 keys]
-constexpr int SMEM_DS = SMEM_P + 2 * TILE_BYTES;
-constexpr int SMEM_BAR = SMEM_DS + 2 * TILE_BYTES;
-constexpr int kNumBars = 14;
+constexpr int SMEM_P = SMEM_DO + 2 * TILE_BYTES;    // [2 buffers][2 key halves][128 rows][64 keys]
+constexpr int SMEM_DS = SMEM_P + 4 * TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_DS + 4 * TILE_BYTES;
+constexpr int kNumBars = 16;
 constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
 constexpr int SMEM_BYTES = SMEM_MISC + 16 + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM exceeded");
@@ -51,7 +60,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM exceeded");
 struct Params {
   const float* lse;    // [bh, q_len] natural log
   const float* delta;  // [bh, q_len]
-  float* dq_part;      // [bh, kv_tiles, q_len, 64]
+  float* dq_part;      // [bh, kv_tiles, q_tiles, 64, 128]
   __nv_bfloat16* dk;   // [bh, kv_len, 64]
   __nv_bfloat16* dv;
   uint32_t heads, bh;
@@ -62,6 +71,18 @@ struct Params {
   int q_heads_inner, k_heads_inner, v_heads_inner, do_heads_inner;
   unsigned int* status;
 };
+
+#ifdef B200_SDPA_PROBE
+// Development build only: per-CTA cycle counters of the row threads, read back by b200_debug_sdpa_bwd_probe.
+__device__ unsigned long long g_bwd_probe[160][16];
+#define PROBE_DECL(n) long long n = 0
+#define PROBE_T0(t) const long long t = clock64()
+#define PROBE_ADD(n, t) n += clock64() - t
+#else
+#define PROBE_DECL(n)
+#define PROBE_T0(t)
+#define PROBE_ADD(n, t)
+#endif
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -94,13 +115,14 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   auto qd_full = [&](int s) { return bar + 8u * (2 + s); };         // per step, two stages
   auto qd_empty = [&](int s) { return bar + 8u * (4 + s); };
   const uint32_t sdp_full = bar + 8 * 6;    // S and dP are in tensor memory
-  const uint32_t sdp_free = bar + 8 * 7;    // the row threads have read them (4 warps)
-  const uint32_t pds_full = bar + 8 * 8;    // P and dS are in shared memory (4 warps)
-  const uint32_t pds_free = bar + 8 * 9;    // the three MMAs that read them have completed
+  const uint32_t sdp_free = bar + 8 * 7;    // the row threads have read them (one arrival per warp)
+  // (bar + 8 * 9 is unused)
+  auto pds_full = [&](int b) { return bar + 8u * (8 + b); };    // P and dS are in shared-memory buffer b (one arrival per warp)
+  auto pds_free = [&](int b) { return bar + 8u * (14 + b); };   // the three MMAs that read buffer b have completed
   const uint32_t dq_full = bar + 8 * 10;    // dQ_j(i) is in tensor memory
-  const uint32_t dq_free = bar + 8 * 11;    // the row threads have read it (4 warps)
+  const uint32_t dq_free = bar + 8 * 11;    // the row threads have read it
   const uint32_t acc_full = bar + 8 * 12;   // dK_i, dV_i complete (per item)
-  const uint32_t acc_free = bar + 8 * 13;   // the row threads have read them (4 warps)
+  const uint32_t acc_free = bar + 8 * 13;   // the row threads have read them
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + SMEM_MISC);
   volatile uint32_t* tmem_holder = misc;
   volatile uint32_t* abort_flag = misc + 1;
@@ -114,13 +136,15 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       ptx::mbar_init(qd_empty(s), 1);
     }
     ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(sdp_free, 4);
-    ptx::mbar_init(pds_full, 4);
-    ptx::mbar_init(pds_free, 1);
+    ptx::mbar_init(sdp_free, kRowWarps);
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(pds_full(b), kRowWarps);
+      ptx::mbar_init(pds_free(b), 1);
+    }
     ptx::mbar_init(dq_full, 1);
-    ptx::mbar_init(dq_free, 4);
+    ptx::mbar_init(dq_free, kRowWarps);
     ptx::mbar_init(acc_full, 1);
-    ptx::mbar_init(acc_free, 4);
+    ptx::mbar_init(acc_free, kRowWarps);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_q);
@@ -190,6 +214,47 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       if (accs > 0) go = go && ptx::mbar_wait(acc_free, (accs - 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, go)) break;
       ++accs;
+      // dV += P^T dO, dK += dS^T Q, dQ = dS K of step n (the j-th query tile), from P / dS buffer n & 1
+      auto issue_products = [&](uint32_t n, int j, bool last) -> bool {
+        const int sb = n & 1;
+        bool ready = ptx::mbar_wait(pds_full(sb), (n >> 1) & 1, abort_flag);
+        if (n > 0) ready = ready && ptx::mbar_wait(dq_free, (n - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ready)) return false;
+        ptx::tc_fence_after_sync();
+        const uint32_t qs = q_smem + sb * TILE_BYTES, dos = do_smem + sb * TILE_BYTES;
+        const uint32_t pb = p_smem + sb * 2 * TILE_BYTES, dsb = ds_smem + sb * 2 * TILE_BYTES;
+        if (ptx::elect_one()) {
+          const uint32_t acc = j > j0 ? 1u : 0u;
+          // contraction over the 128 query rows: eight steps of 16 rows; A = P^T / dS^T through the
+          // MN-major descriptor (two 64-key halves 16 KiB apart, 8-row groups 1 KiB apart)
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_DV, ptx::smem_desc_sw128(pb + kk * 2048, TILE_BYTES, 1024),
+                            ptx::smem_desc_sw128(dos + kk * 2048, 0, 1024), idesc_t, (acc | (kk > 0)) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < BM / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_DK, ptx::smem_desc_sw128(dsb + kk * 2048, TILE_BYTES, 1024),
+                            ptx::smem_desc_sw128(qs + kk * 2048, 0, 1024), idesc_t, (acc | (kk > 0)) ? 1u : 0u);
+          }
+          // contraction over the 128 keys: A = dS K-major (16 keys = 32 bytes inside a 64-key half)
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            ptx::mma_f16_ss(tmem + TMEM_DQ,
+                            ptx::smem_desc_sw128(dsb + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024),
+                            ptx::smem_desc_sw128(k_smem + kk * 2048, 0, 1024), idesc_q, kk > 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(dq_full);
+          ptx::tc_commit(pds_free(sb));
+          ptx::tc_commit(qd_empty(sb));
+          if (last) {
+            ptx::tc_commit(acc_full);
+            ptx::tc_commit(kv_empty);
+          }
+        }
+        __syncwarp();
+        return true;
+      };
       for (int j = j0; j < p.q_tiles; ++j, ++steps) {
         const int s = steps & 1;
         go = ptx::mbar_wait(qd_full(s), (steps >> 1) & 1, abort_flag);
@@ -211,49 +276,23 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           ptx::tc_commit(sdp_full);
         }
         __syncwarp();
-        go = ptx::mbar_wait(pds_full, steps & 1, abort_flag);
-        if (steps > 0) go = go && ptx::mbar_wait(dq_free, (steps - 1) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        if (ptx::elect_one()) {
-          const uint32_t acc = j > j0 ? 1u : 0u;
-          // contraction over the 128 query rows: eight steps of 16 rows; A = P^T / dS^T through the
-          // MN-major descriptor (two 64-key halves 16 KiB apart, 8-row groups 1 KiB apart)
-#pragma unroll
-          for (int kk = 0; kk < BM / 16; ++kk) {
-            ptx::mma_f16_ss(tmem + TMEM_DV, ptx::smem_desc_sw128(p_smem + kk * 2048, TILE_BYTES, 1024),
-                            ptx::smem_desc_sw128(dos + kk * 2048, 0, 1024), idesc_t, (acc | (kk > 0)) ? 1u : 0u);
-          }
-#pragma unroll
-          for (int kk = 0; kk < BM / 16; ++kk) {
-            ptx::mma_f16_ss(tmem + TMEM_DK, ptx::smem_desc_sw128(ds_smem + kk * 2048, TILE_BYTES, 1024),
-                            ptx::smem_desc_sw128(qs + kk * 2048, 0, 1024), idesc_t, (acc | (kk > 0)) ? 1u : 0u);
-          }
-          // contraction over the 128 keys: A = dS K-major (16 keys = 32 bytes inside a 64-key half)
-#pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk) {
-            ptx::mma_f16_ss(tmem + TMEM_DQ,
-                            ptx::smem_desc_sw128(ds_smem + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024),
-                            ptx::smem_desc_sw128(k_smem + kk * 2048, 0, 1024), idesc_q, kk > 0 ? 1u : 0u);
-          }
-          ptx::tc_commit(dq_full);
-          ptx::tc_commit(pds_free);
-          ptx::tc_commit(qd_empty(s));
-          if (j + 1 == p.q_tiles) {
-            ptx::tc_commit(acc_full);
-            ptx::tc_commit(kv_empty);
-          }
-        }
-        __syncwarp();
+        // the products of the PREVIOUS step go behind this step's score MMAs: the row threads work
+        // on this step while the tensor core is busy with them
+        if (j > j0 && !issue_products(steps - 1, j - 1, false)) { ok = false; break; }
       }
+      if (!ok) break;
+      if (!issue_products(steps - 1, p.q_tiles - 1, true)) break;  // the item's last step
     }
   } else {
-    // ---------------- row threads: warps 2-5 ----------------
+    // ---------------- row threads: warps 2-9 ----------------
+    const int half = (warp - 2) >> 2;  // which 64 keys of P / dS, which 32 columns of dQ, which of dK / dV
     const int quad = warp & 3;       // TMEM lane quadrant this warp may access
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     uint32_t items = 0, steps = 0, accs = 0;
     bool ok = true;
+    PROBE_DECL(c_wait_sdp); PROBE_DECL(c_math); PROBE_DECL(c_wait_dq); PROBE_DECL(c_dq); PROBE_DECL(c_wait_acc); PROBE_DECL(c_acc);
+    PROBE_T0(t_start);
     for (uint32_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
       const int i = item_tile(w);
       const uint32_t bh = item_bh(w);
@@ -265,52 +304,78 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       if (j0 >= p.q_tiles) {
         if (key < p.kv_len) {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            reinterpret_cast<uint4*>(dk_row)[c] = make_uint4(0, 0, 0, 0);
-            reinterpret_cast<uint4*>(dv_row)[c] = make_uint4(0, 0, 0, 0);
-          }
+          for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(half ? dv_row : dk_row)[c] = make_uint4(0, 0, 0, 0);
         }
         continue;
       }
+      // this key tile's share of dQ of step n (query tile j): 32 of the 64 columns per thread
+      auto dq_epilogue = [&](uint32_t n, int j) -> bool {
+        PROBE_T0(t2);
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(dq_full, n & 1, abort_flag))) return false;
+        ptx::tc_fence_after_sync();
+        PROBE_ADD(c_wait_dq, t2);
+        PROBE_T0(t3);
+        float* part = p.dq_part + ((((int64_t)bh * p.kv_tiles + i) * p.q_tiles + j) * D + half * 32) * BM + r;
+        uint32_t o[32];
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_DQ + half * 32 + lane_addr, o);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) part[c * BM] = __uint_as_float(o[c]);  // consecutive lanes, consecutive rows
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(dq_free);
+        PROBE_ADD(c_dq, t3);
+        return true;
+      };
       for (int j = j0; j < p.q_tiles; ++j, ++steps) {
         const int32_t row = j * BM + r;
         const bool live = row < p.q_len;
         const float lse2 = live ? p.lse[(int64_t)bh * p.q_len + row] * 1.4426950408889634f : 0.0f;
         const float delta = live ? p.delta[(int64_t)bh * p.q_len + row] : 0.0f;
+        const int sb = steps & 1;  // P / dS buffer of this step
+        PROBE_T0(t0);
         bool go = ptx::mbar_wait(sdp_full, steps & 1, abort_flag);
-        if (steps > 0) go = go && ptx::mbar_wait(pds_free, (steps - 1) & 1, abort_flag);
+        if (steps > 1) go = go && ptx::mbar_wait(pds_free(sb), ((steps >> 1) - 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
         ptx::tc_fence_after_sync();
+        PROBE_ADD(c_wait_sdp, t0);
+        PROBE_T0(t1);
         // keys [kv0, kv0 + visible) of the tile are visible to this row
         int32_t visible = p.kv_len - kv0;
         if (p.causal && row - kv0 + 1 < visible) visible = row - kv0 + 1;
         if (!live) visible = 0;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t sv[32], dpv[32];
-          ptx::tmem_ld_32x32b_x32(tmem + TMEM_S + c * 32 + lane_addr, sv);
-          ptx::tmem_ld_32x32b_x32(tmem + TMEM_DP + c * 32 + lane_addr, dpv);
-          ptx::tmem_ld_wait();
-          uint32_t pp[16], dd[16];
+        // warp-uniform: does any row of this warp have a masked key among its 64? (diagonal and edge tiles only)
+        const bool need_mask = __any_sync(0xffffffffu, visible < (half + 1) * 64);
+        // this thread's 64 scores and 64 dP values: four loads in flight, one wait
+        uint32_t sv[64], dpv[64];
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_S + half * 64 + lane_addr, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_S + half * 64 + 32 + lane_addr, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_DP + half * 64 + lane_addr, reinterpret_cast<uint32_t(&)[32]>(dpv[0]));
+        ptx::tmem_ld_32x32b_x32(tmem + TMEM_DP + half * 64 + 32 + lane_addr, reinterpret_cast<uint32_t(&)[32]>(dpv[32]));
+        ptx::tmem_ld_wait();
+        // packed two-wide arithmetic: P = exp2(S scale log2e - LSE log2e), dS = P (dP scale - delta scale)
+        const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), nlse2 = make_float2(-lse2, -lse2);
+        const float2 sc2 = make_float2(p.scale, p.scale), nds2 = make_float2(-delta * p.scale, -delta * p.scale);
+        const uint32_t half_p = p_smem + (sb * 2 + half) * TILE_BYTES, half_d = ds_smem + (sb * 2 + half) * TILE_BYTES;
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float p0 = ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
-            float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -lse2));
-            if (c * 32 + e >= visible) p0 = 0.0f;
-            if (c * 32 + e + 1 >= visible) p1 = 0.0f;
-            const float d0 = p.scale * p0 * (__uint_as_float(dpv[e]) - delta);
-            const float d1 = p.scale * p1 * (__uint_as_float(dpv[e + 1]) - delta);
-            pp[e >> 1] = pack_bf16x2(p0, p1);
-            dd[e >> 1] = pack_bf16x2(d0, d1);
-          }
-          // 32 keys = four 16-byte units of this row in the 64-key half (c >> 1)
-          const uint32_t half_p = p_smem + (c >> 1) * TILE_BYTES, half_d = ds_smem + (c >> 1) * TILE_BYTES;
+        for (int u = 0; u < 8; ++u) {  // eight 16-byte units of eight keys
+          uint32_t pp[4], dd[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int unit = (c & 1) * 4 + u;
-            st_shared_v4(swz(half_p, r, unit), pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-            st_shared_v4(swz(half_d, r, unit), dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+          for (int e = 0; e < 4; ++e) {
+            const int c = 8 * u + 2 * e;
+            const float2 arg = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sl2, nlse2);
+            float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
+            if (need_mask) {
+              if (half * 64 + c >= visible) pr.x = 0.0f;
+              if (half * 64 + c + 1 >= visible) pr.y = 0.0f;
+            }
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(dpv[c]), __uint_as_float(dpv[c + 1])), sc2, nds2);
+            const float2 ds = __fmul2_rn(pr, t);
+            pp[e] = pack_bf16x2(pr.x, pr.y);
+            dd[e] = pack_bf16x2(ds.x, ds.y);
           }
+          st_shared_v4(swz(half_p, r, u), pp[0], pp[1], pp[2], pp[3]);
+          st_shared_v4(swz(half_d, r, u), dd[0], dd[1], dd[2], dd[3]);
         }
         // S / dP have been read; P / dS are written: make them visible to the tensor core's proxy
         ptx::tc_fence_before_sync();
@@ -318,39 +383,28 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         __syncwarp();
         if (lane == 0) {
           ptx::mbar_arrive(sdp_free);
-          ptx::mbar_arrive(pds_full);
+          ptx::mbar_arrive(pds_full(sb));
         }
-        // this key tile's share of dQ_j
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(dq_full, steps & 1, abort_flag))) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        float* part = p.dq_part + (((int64_t)bh * p.kv_tiles + i) * p.q_len + row) * D;
-#pragma unroll
-        for (int hcol = 0; hcol < 2; ++hcol) {
-          uint32_t o[32];
-          ptx::tmem_ld_32x32b_x32(tmem + TMEM_DQ + hcol * 32 + lane_addr, o);
-          ptx::tmem_ld_wait();
-          if (live) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              reinterpret_cast<uint4*>(part)[hcol * 8 + c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
-          }
-        }
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(dq_free);
+        PROBE_ADD(c_math, t1);
+        // dQ of the previous step, whose products ran on the tensor core during the arithmetic above
+        if (j > j0 && !dq_epilogue(steps - 1, j - 1)) { ok = false; break; }
       }
       if (!ok) break;
+      if (!dq_epilogue(steps - 1, p.q_tiles - 1)) { ok = false; break; }
+      if (!ok) break;
+      PROBE_T0(t4);
       // ---- end of the item: dK_i and dV_i, one key per thread
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(acc_full, accs & 1, abort_flag))) { ok = false; break; }
       ++accs;
       ptx::tc_fence_after_sync();
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* out = which ? dv_row : dk_row;
+      PROBE_ADD(c_wait_acc, t4);
+      PROBE_T0(t5);
+      {
+        __nv_bfloat16* out = half ? dv_row : dk_row;
 #pragma unroll
         for (int hcol = 0; hcol < 2; ++hcol) {
           uint32_t o[32];
-          ptx::tmem_ld_32x32b_x32(tmem + (which ? TMEM_DV : TMEM_DK) + hcol * 32 + lane_addr, o);
+          ptx::tmem_ld_32x32b_x32(tmem + (half ? TMEM_DV : TMEM_DK) + hcol * 32 + lane_addr, o);
           ptx::tmem_ld_wait();
           if (key < p.kv_len) {
 #pragma unroll
@@ -368,7 +422,15 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(acc_free);
+      PROBE_ADD(c_acc, t5);
     }
+#ifdef B200_SDPA_PROBE
+    if (threadIdx.x == 64) {
+      unsigned long long* o = g_bwd_probe[blockIdx.x];
+      o[0] = clock64() - t_start; o[1] = steps; o[2] = items; o[3] = c_wait_sdp; o[4] = c_math; o[5] = c_wait_dq;
+      o[6] = c_dq; o[7] = c_wait_acc; o[8] = c_acc;
+    }
+#endif
   }
 
   // ---------------- teardown ----------------
@@ -408,27 +470,31 @@ __global__ void sdpa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   delta[idx] = acc;
 }
 
-// dq[bh, row, :] = sum over the key tiles that row attends to, in tile order; one thread per 4 columns.
+// dq[bh, row, :] = sum over the key tiles that row attends to, in tile order. The partial tiles are
+// [64 columns][128 rows]: consecutive threads take consecutive rows (contiguous reads), four columns each.
 __global__ void sdpa_dq_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dq, int64_t bh_count,
-                                      int32_t q_len, int32_t kv_tiles, int causal) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // over bh * q_len * 16
-  const int64_t total = bh_count * q_len * (D / 4);
+                                      int32_t q_len, int32_t q_tiles, int32_t kv_tiles, int causal) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // over bh * q_tiles * 16 * 128
+  const int64_t total = bh_count * q_tiles * (D / 4) * BM;
   if (idx >= total) return;
-  const int c4 = (int)(idx % (D / 4));
-  const int64_t rowi = idx / (D / 4);
-  const int32_t row = (int32_t)(rowi % q_len);
-  const int64_t bh = rowi / q_len;
+  const int r = (int)(idx % BM);
+  const int c4 = (int)((idx / BM) % (D / 4));
+  const int j = (int)((idx / (BM * (D / 4))) % q_tiles);
+  const int64_t bh = idx / ((int64_t)BM * (D / 4) * q_tiles);
+  const int32_t row = j * BM + r;
+  if (row >= q_len) return;
   int last = kv_tiles - 1;
-  if (causal && row / BM < last) last = row / BM;
-  float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (causal && j < last) last = j;
+  float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   for (int i = 0; i <= last; ++i) {
-    const float4 t = __ldcs(reinterpret_cast<const float4*>(part + ((bh * kv_tiles + i) * q_len + row) * D) + c4);
-    s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    const float* t = part + ((((int64_t)bh * kv_tiles + i) * q_tiles + j) * D + 4 * c4) * BM + r;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s[c] += __ldcs(t + c * BM);
   }
   uint2 o;
-  o.x = pack_bf16x2(s.x, s.y);
-  o.y = pack_bf16x2(s.z, s.w);
-  reinterpret_cast<uint2*>(dq + rowi * D)[c4] = o;
+  o.x = pack_bf16x2(s[0], s[1]);
+  o.y = pack_bf16x2(s[2], s[3]);
+  reinterpret_cast<uint2*>(dq + (bh * q_len + row) * D)[c4] = o;
 }
 
 // Byte strides of the (position, head, batch) dims with legal stand-ins for size-1 dims.
@@ -498,8 +564,8 @@ const char* sdpa_bwd_ineligible(const b200_sdpa_bwd_args& a) {
 extern "C" B200_API size_t b200_sdpa_bwd_workspace_bytes(const b200_sdpa_bwd_args* a) {
   if (a == nullptr || a->batch <= 0 || a->heads <= 0 || a->q_len <= 0 || a->kv_len <= 0) return 0;
   const size_t bh = (size_t)a->batch * (size_t)a->heads;
-  const size_t kv_tiles = (size_t)((a->kv_len + BN - 1) / BN);
-  return align256(bh * (size_t)a->q_len * sizeof(float)) + bh * kv_tiles * (size_t)a->q_len * D * sizeof(float);
+  const size_t kv_tiles = (size_t)((a->kv_len + BN - 1) / BN), q_tiles = (size_t)((a->q_len + BM - 1) / BM);
+  return align256(bh * (size_t)a->q_len * sizeof(float)) + bh * kv_tiles * q_tiles * BM * D * sizeof(float);
 }
 
 extern "C" B200_API int32_t b200_sdpa_bwd(const b200_sdpa_bwd_args* args, b200_stream_t stream_) {
@@ -574,10 +640,16 @@ extern "C" B200_API int32_t b200_sdpa_bwd(const b200_sdpa_bwd_args* args, b200_s
   sdpa_bwd_tcgen05_kernel<<<(unsigned)grid, kThreads, SMEM_BYTES, stream>>>(mq, mk, mv, mdo, p);
   B200_CHECK_LAUNCH("sdpa_bwd");
   {
-    const int64_t total = bh * a.q_len * (D / 4);
+    const int64_t total = bh * p.q_tiles * (D / 4) * BM;
     sdpa_dq_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        dq_part, static_cast<__nv_bfloat16*>(a.dq), bh, p.q_len, p.kv_tiles, p.causal);
+        dq_part, static_cast<__nv_bfloat16*>(a.dq), bh, p.q_len, p.q_tiles, p.kv_tiles, p.causal);
     B200_CHECK_LAUNCH("sdpa_bwd(dq)");
   }
   return B200_OK;
 }
+
+#ifdef B200_SDPA_PROBE
+extern "C" B200_API int32_t b200_debug_sdpa_bwd_probe(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_bwd_probe, sizeof(g_bwd_probe)) == cudaSuccess ? 0 : -5;
+}
+#endif
