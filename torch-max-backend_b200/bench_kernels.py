@@ -311,6 +311,20 @@ def main():
                 make = lambda i, rows=rows, cols=cols: (randn((rows, cols), bf),)
                 us, rot = time_case(make, lambda t: ops.sum_rows(t[0], f32), nbytes, args.iters, use_graph)
                 report(name, us, rot, nbytes=nbytes)
+        for B, H, T in ((8, 25, 1024), (64, 25, 1024)):
+            name = f"sdpa_backward bf16 causal {B}x{H}x{T}x64"
+            if keep(name):
+                flops = 10.0 * B * H * T * T * 64 * 0.5
+                nbytes = 8 * B * H * T * 64 * 2  # q, k, v, o, dO read; dq, dk, dv written
+
+                def make(i, B=B, H=H, T=T):
+                    qkv = randn((B, T, 3 * H * 64), bf)
+                    q, k, v = (t.view(B, T, H, 64).transpose(1, 2) for t in qkv.split(H * 64, dim=2))
+                    o, lse = ops.sdpa(q, k, v, True)
+                    return randn((B, T, H, 64), bf).transpose(1, 2), q, k, v, o, lse
+
+                us, rot = time_case(make, lambda t: ops.sdpa_backward(t[0], t[1], t[2], t[3], t[4], t[5], True), nbytes, args.iters, use_graph)
+                report(name, us, rot, flops, nbytes, "tensor")
         # weight gradients dW = X^T dY (A stored transposed, K = tokens) and data gradients dX = dY W
         m_tok, d = 8192, 1600
         for label, kin, nout in (("fc", d, 4 * d), ("out", 4 * d, d)):
