@@ -216,6 +216,18 @@ def test_fused_attention_backward(ops, causal, B, H, T, S):
     assert all(torch.equal(a, b) for a, b in zip(again, (dq, dk, dv))), "fixed-order sums: bit-identical reruns"
 
 
+def test_fused_attention_backward_in_batch_chunks(ops, monkeypatch):
+    """A workspace budget that holds one batch entry at a time: the chunked calls give the same gradients."""
+    q, k, v, d_out = (gen((3, 2, 256, 64), torch.bfloat16, 80 + i, std=0.8).cuda() for i in range(4))
+    o, lse = ops.sdpa(q, k, v, True)
+    whole = ops.sdpa_backward(d_out, q, k, v, o, lse, True)
+    import torch_mojo_backend.ops as ops_module
+
+    monkeypatch.setattr(ops_module, "_SDPA_BWD_WORKSPACE_BYTES", 1)
+    chunked = ops.sdpa_backward(d_out, q, k, v, o, lse, True)
+    assert all(torch.equal(a, b) for a, b in zip(whole, chunked))
+
+
 def test_fused_attention_backward_on_fused_qkv_views(ops):
     """q, k, v as strided views of one [B, T, 3 H 64] projection (no copies), d_out in the forward's layout."""
     B, H, T = 2, 4, 512

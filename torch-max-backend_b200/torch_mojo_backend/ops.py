@@ -568,6 +568,9 @@ def _sdpa_meta(q, k, v, causal=False, scale=None, route=0):
     return o, torch.empty((B, H, T), dtype=torch.float32, device=q.device)
 
 
+_SDPA_BWD_WORKSPACE_BYTES = 2 << 30
+
+
 def sdpa_backward_supported(q, k, v) -> bool:
     """What b200_sdpa_bwd takes: bf16, head_dim 64, equal head counts."""
     return (
@@ -591,22 +594,30 @@ def _sdpa_backward_cuda(d_out, q, k, v, o, lse, causal=False, scale=None):
     dq = torch.empty((B, H, T, D), dtype=q.dtype, device=device)
     dk = torch.empty((B, H, S, D), dtype=q.dtype, device=device)
     dv = torch.empty((B, H, S, D), dtype=q.dtype, device=device)
-    a = native.SdpaBwdArgs()
-    a.q, a.k, a.v, a.o, a.d_out, a.lse = (t.data_ptr() for t in (q, k, v, o, d_out, lse_c))
-    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-    a.batch, a.heads, a.q_len, a.kv_len, a.head_dim = B, H, T, S, D
-    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o), ("d_out_strides", d_out)):
-        arr = getattr(a, name)
-        arr[0], arr[1], arr[2] = t.stride(0), t.stride(1), t.stride(2)
-    a.scale, a.causal, a.dtype = float(scale), int(bool(causal)), native.dtype_enum(q.dtype)
     lib = native.lib()
-    ws_bytes = lib.b200_sdpa_bwd_workspace_bytes(ctypes.byref(a))
-    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=device)
-    a.workspace, a.workspace_bytes = ws.data_ptr(), ws_bytes
+
+    def args_for(b0, b1):
+        a = native.SdpaBwdArgs()
+        a.q, a.k, a.v, a.o, a.d_out, a.lse = (t[b0:b1].data_ptr() for t in (q, k, v, o, d_out, lse_c))
+        a.dq, a.dk, a.dv = dq[b0:b1].data_ptr(), dk[b0:b1].data_ptr(), dv[b0:b1].data_ptr()
+        a.batch, a.heads, a.q_len, a.kv_len, a.head_dim = b1 - b0, H, T, S, D
+        for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o), ("d_out_strides", d_out)):
+            arr = getattr(a, name)
+            arr[0], arr[1], arr[2] = t.stride(0), t.stride(1), t.stride(2)
+        a.scale, a.causal, a.dtype = float(scale), int(bool(causal)), native.dtype_enum(q.dtype)
+        return a
+
+    # The per-key-tile shares of dQ live in the workspace (kv_tiles x q_tiles x 32 KB per (batch, head)):
+    # long sequences are processed a few batch entries at a time so that it stays below ~2 GB.
+    per_batch = lib.b200_sdpa_bwd_workspace_bytes(ctypes.byref(args_for(0, 1)))
+    step = max(1, min(B, _SDPA_BWD_WORKSPACE_BYTES // max(per_batch, 1)))
+    ws = torch.empty(max(per_batch * step, 256), dtype=torch.uint8, device=device)
     start = _prof_begin(device)
     with torch.cuda.device(device):
-        status = lib.b200_sdpa_bwd(ctypes.byref(a), native.current_stream(device))
-    native.check("sdpa_backward", status)
+        for b0 in range(0, B, step):
+            a = args_for(b0, min(B, b0 + step))
+            a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            native.check("sdpa_backward", lib.b200_sdpa_bwd(ctypes.byref(a), native.current_stream(device)))
     flops = 10.0 * B * H * T * S * D * (0.5 if causal else 1.0)
     _launched(device, start, "sdpa_backward", flops, _nbytes(q, k, v, o, d_out, dq, dk, dv))
     return dq, dk, dv
