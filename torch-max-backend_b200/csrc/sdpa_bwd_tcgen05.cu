@@ -327,11 +327,19 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         PROBE_ADD(c_dq, t3);
         return true;
       };
+      // LSE and delta of this thread's row, fetched one step ahead of their use
+      auto row_stats = [&](int j) {
+        const int32_t row = j * BM + r;
+        return row < p.q_len ? make_float2(p.lse[(int64_t)bh * p.q_len + row], p.delta[(int64_t)bh * p.q_len + row])
+                             : make_float2(0.0f, 0.0f);
+      };
+      float2 stats = row_stats(j0);
       for (int j = j0; j < p.q_tiles; ++j, ++steps) {
         const int32_t row = j * BM + r;
         const bool live = row < p.q_len;
-        const float lse2 = live ? p.lse[(int64_t)bh * p.q_len + row] * 1.4426950408889634f : 0.0f;
-        const float delta = live ? p.delta[(int64_t)bh * p.q_len + row] : 0.0f;
+        const float lse2 = stats.x * 1.4426950408889634f;
+        const float delta = stats.y;
+        if (j + 1 < p.q_tiles) stats = row_stats(j + 1);
         const int sb = steps & 1;  // P / dS buffer of this step
         PROBE_T0(t0);
         bool go = ptx::mbar_wait(sdp_full, steps & 1, abort_flag);
@@ -353,6 +361,10 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         ptx::tmem_ld_32x32b_x32(tmem + TMEM_DP + half * 64 + lane_addr, reinterpret_cast<uint32_t(&)[32]>(dpv[0]));
         ptx::tmem_ld_32x32b_x32(tmem + TMEM_DP + half * 64 + 32 + lane_addr, reinterpret_cast<uint32_t(&)[32]>(dpv[32]));
         ptx::tmem_ld_wait();
+        // S and dP are in registers: the score MMAs of the next step may overwrite them right away
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(sdp_free);
         // packed two-wide arithmetic: P = exp2(S scale log2e - LSE log2e), dS = P (dP scale - delta scale)
         const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), nlse2 = make_float2(-lse2, -lse2);
         const float2 sc2 = make_float2(p.scale, p.scale), nds2 = make_float2(-delta * p.scale, -delta * p.scale);
@@ -377,14 +389,10 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           st_shared_v4(swz(half_p, r, u), pp[0], pp[1], pp[2], pp[3]);
           st_shared_v4(swz(half_d, r, u), dd[0], dd[1], dd[2], dd[3]);
         }
-        // S / dP have been read; P / dS are written: make them visible to the tensor core's proxy
-        ptx::tc_fence_before_sync();
+        // P / dS are written: make them visible to the tensor core's proxy
         ptx::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          ptx::mbar_arrive(sdp_free);
-          ptx::mbar_arrive(pds_full(sb));
-        }
+        if (lane == 0) ptx::mbar_arrive(pds_full(sb));
         PROBE_ADD(c_math, t1);
         // dQ of the previous step, whose products ran on the tensor core during the arithmetic above
         if (j > j0 && !dq_epilogue(steps - 1, j - 1)) { ok = false; break; }
