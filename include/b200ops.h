@@ -311,7 +311,9 @@ typedef struct b200_sdpa_args {
 B200_API int32_t b200_sdpa_route(const b200_sdpa_args* args);
 B200_API int32_t b200_sdpa_fwd(const b200_sdpa_args* args, b200_stream_t stream);
 
-/* Gradients of b200_sdpa_fwd: dq, dk, dv (contiguous [batch, heads, len, head_dim], dtype of q) from
+/* Gradients of b200_sdpa_fwd: dq, dk, dv ([batch, heads, len, head_dim] with the given element strides
+ * and head_dim contiguous, dtype of q; a caller that wants them as [batch, len, heads * head_dim] passes
+ * those strides and needs no transpose copy afterwards) from
  * d_out, the forward's output o and its natural-log LSE (fp32 [batch, heads, q_len], contiguous).
  * bf16 with head_dim 64 only (the tensor-core kernel); anything else is B200_ERR_UNSUPPORTED and the
  * caller composes the gradient from b200_gemm / b200_softmax_backward. Per 128-key tile one CTA keeps
@@ -338,6 +340,9 @@ typedef struct b200_sdpa_bwd_args {
   int64_t v_strides[3];
   int64_t o_strides[3];
   int64_t d_out_strides[3];
+  int64_t dq_strides[3];
+  int64_t dk_strides[3];
+  int64_t dv_strides[3];
   float scale;
   int32_t causal;
   int32_t dtype;

@@ -15,6 +15,7 @@ from torch_mojo_backend import mojo_backend
 class _TrainingStandIns(_StandIns):
     @staticmethod
     def layer_norm(x, w, b, eps, out_dtype=None):
+        _StandIns._record(x, ("layer_norm", out_dtype))
         xf = x.float()
         mean = xf.mean(-1)
         rstd = torch.rsqrt(xf.var(-1, unbiased=False) + eps)
@@ -110,6 +111,35 @@ def test_gpt2_training_step_matches_eager_autograd(training_stand_ins, attention
     assert {"gelu_backward", "layer_norm_backward", "sum_rows"} <= kinds
     if attention == "masked_softmax":
         assert "softmax_backward" in kinds
+
+
+def test_bf16_policy_training_graph_folds_the_layer_norm_cast(training_stand_ins):
+    """In the bf16 policy every LayerNorm output is cast to bf16 for the next GEMM; the forward of a
+    training step also keeps mean and rstd for the backward. The cast is folded into the LayerNorm
+    launch there too, and the gradients still match eager autograd."""
+    from demo_scripts.gpt2 import GPT2, GPTConfig
+
+    cfg = GPTConfig(vocab_size=97, block_size=16, n_layer=2, n_head=2, n_embd=32)
+    model = GPT2(cfg, "masked_softmax").init_weights(0).train().set_precision("bf16")
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 97, (2, 16), generator=g)
+    targets = torch.randint(0, 97, (2, 16), generator=g)
+
+    def loss_of(m):
+        return F.cross_entropy(m(ids).reshape(-1, 97).float(), targets.reshape(-1))
+
+    loss_of(model).backward()
+    want = _grads(model)
+    model.zero_grad()
+    before = af.fused_layer_norm_with_statistics.call_count
+    loss_of(torch.compile(model, backend=mojo_backend)).backward()
+    got = _grads(model)
+    assert af.fused_layer_norm_with_statistics.call_count > before
+    assert ("layer_norm", torch.bfloat16) in training_stand_ins.calls
+    for name in want:
+        scale = float(want[name].float().abs().max())
+        err = float((got[name].float() - want[name].float()).abs().max())
+        assert err <= 6e-2 * max(scale, 1e-8), f"{name}: {err:.3e} against {scale:.3e}"
 
 
 @pytest.mark.parametrize("causal", [False, True])

@@ -61,8 +61,9 @@ struct Params {
   const float* lse;    // [bh, q_len] natural log
   const float* delta;  // [bh, q_len]
   float* dq_part;      // [bh, kv_tiles, q_tiles, 64, 128]
-  __nv_bfloat16* dk;   // [bh, kv_len, 64]
+  __nv_bfloat16* dk;   // element strides (batch, head, position) below; 64 contiguous
   __nv_bfloat16* dv;
+  int64_t dk_sb, dk_sh, dk_st, dv_sb, dv_sh, dv_st;
   uint32_t heads, bh;
   int32_t q_len, kv_len, q_tiles, kv_tiles;
   float scale, scale_log2;
@@ -299,8 +300,9 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const int j0 = first_q_tile(i);
       const int32_t kv0 = i * BN;
       const int32_t key = kv0 + r;  // the key this thread owns in the dK / dV epilogue
-      __nv_bfloat16* dk_row = p.dk + ((int64_t)bh * p.kv_len + key) * D;
-      __nv_bfloat16* dv_row = p.dv + ((int64_t)bh * p.kv_len + key) * D;
+      const int64_t ob = bh / p.heads, oh = bh - (bh / p.heads) * p.heads;
+      __nv_bfloat16* dk_row = p.dk + ob * p.dk_sb + oh * p.dk_sh + (int64_t)key * p.dk_st;
+      __nv_bfloat16* dv_row = p.dv + ob * p.dv_sb + oh * p.dv_sh + (int64_t)key * p.dv_st;
       if (j0 >= p.q_tiles) {
         if (key < p.kv_len) {
 #pragma unroll
@@ -481,7 +483,8 @@ __global__ void sdpa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 // dq[bh, row, :] = sum over the key tiles that row attends to, in tile order. The partial tiles are
 // [64 columns][128 rows]: consecutive threads take consecutive rows (contiguous reads), four columns each.
 __global__ void sdpa_dq_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dq, int64_t bh_count,
-                                      int32_t q_len, int32_t q_tiles, int32_t kv_tiles, int causal) {
+                                      int64_t heads, int64_t dq_sb, int64_t dq_sh, int64_t dq_st, int32_t q_len,
+                                      int32_t q_tiles, int32_t kv_tiles, int causal) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // over bh * q_tiles * 16 * 128
   const int64_t total = bh_count * q_tiles * (D / 4) * BM;
   if (idx >= total) return;
@@ -502,7 +505,8 @@ __global__ void sdpa_dq_reduce_kernel(const float* __restrict__ part, __nv_bfloa
   uint2 o;
   o.x = pack_bf16x2(s[0], s[1]);
   o.y = pack_bf16x2(s[2], s[3]);
-  reinterpret_cast<uint2*>(dq + (bh * q_len + row) * D)[c4] = o;
+  const int64_t b = bh / heads, h = bh - b * heads;
+  reinterpret_cast<uint2*>(dq + b * dq_sb + h * dq_sh + (int64_t)row * dq_st)[c4] = o;
 }
 
 // Byte strides of the (position, head, batch) dims with legal stand-ins for size-1 dims.
@@ -562,6 +566,10 @@ const char* sdpa_bwd_ineligible(const b200_sdpa_bwd_args& a) {
       !strides_ok(a.v_strides, a.batch, a.heads, a.kv_len) || !strides_ok(a.d_out_strides, a.batch, a.heads, a.q_len))
     return "stride not a multiple of 16 bytes";
   if (a.o_strides[0] % 8 != 0 || a.o_strides[1] % 8 != 0 || a.o_strides[2] % 8 != 0) return "output stride not a multiple of 16 bytes";
+  for (int i = 0; i < 3; ++i)
+    if (a.dq_strides[i] % 8 != 0 || a.dk_strides[i] % 8 != 0 || a.dv_strides[i] % 8 != 0 || a.dq_strides[i] < 0 ||
+        a.dk_strides[i] < 0 || a.dv_strides[i] < 0)
+      return "gradient stride not a non-negative multiple of 16 bytes";
   if (a.q_len > INT32_MAX - 512 || a.kv_len > INT32_MAX - 512) return "sequence too long";
   if (a.batch * a.heads > (1ll << 24) || (a.batch * a.heads) * ((a.kv_len + BN - 1) / BN) > (1ll << 30))
     return "too many (batch, head, key tile) work items";
@@ -621,6 +629,8 @@ extern "C" B200_API int32_t b200_sdpa_bwd(const b200_sdpa_bwd_args* args, b200_s
   p.dq_part = dq_part;
   p.dk = static_cast<__nv_bfloat16*>(a.dk);
   p.dv = static_cast<__nv_bfloat16*>(a.dv);
+  p.dk_sb = a.dk_strides[0]; p.dk_sh = a.dk_strides[1]; p.dk_st = a.dk_strides[2];
+  p.dv_sb = a.dv_strides[0]; p.dv_sh = a.dv_strides[1]; p.dv_st = a.dv_strides[2];
   p.heads = (uint32_t)a.heads;
   p.bh = (uint32_t)bh;
   p.q_len = (int32_t)a.q_len;
@@ -650,7 +660,8 @@ extern "C" B200_API int32_t b200_sdpa_bwd(const b200_sdpa_bwd_args* args, b200_s
   {
     const int64_t total = bh * p.q_tiles * (D / 4) * BM;
     sdpa_dq_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        dq_part, static_cast<__nv_bfloat16*>(a.dq), bh, p.q_len, p.q_tiles, p.kv_tiles, p.causal);
+        dq_part, static_cast<__nv_bfloat16*>(a.dq), bh, a.heads, a.dq_strides[0], a.dq_strides[1], a.dq_strides[2],
+        p.q_len, p.q_tiles, p.kv_tiles, p.causal);
     B200_CHECK_LAUNCH("sdpa_bwd(dq)");
   }
   return B200_OK;

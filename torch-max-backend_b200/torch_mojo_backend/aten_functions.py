@@ -720,6 +720,21 @@ def fused_layer_norm(input, normalized_shape, weight, bias, eps, *, out_dtype):
 
 
 @_count_calls
+def fused_layer_norm_with_statistics(input, normalized_shape, weight, bias, eps, *, out_dtype):
+    """native_layer_norm whose output 0 only fed a dtype cast and whose statistics are used as well
+    (the forward of a training step): (y in `out_dtype`, mean, rstd) from one launch."""
+    k = len(normalized_shape)
+    lead = input.shape[: input.dim() - k]
+    cols = math.prod(normalized_shape)
+    w = weight.reshape(cols) if weight is not None else None
+    b = bias.reshape(cols) if bias is not None else None
+    y, mean, rstd = ops.layer_norm(input.reshape(*lead, cols), w, b, eps, out_dtype)
+    stat_shape = (*lead, *([1] * k))
+    stat_dtype = _traced_output_dtype(1, torch.float32)
+    return y.reshape(input.shape), mean.reshape(stat_shape).to(stat_dtype), rstd.reshape(stat_shape).to(stat_dtype)
+
+
+@_count_calls
 def fused_gemm(a, b, bias, residual, *, alpha, beta, epilogue, out_dtype, out_shape):
     """addmm / mm followed by (views,) gelu, an fp32 cast and/or a residual add, as one GEMM:
     out = act(alpha * a @ b + beta * bias) + residual, stored as `out_dtype`, viewed as `out_shape`."""
@@ -756,7 +771,8 @@ def fused_masked_softmax(x, mask, *, fill, scale, invert):
     return ops.softmax(masked)
 
 
-for _fused in (fused_layer_norm, fused_gemm, contiguous_or_alias, fused_masked_softmax, fused_embedding_sum):
+for _fused in (fused_layer_norm, fused_layer_norm_with_statistics, fused_gemm, contiguous_or_alias, fused_masked_softmax,
+               fused_embedding_sum):
     MAPPING_TORCH_ATEN_TO_MOJO[_fused] = _fused
 
 

@@ -173,6 +173,9 @@ class SdpaBwdArgs(ctypes.Structure):
         ("v_strides", ctypes.c_int64 * 3),
         ("o_strides", ctypes.c_int64 * 3),
         ("d_out_strides", ctypes.c_int64 * 3),
+        ("dq_strides", ctypes.c_int64 * 3),
+        ("dk_strides", ctypes.c_int64 * 3),
+        ("dv_strides", ctypes.c_int64 * 3),
         ("scale", ctypes.c_float),
         ("causal", ctypes.c_int32),
         ("dtype", ctypes.c_int32),

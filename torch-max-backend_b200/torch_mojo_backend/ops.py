@@ -591,9 +591,11 @@ def _sdpa_backward_cuda(d_out, q, k, v, o, lse, causal=False, scale=None):
     q, k, v, o = _unit_last_stride(q), _unit_last_stride(k), _unit_last_stride(v), _unit_last_stride(o)
     d_out = _unit_last_stride(d_out.to(q.dtype))
     lse_c = lse.reshape(B, H, -1)[:, :, :T].float().contiguous()
-    dq = torch.empty((B, H, T, D), dtype=q.dtype, device=device)
-    dk = torch.empty((B, H, S, D), dtype=q.dtype, device=device)
-    dv = torch.empty((B, H, S, D), dtype=q.dtype, device=device)
+    # Gradients laid out [B, T, H, D] in memory (returned as their [B, H, T, D] views), like the forward's
+    # output: the `transpose(1, 2)` + `contiguous` that follows in a projection's backward is then a view.
+    dq = torch.empty((B, T, H, D), dtype=q.dtype, device=device).transpose(1, 2)
+    dk = torch.empty((B, S, H, D), dtype=q.dtype, device=device).transpose(1, 2)
+    dv = torch.empty((B, S, H, D), dtype=q.dtype, device=device).transpose(1, 2)
     lib = native.lib()
 
     def args_for(b0, b1):
@@ -601,7 +603,8 @@ def _sdpa_backward_cuda(d_out, q, k, v, o, lse, causal=False, scale=None):
         a.q, a.k, a.v, a.o, a.d_out, a.lse = (t[b0:b1].data_ptr() for t in (q, k, v, o, d_out, lse_c))
         a.dq, a.dk, a.dv = dq[b0:b1].data_ptr(), dk[b0:b1].data_ptr(), dv[b0:b1].data_ptr()
         a.batch, a.heads, a.q_len, a.kv_len, a.head_dim = b1 - b0, H, T, S, D
-        for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o), ("d_out_strides", d_out)):
+        for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o), ("d_out_strides", d_out),
+                        ("dq_strides", dq), ("dk_strides", dk), ("dv_strides", dv)):
             arr = getattr(a, name)
             arr[0], arr[1], arr[2] = t.stride(0), t.stride(1), t.stride(2)
         a.scale, a.causal, a.dtype = float(scale), int(bool(causal)), native.dtype_enum(q.dtype)
@@ -624,8 +627,13 @@ def _sdpa_backward_cuda(d_out, q, k, v, o, lse, causal=False, scale=None):
 
 
 def _sdpa_backward_meta(d_out, q, k, v, o, lse, causal=False, scale=None):
-    return torch.empty_like(q, memory_format=torch.contiguous_format), torch.empty(
-        k.shape, dtype=k.dtype, device=k.device), torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    B, H, T, D = q.shape
+    S = k.shape[2]
+    return (
+        torch.empty((B, T, H, D), dtype=q.dtype, device=q.device).transpose(1, 2),
+        torch.empty((B, S, H, D), dtype=k.dtype, device=k.device).transpose(1, 2),
+        torch.empty((B, S, H, D), dtype=v.dtype, device=v.device).transpose(1, 2),
+    )
 
 
 # ---- embedding (+ second table) ---------------------------------------------------------------

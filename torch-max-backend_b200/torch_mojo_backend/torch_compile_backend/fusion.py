@@ -45,6 +45,10 @@ SDPA_OPS = (
     aten._scaled_dot_product_efficient_attention.default,
     aten._scaled_dot_product_cudnn_attention.default,
     aten.scaled_dot_product_attention.default,
+    # the gradients of the fused backward come out in [B, T, H, D] memory order as well
+    aten._scaled_dot_product_flash_attention_backward.default,
+    aten._scaled_dot_product_efficient_attention_backward.default,
+    aten._scaled_dot_product_cudnn_attention_backward.default,
 )
 
 
@@ -116,6 +120,49 @@ def _fuse_layer_norm(graph) -> int:
         if not native.supported_dtype(x.dtype):
             continue
         _replace(graph, cast, af.fused_layer_norm, tuple(node.args), {"out_dtype": dtype})
+        count += 1
+    return count
+
+
+def _fuse_layer_norm_with_statistics(graph) -> int:
+    """The same fold in a graph that also uses the statistics (the forward of a training step keeps
+    mean and rstd for the backward): output 0 -> cast becomes output 0 of a node that returns
+    (y in the cast's dtype, mean, rstd)."""
+    count = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten.native_layer_norm.default):
+            continue
+        items = {}
+        for user in node.users:
+            if not (_is_call(user, operator.getitem) and user.args[0] is node and user.args[1] in (0, 1, 2)):
+                items = None
+                break
+            if user.args[1] in items:
+                items = None
+                break
+            items[user.args[1]] = user
+        if not items or 0 not in items or len(items) < 2:
+            continue  # no statistics in use: _fuse_layer_norm's case
+        cast = _only_user(items[0])
+        dtype = _plain_cast(cast)
+        x = _val(node.args[0])
+        if dtype is None or not native.supported_dtype(dtype) or not isinstance(x, torch.Tensor):
+            continue
+        if not native.supported_dtype(x.dtype):
+            continue
+        with graph.inserting_after(node):
+            new = graph.call_function(af.fused_layer_norm_with_statistics, args=tuple(node.args), kwargs={"out_dtype": dtype})
+        old_val = _val(node)
+        new.meta = dict(node.meta)
+        if isinstance(old_val, (tuple, list)):
+            new.meta["val"] = (_val(cast),) + tuple(old_val[1:])
+        with graph.inserting_after(new):
+            y = graph.call_function(operator.getitem, args=(new, 0))
+        y.meta = dict(cast.meta)
+        cast.replace_all_uses_with(y)
+        for index in (1, 2):
+            if index in items:
+                items[index].args = (new, index)
         count += 1
     return count
 
@@ -323,7 +370,7 @@ def fuse_graph(gm: torch.fx.GraphModule) -> dict[str, int]:
     """Rewrites gm.graph in place and returns how many chains of each kind were folded."""
     graph = gm.graph
     stats = {
-        "layer_norm_cast": _fuse_layer_norm(graph),
+        "layer_norm_cast": _fuse_layer_norm(graph) + _fuse_layer_norm_with_statistics(graph),
         "gemm_epilogue": _fuse_gemm_epilogues(graph),
         "attention_output_copy": _drop_attention_output_copies(graph),
         "masked_softmax": _fuse_masked_softmax(graph),
