@@ -15,11 +15,11 @@
 // [batch*heads, key tile, query tile, 64 columns, 128 rows] (fp32, rows innermost so that a warp's
 // stores are contiguous) and a second kernel adds the tiles up in tile order, so the gradient does
 // not depend on which CTA ran first (no atomics).
-// Steps overlap: P / dS have two shared-memory buffers, the score MMAs of step n + 1 are issued
-// BEFORE the three products of step n, and the row threads read dQ of step n after their
-// arithmetic for step n + 1 -- so the tensor core works on step n while the row threads are already
-// on step n + 1, and neither waits for the other inside an item.
-//   warp 0      TMA producer: K_i, V_i per item; Q_j, dO_j into a two-deep ring.
+// Steps overlap: Q_j / dO_j have a three-deep ring, the score MMAs of step n + 1 are issued as soon
+// as the row threads have pulled S and dP of step n into registers -- BEFORE the three products of
+// step n --, the row threads do the arithmetic of step n + 1 in registers while those products run
+// and store P / dS only when they have completed, and they read dQ of step n after that.
+//   warp 0      TMA producer: K_i, V_i per item; Q_j, dO_j into a three-deep ring.
 //   warp 1      MMA issuer (converged warp, one elected lane).
 //   warps 2-9   two threads per query row (warps w and w + 4 address the same 32 TMEM lanes): each
 //               takes 64 of the tile's 128 keys for P and dS -- with the LSE given, no value
@@ -47,11 +47,12 @@ constexpr int TMEM_S = 0, TMEM_DP = 128, TMEM_DV = 256, TMEM_DK = 320, TMEM_DQ =
 
 constexpr int SMEM_K = 0;
 constexpr int SMEM_V = SMEM_K + TILE_BYTES;
-constexpr int SMEM_Q = SMEM_V + TILE_BYTES;         // two stages
-constexpr int SMEM_DO = SMEM_Q + 2 * TILE_BYTES;    // two stages
-constexpr int SMEM_P = SMEM_DO + 2 * TILE_BYTES;    // [2 buffers][2 key halves][128 rows][64 keys]
-constexpr int SMEM_DS = SMEM_P + 4 * TILE_BYTES;
-constexpr int SMEM_BAR = SMEM_DS + 4 * TILE_BYTES;
+constexpr int kStages = 3;                          // Q_j / dO_j ring
+constexpr int SMEM_Q = SMEM_V + TILE_BYTES;
+constexpr int SMEM_DO = SMEM_Q + kStages * TILE_BYTES;
+constexpr int SMEM_P = SMEM_DO + kStages * TILE_BYTES;  // [2 key halves][128 rows][64 keys]
+constexpr int SMEM_DS = SMEM_P + 2 * TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_DS + 2 * TILE_BYTES;
 constexpr int kNumBars = 16;
 constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
 constexpr int SMEM_BYTES = SMEM_MISC + 16 + 1024;
@@ -113,17 +114,16 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   // Each barrier is used once per item or once per (i, j) step by one producer and one consumer
   // side, in strict alternation, so use n is waited for with parity n & 1.
   const uint32_t kv_full = bar, kv_empty = bar + 8;                  // per item
-  auto qd_full = [&](int s) { return bar + 8u * (2 + s); };         // per step, two stages
-  auto qd_empty = [&](int s) { return bar + 8u * (4 + s); };
+  auto qd_full = [&](int s) { return bar + 8u * (2 + s); };         // per step, kStages stages (bars 2-4)
+  auto qd_empty = [&](int s) { return bar + 8u * (13 + s); };       // (bars 13-15)
   const uint32_t sdp_full = bar + 8 * 6;    // S and dP are in tensor memory
   const uint32_t sdp_free = bar + 8 * 7;    // the row threads have read them (one arrival per warp)
-  // (bar + 8 * 9 is unused)
-  auto pds_full = [&](int b) { return bar + 8u * (8 + b); };    // P and dS are in shared-memory buffer b (one arrival per warp)
-  auto pds_free = [&](int b) { return bar + 8u * (14 + b); };   // the three MMAs that read buffer b have completed
+  const uint32_t pds_full = bar + 8 * 8;    // P and dS are in shared memory (one arrival per warp)
+  const uint32_t pds_free = bar + 8 * 9;    // the three MMAs that read them have completed
   const uint32_t dq_full = bar + 8 * 10;    // dQ_j(i) is in tensor memory
   const uint32_t dq_free = bar + 8 * 11;    // the row threads have read it
   const uint32_t acc_full = bar + 8 * 12;   // dK_i, dV_i complete (per item)
-  const uint32_t acc_free = bar + 8 * 13;   // the row threads have read them
+  const uint32_t acc_free = bar + 8 * 5;    // the row threads have read them
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + SMEM_MISC);
   volatile uint32_t* tmem_holder = misc;
   volatile uint32_t* abort_flag = misc + 1;
@@ -132,16 +132,14 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   if (threadIdx.x == 0) {
     ptx::mbar_init(kv_full, 1);
     ptx::mbar_init(kv_empty, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(qd_full(s), 1);
       ptx::mbar_init(qd_empty(s), 1);
     }
     ptx::mbar_init(sdp_full, 1);
     ptx::mbar_init(sdp_free, kRowWarps);
-    for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(pds_full(b), kRowWarps);
-      ptx::mbar_init(pds_free(b), 1);
-    }
+    ptx::mbar_init(pds_full, kRowWarps);
+    ptx::mbar_init(pds_free, 1);
     ptx::mbar_init(dq_full, 1);
     ptx::mbar_init(dq_free, kRowWarps);
     ptx::mbar_init(acc_full, 1);
@@ -183,8 +181,8 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         if (p.v_heads_inner) ptx::tma_load_4d(v_smem, &tmap_v, kv_full, 0, h, i * BN, b);
         else ptx::tma_load_4d(v_smem, &tmap_v, kv_full, 0, i * BN, h, b);
         for (int j = first_q_tile(i); j < p.q_tiles; ++j, ++steps) {
-          const int s = steps & 1;
-          if (!ptx::mbar_wait_relaxed(qd_empty(s), ((steps >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          const int s = steps % kStages;
+          if (!ptx::mbar_wait_relaxed(qd_empty(s), ((steps / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
           ptx::mbar_arrive_expect_tx(qd_full(s), 2 * TILE_BYTES);
           if (p.q_heads_inner) ptx::tma_load_4d(q_smem + s * TILE_BYTES, &tmap_q, qd_full(s), 0, h, j * BM, b);
           else ptx::tma_load_4d(q_smem + s * TILE_BYTES, &tmap_q, qd_full(s), 0, j * BM, h, b);
@@ -217,13 +215,13 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       ++accs;
       // dV += P^T dO, dK += dS^T Q, dQ = dS K of step n (the j-th query tile), from P / dS buffer n & 1
       auto issue_products = [&](uint32_t n, int j, bool last) -> bool {
-        const int sb = n & 1;
-        bool ready = ptx::mbar_wait(pds_full(sb), (n >> 1) & 1, abort_flag);
+        const int sb = n % kStages;
+        bool ready = ptx::mbar_wait(pds_full, n & 1, abort_flag);
         if (n > 0) ready = ready && ptx::mbar_wait(dq_free, (n - 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ready)) return false;
         ptx::tc_fence_after_sync();
         const uint32_t qs = q_smem + sb * TILE_BYTES, dos = do_smem + sb * TILE_BYTES;
-        const uint32_t pb = p_smem + sb * 2 * TILE_BYTES, dsb = ds_smem + sb * 2 * TILE_BYTES;
+        const uint32_t pb = p_smem, dsb = ds_smem;
         if (ptx::elect_one()) {
           const uint32_t acc = j > j0 ? 1u : 0u;
           // contraction over the 128 query rows: eight steps of 16 rows; A = P^T / dS^T through the
@@ -246,7 +244,7 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                             ptx::smem_desc_sw128(k_smem + kk * 2048, 0, 1024), idesc_q, kk > 0 ? 1u : 0u);
           }
           ptx::tc_commit(dq_full);
-          ptx::tc_commit(pds_free(sb));
+          ptx::tc_commit(pds_free);
           ptx::tc_commit(qd_empty(sb));
           if (last) {
             ptx::tc_commit(acc_full);
@@ -257,8 +255,8 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         return true;
       };
       for (int j = j0; j < p.q_tiles; ++j, ++steps) {
-        const int s = steps & 1;
-        go = ptx::mbar_wait(qd_full(s), (steps >> 1) & 1, abort_flag);
+        const int s = steps % kStages;
+        go = ptx::mbar_wait(qd_full(s), (steps / kStages) & 1, abort_flag);
         if (steps > 0) go = go && ptx::mbar_wait(sdp_free, (steps - 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
         ptx::tc_fence_after_sync();
@@ -342,11 +340,8 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         const float lse2 = stats.x * 1.4426950408889634f;
         const float delta = stats.y;
         if (j + 1 < p.q_tiles) stats = row_stats(j + 1);
-        const int sb = steps & 1;  // P / dS buffer of this step
         PROBE_T0(t0);
-        bool go = ptx::mbar_wait(sdp_full, steps & 1, abort_flag);
-        if (steps > 1) go = go && ptx::mbar_wait(pds_free(sb), ((steps >> 1) - 1) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(sdp_full, steps & 1, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
         PROBE_ADD(c_wait_sdp, t0);
         PROBE_T0(t1);
@@ -370,10 +365,10 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         // packed two-wide arithmetic: P = exp2(S scale log2e - LSE log2e), dS = P (dP scale - delta scale)
         const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), nlse2 = make_float2(-lse2, -lse2);
         const float2 sc2 = make_float2(p.scale, p.scale), nds2 = make_float2(-delta * p.scale, -delta * p.scale);
-        const uint32_t half_p = p_smem + (sb * 2 + half) * TILE_BYTES, half_d = ds_smem + (sb * 2 + half) * TILE_BYTES;
+        const uint32_t half_p = p_smem + half * TILE_BYTES, half_d = ds_smem + half * TILE_BYTES;
+        uint32_t pp[32], dd[32];  // the 64 probabilities and 64 dS values of this thread, as bf16 pairs
 #pragma unroll
         for (int u = 0; u < 8; ++u) {  // eight 16-byte units of eight keys
-          uint32_t pp[4], dd[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = 8 * u + 2 * e;
@@ -385,16 +380,21 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             }
             const float2 t = __ffma2_rn(make_float2(__uint_as_float(dpv[c]), __uint_as_float(dpv[c + 1])), sc2, nds2);
             const float2 ds = __fmul2_rn(pr, t);
-            pp[e] = pack_bf16x2(pr.x, pr.y);
-            dd[e] = pack_bf16x2(ds.x, ds.y);
+            pp[4 * u + e] = pack_bf16x2(pr.x, pr.y);
+            dd[4 * u + e] = pack_bf16x2(ds.x, ds.y);
           }
-          st_shared_v4(swz(half_p, r, u), pp[0], pp[1], pp[2], pp[3]);
-          st_shared_v4(swz(half_d, r, u), dd[0], dd[1], dd[2], dd[3]);
+        }
+        // the products of the previous step read P / dS from shared memory: store only when they are done
+        if (steps > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(pds_free, (steps - 1) & 1, abort_flag))) { ok = false; break; }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          st_shared_v4(swz(half_p, r, u), pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+          st_shared_v4(swz(half_d, r, u), dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
         }
         // P / dS are written: make them visible to the tensor core's proxy
         ptx::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(pds_full(sb));
+        if (lane == 0) ptx::mbar_arrive(pds_full);
         PROBE_ADD(c_math, t1);
         // dQ of the previous step, whose products ran on the tensor core during the arithmetic above
         if (j > j0 && !dq_epilogue(steps - 1, j - 1)) { ok = false; break; }
