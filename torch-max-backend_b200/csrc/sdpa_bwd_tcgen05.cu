@@ -19,7 +19,8 @@
 // as the row threads have pulled S and dP of step n into registers -- BEFORE the three products of
 // step n --, the row threads do the arithmetic of step n + 1 in registers while those products run
 // and store P / dS only when they have completed, and they read dQ of step n after that.
-//   warp 0      TMA producer: K_i, V_i per item; Q_j, dO_j into a three-deep ring.
+//   warp 0      TMA producer: K_i, V_i per item (two stages: the next item's land while this one
+//               computes); Q_j, dO_j into a three-deep ring.
 //   warp 1      MMA issuer (converged warp, one elected lane).
 //   warps 2-9   two threads per query row (warps w and w + 4 address the same 32 TMEM lanes): each
 //               takes 64 of the tile's 128 keys for P and dS -- with the LSE given, no value
@@ -45,15 +46,15 @@ constexpr int TILE_BYTES = 128 * D * 2;  // 16 KiB: a [128][64] bf16 tile; also 
 constexpr int kTmemCols = 512;
 constexpr int TMEM_S = 0, TMEM_DP = 128, TMEM_DV = 256, TMEM_DK = 320, TMEM_DQ = 384;
 
-constexpr int SMEM_K = 0;
-constexpr int SMEM_V = SMEM_K + TILE_BYTES;
+constexpr int SMEM_K = 0;                           // two stages: the next item's K_i / V_i land during this one
+constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;
 constexpr int kStages = 3;                          // Q_j / dO_j ring
-constexpr int SMEM_Q = SMEM_V + TILE_BYTES;
+constexpr int SMEM_Q = SMEM_V + 2 * TILE_BYTES;
 constexpr int SMEM_DO = SMEM_Q + kStages * TILE_BYTES;
 constexpr int SMEM_P = SMEM_DO + kStages * TILE_BYTES;  // [2 key halves][128 rows][64 keys]
 constexpr int SMEM_DS = SMEM_P + 2 * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_DS + 2 * TILE_BYTES;
-constexpr int kNumBars = 16;
+constexpr int kNumBars = 18;
 constexpr int SMEM_MISC = SMEM_BAR + kNumBars * 8;
 constexpr int SMEM_BYTES = SMEM_MISC + 16 + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of one SM exceeded");
@@ -113,7 +114,8 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   const uint32_t bar = base + SMEM_BAR;
   // Each barrier is used once per item or once per (i, j) step by one producer and one consumer
   // side, in strict alternation, so use n is waited for with parity n & 1.
-  const uint32_t kv_full = bar, kv_empty = bar + 8;                  // per item
+  auto kv_full = [&](int st) { return bar + 8u * st; };              // per item, two stages (bars 0-1)
+  auto kv_empty = [&](int st) { return bar + 8u * (16 + st); };       // (bars 16-17)
   auto qd_full = [&](int s) { return bar + 8u * (2 + s); };         // per step, kStages stages (bars 2-4)
   auto qd_empty = [&](int s) { return bar + 8u * (13 + s); };       // (bars 13-15)
   const uint32_t sdp_full = bar + 8 * 6;    // S and dP are in tensor memory
@@ -130,8 +132,10 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    ptx::mbar_init(kv_full, 1);
-    ptx::mbar_init(kv_empty, 1);
+    for (int st = 0; st < 2; ++st) {
+      ptx::mbar_init(kv_full(st), 1);
+      ptx::mbar_init(kv_empty(st), 1);
+    }
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(qd_full(s), 1);
       ptx::mbar_init(qd_empty(s), 1);
@@ -174,12 +178,13 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         const int i = item_tile(w);
         const uint32_t bh = item_bh(w);
         const int32_t b = (int32_t)(bh / p.heads), h = (int32_t)(bh - (uint32_t)b * p.heads);
-        if (!ptx::mbar_wait_relaxed(kv_empty, (items & 1) ^ 1, abort_flag)) break;
-        ptx::mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
-        if (p.k_heads_inner) ptx::tma_load_4d(k_smem, &tmap_k, kv_full, 0, h, i * BN, b);
-        else ptx::tma_load_4d(k_smem, &tmap_k, kv_full, 0, i * BN, h, b);
-        if (p.v_heads_inner) ptx::tma_load_4d(v_smem, &tmap_v, kv_full, 0, h, i * BN, b);
-        else ptx::tma_load_4d(v_smem, &tmap_v, kv_full, 0, i * BN, h, b);
+        const int st = items & 1;
+        if (!ptx::mbar_wait_relaxed(kv_empty(st), ((items >> 1) & 1) ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(kv_full(st), 2 * TILE_BYTES);
+        if (p.k_heads_inner) ptx::tma_load_4d(k_smem + st * TILE_BYTES, &tmap_k, kv_full(st), 0, h, i * BN, b);
+        else ptx::tma_load_4d(k_smem + st * TILE_BYTES, &tmap_k, kv_full(st), 0, i * BN, h, b);
+        if (p.v_heads_inner) ptx::tma_load_4d(v_smem + st * TILE_BYTES, &tmap_v, kv_full(st), 0, h, i * BN, b);
+        else ptx::tma_load_4d(v_smem + st * TILE_BYTES, &tmap_v, kv_full(st), 0, i * BN, h, b);
         for (int j = first_q_tile(i); j < p.q_tiles; ++j, ++steps) {
           const int s = steps % kStages;
           if (!ptx::mbar_wait_relaxed(qd_empty(s), ((steps / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -201,14 +206,16 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     for (uint32_t w = blockIdx.x; w < p.num_items && ok; w += gridDim.x, ++items) {
       const int i = item_tile(w);
       const int j0 = first_q_tile(i);
+      const int st = items & 1;  // K / V stage of this item
+      const uint32_t kt = k_smem + st * TILE_BYTES, vt = v_smem + st * TILE_BYTES;
       if (j0 >= p.q_tiles) {
-        // no query row attends to this key tile: nothing to accumulate; free K/V for the next item
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(kv_full, items & 1, abort_flag))) break;
-        if (ptx::elect_one()) ptx::tc_commit(kv_empty);
+        // no query row attends to this key tile: nothing to accumulate; free its K/V stage
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(kv_full(st), (items >> 1) & 1, abort_flag))) break;
+        if (ptx::elect_one()) ptx::tc_commit(kv_empty(st));
         __syncwarp();
         continue;
       }
-      bool go = ptx::mbar_wait(kv_full, items & 1, abort_flag);
+      bool go = ptx::mbar_wait(kv_full(st), (items >> 1) & 1, abort_flag);
       // dK / dV restart with this item: the row threads must have read the previous item's
       if (accs > 0) go = go && ptx::mbar_wait(acc_free, (accs - 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, go)) break;
@@ -241,14 +248,14 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           for (int kk = 0; kk < BN / 16; ++kk) {
             ptx::mma_f16_ss(tmem + TMEM_DQ,
                             ptx::smem_desc_sw128(dsb + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024),
-                            ptx::smem_desc_sw128(k_smem + kk * 2048, 0, 1024), idesc_q, kk > 0 ? 1u : 0u);
+                            ptx::smem_desc_sw128(kt + kk * 2048, 0, 1024), idesc_q, kk > 0 ? 1u : 0u);
           }
           ptx::tc_commit(dq_full);
           ptx::tc_commit(pds_free);
           ptx::tc_commit(qd_empty(sb));
           if (last) {
             ptx::tc_commit(acc_full);
-            ptx::tc_commit(kv_empty);
+            ptx::tc_commit(kv_empty(st));
           }
         }
         __syncwarp();
@@ -265,12 +272,12 @@ sdpa_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             ptx::mma_f16_ss(tmem + TMEM_S, ptx::smem_desc_sw128(qs + kk * 32, 0, 1024),
-                            ptx::smem_desc_sw128(k_smem + kk * 32, 0, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                            ptx::smem_desc_sw128(kt + kk * 32, 0, 1024), idesc_s, kk > 0 ? 1u : 0u);
           }
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             ptx::mma_f16_ss(tmem + TMEM_DP, ptx::smem_desc_sw128(dos + kk * 32, 0, 1024),
-                            ptx::smem_desc_sw128(v_smem + kk * 32, 0, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                            ptx::smem_desc_sw128(vt + kk * 32, 0, 1024), idesc_s, kk > 0 ? 1u : 0u);
           }
           ptx::tc_commit(sdp_full);
         }
