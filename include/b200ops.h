@@ -158,8 +158,11 @@ B200_API int32_t b200_softmax_backward(const void* dy, const void* y, void* dx, 
  *   dx = rstd (g - mean_j g - xhat mean_j(g xhat)),  xhat = (x - mean) rstd,  g = dy gamma,
  *   dgamma = sum_rows dy xhat,  dbeta = sum_rows dy   (fp32 sums in a fixed order).
  * gamma may be NULL (ones); dgamma / dbeta may be NULL (not wanted) and are written in
- * param_dtype; dx is contiguous and has the dtype of dy. The workspace holds the per-CTA column
- * sums (b200_layer_norm_backward_workspace_bytes, 16-byte aligned).
+ * param_dtype; dx is contiguous and has the dtype of dy, or fp32 when x is fp32 and dy bf16 (the
+ * gradient a bf16 consumer sends back into an fp32 stream: no widening pass before the kernel).
+ * dx_add may be NULL; otherwise it is a contiguous [rows, cols] tensor of dx's dtype that is added to
+ * dx in the same pass (the gradient that reaches x along a residual branch). The workspace holds the
+ * per-CTA column sums (b200_layer_norm_backward_workspace_bytes, 16-byte aligned).
  * Replaces: the decomposition of aten.native_layer_norm_backward
  * (torch_mojo_backend/aten_functions.py:2871) and the reference's eager kernels
  * _dx_warp_rows (torch_mojo_backend/eager_kernels/normalization_backward_dx.mojo:66-175) and
@@ -167,8 +170,9 @@ B200_API int32_t b200_softmax_backward(const void* dy, const void* y, void* dx, 
  * (torch_mojo_backend/eager_kernels/normalization_backward_params.mojo:75-180). */
 B200_API size_t b200_layer_norm_backward_workspace_bytes(int64_t rows, int64_t cols);
 B200_API int32_t b200_layer_norm_backward(const void* dy, const void* x, const float* mean,
-                                 const float* rstd, const void* gamma, void* dx, void* dgamma,
-                                 void* dbeta, void* workspace, size_t workspace_bytes,
+                                 const float* rstd, const void* gamma, const void* dx_add,
+                                 void* dx, void* dgamma, void* dbeta, void* workspace,
+                                 size_t workspace_bytes,
                                  int64_t rows, int64_t cols, int64_t dy_row_stride,
                                  int64_t x_row_stride, int32_t x_dtype, int32_t dy_dtype,
                                  int32_t param_dtype, int32_t dx_dtype, b200_stream_t stream);

@@ -121,6 +121,48 @@ def test_layer_norm_backward_mixed_dtypes_no_weight_and_determinism(ops):
     assert_parity(dx2, ref_ops.layer_norm_backward(dy, x, mean, rstd, None)[0], bf16=True)
 
 
+@pytest.mark.parametrize("shape", [(8192, 1600), (4096, 768), (37, 40), (5, 7), (3, 5000), (2, 9, 64)])
+@pytest.mark.parametrize("param_dtype", DTYPES)
+def test_layer_norm_backward_widening_with_residual_gradient(ops, shape, param_dtype):
+    """bf16 dy, fp32 x -> fp32 dx with the residual branch's gradient added in the same launch: dx is
+    the fp32 result of the formula on the bf16-valued dy plus dx_add, never rounded to bf16."""
+    cols = shape[-1]
+    x = gen(shape, torch.float32, 70)
+    dy = gen(shape, torch.bfloat16, 71)
+    extra = gen(shape, torch.float32, 72)
+    w = gen((cols,), param_dtype, 73, mean=1.0, std=0.2)
+    _, mean, rstd = ref_ops.layer_norm(x, [cols], w, None, 1e-5)
+    rdx, rdgamma, rdbeta = ref_ops.layer_norm_backward(dy.float(), x, mean, rstd, w.float())
+    dev = (dy.cuda(), x.cuda(), mean.cuda(), rstd.cuda(), w.cuda())
+    dx, dgamma, dbeta = ops.layer_norm_backward(*dev, True, True, extra.cuda(), torch.float32)
+    assert dx.dtype == torch.float32 and dgamma.dtype == param_dtype and dx.shape == x.shape
+    assert_parity(dx, rdx + extra, bf16=False, what="dx + dx_add")
+    assert_parity(dgamma, rdgamma, bf16=param_dtype == torch.bfloat16, what="dgamma")
+    assert_parity(dbeta, rdbeta, bf16=param_dtype == torch.bfloat16, what="dbeta")
+    plain, _, _ = ops.layer_norm_backward(*dev, False, False, None, torch.float32)
+    assert_parity(plain, rdx, bf16=False, what="dx (fp32 from bf16 dy)")
+    assert torch.equal(dx, plain + extra.cuda()), "dx_add is added to the fp32 value that would have been stored"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layer_norm_backward_residual_gradient_same_dtype_and_errors(ops, dtype):
+    x, dy, extra = gen((300, 1600), dtype, 74), gen((300, 1600), dtype, 75), gen((300, 1600), dtype, 76)
+    w = gen((1600,), dtype, 77, mean=1.0, std=0.2)
+    _, mean, rstd = ref_ops.layer_norm(x, [1600], w, None, 1e-5)
+    dev = (dy.cuda(), x.cuda(), mean.cuda(), rstd.cuda(), w.cuda())
+    dx, _, _ = ops.layer_norm_backward(*dev, True, True, extra.cuda())
+    rdx = ref_ops.layer_norm_backward(dy, x, mean, rstd, w)[0]
+    assert dx.dtype == dtype
+    assert_parity(dx, rdx.float() + extra.float(), bf16=dtype == torch.bfloat16, what="dx + dx_add")
+    with pytest.raises(RuntimeError, match="dx_add"):
+        ops.layer_norm_backward(*dev, True, True, extra.cuda()[:100])
+    with pytest.raises(RuntimeError, match="dx_add"):
+        ops.layer_norm_backward(*dev, True, True, extra.cuda().double())
+    if dtype == torch.float32:
+        with pytest.raises(RuntimeError, match="dx takes the dtype of dy"):
+            ops.layer_norm_backward(*dev, True, True, None, torch.bfloat16)  # narrowing is not offered
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(65536, 1600), (8192, 6400), (33, 65), (5, 4), (1, 8), (300, 5000)])
 def test_sum_rows(ops, dtype, shape):
@@ -129,6 +171,41 @@ def test_sum_rows(ops, dtype, shape):
     assert y.shape == (shape[-1],) and y.dtype == torch.float32
     assert_parity(y, x.double().sum(0).float(), bf16=False, scale=float(shape[0]) ** 0.5 * 4)
     assert torch.equal(ops.sum_rows(x.cuda(), torch.float32), y)
+
+
+def test_backward_kernels_empty_and_error_cases(ops):
+    from torch_mojo_backend import native
+
+    e = torch.empty((0, 64), device="cuda")
+    assert ops.gelu_backward(e, e, "tanh").shape == (0, 64)
+    assert ops.softmax_backward(e, e).shape == (0, 64)
+    w = torch.ones(64, device="cuda")
+    dx, dg, db = ops.layer_norm_backward(e, e, torch.empty(0, device="cuda"), torch.empty(0, device="cuda"), w)
+    assert dx.shape == (0, 64) and float(dg.abs().sum()) == 0.0 and float(db.abs().sum()) == 0.0
+    assert float(ops.sum_rows(e).abs().sum()) == 0.0 and ops.sum_rows(e).shape == (64,)
+    x = torch.randn(4, 8, device="cuda")
+    with pytest.raises(RuntimeError, match="differ"):
+        ops.gelu_backward(x, x.bfloat16(), "none")
+    with pytest.raises(ValueError, match="approximate"):
+        ops.gelu_backward(x, x, "fast")
+    with pytest.raises(RuntimeError, match="differ"):
+        ops.softmax_backward(x, x[:, :4])
+    with pytest.raises(RuntimeError, match="mean / rstd"):
+        ops.layer_norm_backward(x, x, torch.zeros(3, device="cuda"), torch.ones(3, device="cuda"), None)
+    with pytest.raises(RuntimeError, match="head_dim 64"):
+        q = torch.randn(1, 1, 16, 32, device="cuda").bfloat16()
+        ops.sdpa_backward(q, q, q, q, q, torch.zeros(1, 1, 16, device="cuda"))
+    with pytest.raises(RuntimeError, match="CPU"):
+        ops.gelu_backward(x.cpu(), x.cpu(), "none")
+    # a workspace that is too small is refused before anything is launched
+    import ctypes
+
+    lib = native.lib()
+    big = torch.randn(512, 256, device="cuda")
+    out = torch.empty(256, device="cuda")
+    status = lib.b200_sum_rows(big.data_ptr(), out.data_ptr(), None, 0, 512, 256, 256, 0, 0, native.current_stream(big.device))
+    assert status == native.ERR_WORKSPACE if hasattr(native, "ERR_WORKSPACE") else status == -4
+    assert native.device_status() == 0
 
 
 @pytest.mark.parametrize("b_layout", ["kn", "nk"])

@@ -46,8 +46,10 @@ class _TrainingStandIns(_StandIns):
         return (scale * yf * (gf - (gf * yf).sum(-1, keepdim=True))).to(out_dtype or y.dtype)
 
     @staticmethod
-    def layer_norm_backward(dy, x, mean, rstd, weight, want_weight=True, want_bias=True):
-        _StandIns._record(x, ("layer_norm_backward", want_weight, want_bias))
+    def layer_norm_backward(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None, dx_dtype=None):
+        _StandIns._record(x, ("layer_norm_backward", want_weight, want_bias, dx_add is not None, dx_dtype))
+        assert dx_dtype in (None, dy.dtype) or (dy.dtype, x.dtype, dx_dtype) == (torch.bfloat16, torch.float32, torch.float32)
+        assert dx_add is None or (dx_add.shape == x.shape and dx_add.dtype == (dx_dtype or dy.dtype))
         cols = x.shape[-1]
         xf, gf = x.float().reshape(-1, cols), dy.float().reshape(-1, cols)
         xh = (xf - mean.reshape(-1, 1).float()) * rstd.reshape(-1, 1).float()
@@ -55,7 +57,7 @@ class _TrainingStandIns(_StandIns):
         dx = rstd.reshape(-1, 1).float() * (g - g.mean(-1, keepdim=True) - xh * (g * xh).mean(-1, keepdim=True))
         pd = weight.dtype if weight is not None else x.dtype
         return (
-            dx.reshape(x.shape).to(dy.dtype),
+            (dx.reshape(x.shape) + (dx_add.float() if dx_add is not None else 0.0)).to(dx_dtype or dy.dtype),
             (gf * xh).sum(0).to(pd) if want_weight else None,
             gf.sum(0).to(pd) if want_bias else None,
         )
@@ -132,10 +134,17 @@ def test_bf16_policy_training_graph_folds_the_layer_norm_cast(training_stand_ins
     want = _grads(model)
     model.zero_grad()
     before = af.fused_layer_norm_with_statistics.call_count
+    before_backward = af.fused_layer_norm_backward.call_count
     loss_of(torch.compile(model, backend=mojo_backend)).backward()
     got = _grads(model)
     assert af.fused_layer_norm_with_statistics.call_count > before
     assert ("layer_norm", torch.bfloat16) in training_stand_ins.calls
+    # backward: all five LayerNorm gradients read the bf16 gradient of the GEMM before them and write
+    # fp32; the four inside the blocks also add the gradient of the residual branch in the same launch
+    assert af.fused_layer_norm_backward.call_count > before_backward
+    kinds = [c for c in training_stand_ins.calls if c[0] == "layer_norm_backward"]
+    assert len(kinds) == 5 and all(c[4] == torch.float32 for c in kinds)
+    assert sum(1 for c in kinds if c[3]) == 4
     for name in want:
         scale = float(want[name].float().abs().max())
         err = float((got[name].float() - want[name].float()).abs().max())

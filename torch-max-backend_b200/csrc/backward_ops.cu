@@ -304,6 +304,7 @@ struct Raw4<float> {
   float4 v;
   __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
   __device__ __forceinline__ void load_stream(const float* p) { v = __ldcs(reinterpret_cast<const float4*>(p)); }
+  __device__ __forceinline__ void load_shared(const float* p) { v = *reinterpret_cast<const float4*>(p); }
   __device__ __forceinline__ void unpack(float (&o)[4]) const { o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
 };
 template <>
@@ -311,11 +312,24 @@ struct Raw4<__nv_bfloat16> {
   uint2 v;
   __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint2*>(p); }
   __device__ __forceinline__ void load_stream(const __nv_bfloat16* p) { v = __ldcs(reinterpret_cast<const uint2*>(p)); }
+  __device__ __forceinline__ void load_shared(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint2*>(p); }
   __device__ __forceinline__ void unpack(float (&o)[4]) const {
     o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
     o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
   }
 };
+// Asynchronous global -> shared copy of 8 or 16 bytes (both addresses aligned to the size), read
+// back by the thread that issued it after cp_async_wait_all().
+template <int BYTES>
+__device__ __forceinline__ void cp_async_small(void* smem_dst, const void* gmem_src) {
+  static_assert(BYTES == 8 || BYTES == 16, "cp.async.ca copies 4, 8 or 16 bytes");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src), "n"(BYTES)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 constexpr int kLnbMaxChunks = 16; // 128-column chunks a lane can keep column sums for (2048 columns)
 
 // LayerNorm backward, one WARP per row and no CTA-wide synchronisation while rows stream. A warp
@@ -332,14 +346,28 @@ constexpr int kLnbMaxChunks = 16; // 128-column chunks a lane can keep column su
 template <typename Tx, typename Tg, typename Tp, typename Td, int MAXC>
 __global__ void __launch_bounds__(kLnbWarps * 32, kLnbCtasPerSm)
 layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, const float* __restrict__ mean,
-                           const float* __restrict__ rstd, const Tp* __restrict__ gamma, Td* __restrict__ dx,
-                           float* __restrict__ part_g, float* __restrict__ part_b, int64_t rows, int cols,
-                           int64_t dy_rs, int64_t x_rs) {
-  extern __shared__ float lnb_smem[];  // [kLnbWarps][2][cols]: every warp's column sums of dy xhat and dy
+                           const float* __restrict__ rstd, const Tp* __restrict__ gamma, const Td* __restrict__ dx_add,
+                           Td* __restrict__ dx, float* __restrict__ part_g, float* __restrict__ part_b, int64_t rows,
+                           int cols, int64_t dy_rs, int64_t x_rs) {
+  // [kLnbWarps][2][cols] floats: every warp's column sums of dy xhat and dy; then, with a dx_add,
+  // [kLnbWarps][cols] Td: the dx_add row of the warp's next row, copied asynchronously
+  extern __shared__ float lnb_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t total_warps = (int64_t)gridDim.x * kLnbWarps;
   float* sm_g = lnb_smem + (size_t)warp * 2 * cols;
   float* sm_b = sm_g + cols;
+  Td* sm_add = reinterpret_cast<Td*>(lnb_smem + (size_t)kLnbWarps * 2 * cols) + (size_t)warp * cols;
+  // Every lane copies the columns it will add itself, so no other lane waits for the copy. The row
+  // is asked for one row ahead (after the previous row's values were read and used), which leaves
+  // the whole first pass of the row to cover the latency without holding registers for it.
+  auto stage_add = [&](int64_t row) {
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = 128 * i + 4 * lane;
+      if (c < cols) cp_async_small<4 * (int)sizeof(Td)>(sm_add + c, dx_add + row * (int64_t)cols + c);
+    }
+    cp_async_commit();
+  };
 #pragma unroll
   for (int i = 0; i < MAXC; ++i) {
     const int c = 128 * i + 4 * lane;
@@ -379,7 +407,8 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
   // The arithmetic is arranged for the packed two-wide FMA pipe and few operations per element:
   //   xhat = x rs - mu rs,  t = dy xhat,  s1 += dy w,  s2 += t w,  dgamma += t,  dbeta += dy   (pass 1)
   //   dx = dy (w rs) + x A + B  with  A = -rs^2 c2,  B = rs^2 c2 mu - rs c1                       (pass 2)
-  auto process = [&](int64_t row, const Raw4<Tx> (&xr)[MAXC], const Raw4<Tg> (&gr)[MAXC], float2 stat) {
+  auto process = [&](int64_t row, int64_t next_row, const Raw4<Tx> (&xr)[MAXC], const Raw4<Tg> (&gr)[MAXC],
+                     float2 stat) {
     const float mu = stat.x, rs = stat.y;
     const float2 rs2 = make_float2(rs, rs), nmurs2 = make_float2(-mu * rs, -mu * rs);
     float2 s1 = make_float2(0.0f, 0.0f), s2 = make_float2(0.0f, 0.0f);
@@ -413,6 +442,7 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
     const float a = -rs * rs * c2, b = rs * rs * c2 * mu - rs * c1;
     const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
     Td* dr = dx + row * (int64_t)cols;
+    if (dx_add != nullptr) cp_async_wait_all();
 #pragma unroll
     for (int i = 0; i < MAXC; ++i) {
       const int c = 128 * i + 4 * lane;
@@ -429,21 +459,33 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
           o[2 * h] = r.x;
           o[2 * h + 1] = r.y;
         }
+        if (dx_add != nullptr) {  // the gradient that reaches x along the residual branch, added in the same pass
+          float extra[4];
+          Raw4<Td> staged;
+          staged.load_shared(sm_add + c);
+          staged.unpack(extra);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] += extra[j];
+        }
         store_vec4<Td>(dr + c, o);
       }
     }
+    if (dx_add != nullptr && next_row < rows) stage_add(next_row);
   };
 
   int64_t row = (int64_t)blockIdx.x * kLnbWarps + warp;
-  if (row < rows) fetch(row, xa, ga, stat_a);
+  if (row < rows) {
+    fetch(row, xa, ga, stat_a);
+    if (dx_add != nullptr) stage_add(row);
+  }
   while (row < rows) {
     const int64_t row_b = row + total_warps;
     if (row_b < rows) fetch(row_b, xb, gb, stat_b);
-    process(row, xa, ga, stat_a);
+    process(row, row_b, xa, ga, stat_a);
     if (row_b >= rows) break;
     row = row_b + total_warps;
     if (row < rows) fetch(row, xa, ga, stat_a);
-    process(row_b, xb, gb, stat_b);
+    process(row_b, row, xb, gb, stat_b);
   }
 
   // column sums of the CTA: warp order, then one partial row per CTA
@@ -517,8 +559,8 @@ template <typename Tx, typename Tg, typename Tp, typename Td>
 __global__ void __launch_bounds__(kGenThreads)
 layer_norm_backward_dx_generic_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x,
                                       const float* __restrict__ mean, const float* __restrict__ rstd,
-                                      const Tp* __restrict__ gamma, Td* __restrict__ dx, int64_t cols,
-                                      int64_t dy_rs, int64_t x_rs) {
+                                      const Tp* __restrict__ gamma, const Td* __restrict__ dx_add, Td* __restrict__ dx,
+                                      int64_t cols, int64_t dy_rs, int64_t x_rs) {
   __shared__ float red[kGenThreads / 32][2];
   const int64_t row = blockIdx.x;
   const float mu = mean[row], rs = rstd[row];
@@ -533,7 +575,9 @@ layer_norm_backward_dx_generic_kernel(const Tg* __restrict__ dy, const Tx* __res
   for (int64_t c = threadIdx.x; c < cols; c += kGenThreads) {
     const float g = Elem<Tg>::to_f32(dy[row * dy_rs + c]) * (gamma != nullptr ? Elem<Tp>::to_f32(gamma[c]) : 1.0f);
     const float xh = (Elem<Tx>::to_f32(x[row * x_rs + c]) - mu) * rs;
-    dx[row * cols + c] = Elem<Td>::from_f32(rs * (g - c1 - xh * c2));
+    const float extra = dx_add != nullptr ? Elem<Td>::to_f32(dx_add[row * cols + c]) : 0.0f;
+    // a separate rounding for the add: the sum equals (dx as it would be stored in fp32) + dx_add
+    dx[row * cols + c] = Elem<Td>::from_f32(__fadd_rn(__fmul_rn(rs, g - c1 - xh * c2), extra));
   }
 }
 
@@ -583,20 +627,23 @@ int64_t lnb_parts(int64_t rows, int64_t cols) {
 
 template <typename Tx, typename Tg, typename Tp, typename Td>
 int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* mean, const float* rstd,
-                                   const void* gamma, void* dx, void* dgamma, void* dbeta, float* ws, int64_t rows,
-                                   int64_t cols, int64_t dy_rs, int64_t x_rs, cudaStream_t stream) {
+                                   const void* gamma, const void* dx_add, void* dx, void* dgamma, void* dbeta, float* ws,
+                                   int64_t rows, int64_t cols, int64_t dy_rs, int64_t x_rs, cudaStream_t stream) {
   const Tg* gp = static_cast<const Tg*>(dy);
   const Tx* xp = static_cast<const Tx*>(x);
   const Tp* wp = static_cast<const Tp*>(gamma);
   Td* op = static_cast<Td*>(dx);
+  const Td* ap = static_cast<const Td*>(dx_add);
   const int64_t nparts = lnb_parts(rows, cols);
   float* part_g = ws;
   float* part_b = ws + nparts * cols;
   const bool fast = lnb_fast(cols) && dy_rs % 4 == 0 && x_rs % 4 == 0 && aligned_to(dy, 4 * sizeof(Tg)) &&
-                    aligned_to(x, 4 * sizeof(Tx)) && aligned_to(dx, 4 * sizeof(Td));
+                    aligned_to(x, 4 * sizeof(Tx)) && aligned_to(dx, 4 * sizeof(Td)) &&
+                    (dx_add == nullptr || aligned_to(dx_add, 4 * sizeof(Td)));
   if (fast) {
     const int chunks = (int)((cols + 127) / 128);
-    const size_t smem = (size_t)kLnbWarps * 2 * (size_t)cols * sizeof(float);  // at most 64 KiB
+    // at most 64 KiB of column sums and 32 KiB for the staged dx_add rows
+    const size_t smem = (size_t)kLnbWarps * (size_t)cols * (2 * sizeof(float) + (dx_add != nullptr ? sizeof(Td) : 0));
 #define LNB(MAXC)                                                                                              \
   do {                                                                                                         \
     auto kernel = layer_norm_backward_kernel<Tx, Tg, Tp, Td, MAXC>;                                            \
@@ -606,14 +653,14 @@ int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* m
     cudaGetDevice(&dev);                                                                                       \
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {                                                              \
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
-                                           kLnbWarps * 2 * 128 * kLnbMaxChunks * (int)sizeof(float));          \
+                                           kLnbWarps * 128 * kLnbMaxChunks * (int)(2 * sizeof(float) + sizeof(Td))); \
       if (e != cudaSuccess)                                                                                    \
         B200_FAIL(B200_ERR_CUDA, "layer_norm_backward: cannot opt in to shared memory: %s",                    \
                   cudaGetErrorString(e));                                                                      \
       attr_set[dev] = true;                                                                                    \
     }                                                                                                          \
-    kernel<<<(unsigned)nparts, kLnbWarps * 32, smem, stream>>>(gp, xp, mean, rstd, wp, op, part_g, part_b, rows, \
-                                                               (int)cols, dy_rs, x_rs);                        \
+    kernel<<<(unsigned)nparts, kLnbWarps * 32, smem, stream>>>(gp, xp, mean, rstd, wp, ap, op, part_g, part_b,  \
+                                                               rows, (int)cols, dy_rs, x_rs);                  \
   } while (0)
     if (chunks <= 2) LNB(2);
     else if (chunks <= 4) LNB(4);
@@ -626,7 +673,7 @@ int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* m
   } else {
     B200_REQUIRE(rows <= INT32_MAX, B200_ERR_UNSUPPORTED, "layer_norm_backward: too many rows");
     layer_norm_backward_dx_generic_kernel<Tx, Tg, Tp, Td><<<(unsigned)rows, kGenThreads, 0, stream>>>(
-        gp, xp, mean, rstd, wp, op, cols, dy_rs, x_rs);
+        gp, xp, mean, rstd, wp, ap, op, cols, dy_rs, x_rs);
     B200_CHECK_LAUNCH("layer_norm_backward(dx)");
     const int64_t per_slab = (rows + nparts - 1) / nparts;
     const int64_t bx = (cols + 255) / 256;
@@ -727,8 +774,9 @@ extern "C" B200_API size_t b200_layer_norm_backward_workspace_bytes(int64_t rows
 }
 
 extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void* x, const float* mean,
-                                                     const float* rstd, const void* gamma, void* dx, void* dgamma,
-                                                     void* dbeta, void* workspace, size_t workspace_bytes,
+                                                     const float* rstd, const void* gamma, const void* dx_add,
+                                                     void* dx, void* dgamma, void* dbeta, void* workspace,
+                                                     size_t workspace_bytes,
                                                      int64_t rows, int64_t cols, int64_t dy_row_stride,
                                                      int64_t x_row_stride, int32_t x_dtype, int32_t dy_dtype,
                                                      int32_t param_dtype, int32_t dx_dtype, b200_stream_t stream_) {
@@ -738,7 +786,9 @@ extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void*
                B200_ERR_INVALID_ARG, "layer_norm_backward: bad dtype enum");
   B200_REQUIRE(cols > 0 || rows == 0, B200_ERR_INVALID_ARG, "layer_norm_backward: cols must be positive");
   B200_REQUIRE(cols <= INT32_MAX, B200_ERR_UNSUPPORTED, "layer_norm_backward: too many columns");
-  B200_REQUIRE(dy_dtype == dx_dtype, B200_ERR_UNSUPPORTED, "layer_norm_backward: dx takes the dtype of dy");
+  B200_REQUIRE(dy_dtype == dx_dtype || (x_dtype == B200_F32 && dy_dtype == B200_BF16 && dx_dtype == B200_F32),
+               B200_ERR_UNSUPPORTED,
+               "layer_norm_backward: dx takes the dtype of dy (or fp32 for a bf16 dy and an fp32 x)");
   if (rows == 0) {
     // no rows: the parameter gradients are zero
     if (dgamma != nullptr && cudaMemsetAsync(dgamma, 0, (size_t)cols * dtype_size(param_dtype), stream) != cudaSuccess)
@@ -752,16 +802,21 @@ extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void*
   B200_REQUIRE((dy_row_stride >= cols && x_row_stride >= cols) || rows == 1, B200_ERR_INVALID_ARG,
                "layer_norm_backward: row stride smaller than cols");
   B200_REQUIRE(aligned_to(dy, dtype_size(dy_dtype)) && aligned_to(x, dtype_size(x_dtype)) &&
-                   aligned_to(dx, dtype_size(dx_dtype)),
+                   aligned_to(dx, dtype_size(dx_dtype)) && aligned_to(dx_add, dtype_size(dx_dtype)),
                B200_ERR_ALIGNMENT, "layer_norm_backward: pointer not element aligned");
   const size_t need = b200_layer_norm_backward_workspace_bytes(rows, cols);
   B200_REQUIRE(workspace != nullptr && workspace_bytes >= need, B200_ERR_WORKSPACE,
                "layer_norm_backward: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
   B200_REQUIRE(aligned_to(workspace, 16), B200_ERR_ALIGNMENT, "layer_norm_backward: workspace not 16-byte aligned");
   float* ws = static_cast<float*>(workspace);
-#define LNB_CASE(TX, TG, TP) \
-  return launch_layer_norm_backward<TX, TG, TP, TG>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, rows, cols, \
+#define LNB_CASE_D(TX, TG, TP, TD)                                                                                  \
+  return launch_layer_norm_backward<TX, TG, TP, TD>(dy, x, mean, rstd, gamma, dx_add, dx, dgamma, dbeta, ws, rows, cols, \
                                                     dy_row_stride, x_row_stride, stream)
+#define LNB_CASE(TX, TG, TP) LNB_CASE_D(TX, TG, TP, TG)
+  if (dx_dtype != dy_dtype) {  // fp32 x, bf16 dy, fp32 dx: the gradient of a bf16 consumer of an fp32 stream
+    if (param_dtype == B200_F32) LNB_CASE_D(float, bf16, float, float);
+    LNB_CASE_D(float, bf16, bf16, float);
+  }
   const int key = x_dtype * 4 + dy_dtype * 2 + param_dtype;
   switch (key) {
     case 0: LNB_CASE(float, float, float);
@@ -774,6 +829,7 @@ extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void*
     default: LNB_CASE(bf16, bf16, bf16);
   }
 #undef LNB_CASE
+#undef LNB_CASE_D
 }
 
 extern "C" B200_API size_t b200_sum_rows_workspace_bytes(int64_t rows, int64_t cols, int32_t in_dtype) {

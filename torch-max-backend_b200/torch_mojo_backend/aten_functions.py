@@ -268,7 +268,8 @@ def aten__softmax_backward_data(grad_output, output, dim, input_dtype):
 # native_layer_norm_backward(Tensor grad_out, Tensor input, SymInt[] normalized_shape, Tensor mean,
 #   Tensor rstd, Tensor? weight, Tensor? bias, bool[3] output_mask) -> (Tensor, Tensor, Tensor)
 @map_to(aten.native_layer_norm_backward)
-def aten_native_layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask):
+def aten_native_layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask,
+                                    *, dx_add=None, dx_dtype=None):
     _require_kernel_dtype("aten.native_layer_norm_backward", grad_out, input, weight)
     norm = 1
     for d in normalized_shape:
@@ -282,7 +283,7 @@ def aten_native_layer_norm_backward(grad_out, input, normalized_shape, mean, rst
         grad_out = grad_out.reshape(input.shape)
     dx, dgamma, dbeta = ops.layer_norm_backward(
         grad_out, input, mean, rstd, w, bool(output_mask[1]) and weight is not None,
-        bool(output_mask[2]) and bias is not None,
+        bool(output_mask[2]) and bias is not None, dx_add, dx_dtype,
     )
     if dx.dtype != input.dtype:
         dx = dx.to(input.dtype)
@@ -735,6 +736,17 @@ def fused_layer_norm_with_statistics(input, normalized_shape, weight, bias, eps,
 
 
 @_count_calls
+def fused_layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask,
+                              *, dx_add=None, dx_dtype=None):
+    """native_layer_norm_backward whose grad_out was a bf16 tensor widened to fp32 just before it
+    (`dx_dtype`: the kernel reads the bf16 tensor and writes fp32), and / or whose dx only fed an add
+    with the gradient of the residual branch (`dx_add`: added before dx is stored)."""
+    return aten_native_layer_norm_backward(
+        grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask, dx_add=dx_add, dx_dtype=dx_dtype
+    )
+
+
+@_count_calls
 def fused_gemm(a, b, bias, residual, *, alpha, beta, epilogue, out_dtype, out_shape):
     """addmm / mm followed by (views,) gelu, an fp32 cast and/or a residual add, as one GEMM:
     out = act(alpha * a @ b + beta * bias) + residual, stored as `out_dtype`, viewed as `out_shape`."""
@@ -771,7 +783,7 @@ def fused_masked_softmax(x, mask, *, fill, scale, invert):
     return ops.softmax(masked)
 
 
-for _fused in (fused_layer_norm, fused_layer_norm_with_statistics, fused_gemm, contiguous_or_alias, fused_masked_softmax,
+for _fused in (fused_layer_norm, fused_layer_norm_with_statistics, fused_layer_norm_backward, fused_gemm, contiguous_or_alias, fused_masked_softmax,
                fused_embedding_sum):
     MAPPING_TORCH_ATEN_TO_MOJO[_fused] = _fused
 

@@ -54,7 +54,7 @@ _lib.define("gelu_backward(Tensor dy, Tensor x, str approximate='none') -> Tenso
 _lib.define("softmax_backward(Tensor dy, Tensor y, float scale=1.0, ScalarType? out_dtype=None) -> Tensor")
 _lib.define(
     "layer_norm_backward(Tensor dy, Tensor x, Tensor mean, Tensor rstd, Tensor? weight, bool want_weight=True,"
-    " bool want_bias=True) -> (Tensor, Tensor?, Tensor?)"
+    " bool want_bias=True, Tensor? dx_add=None, ScalarType? dx_dtype=None) -> (Tensor, Tensor?, Tensor?)"
 )
 _lib.define("sum_rows(Tensor x, ScalarType? out_dtype=None) -> Tensor")
 _lib.define("argmax(Tensor x) -> Tensor")
@@ -298,10 +298,17 @@ def _softmax_backward_meta(dy, y, scale=1.0, out_dtype=None):
     return torch.empty(y.shape, dtype=out_dtype or y.dtype, device=y.device)
 
 
-def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_bias=True):
-    device = native.require_cuda("layer_norm_backward", dy, x, mean, rstd, weight)
+def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None, dx_dtype=None):
+    """dx (+ dx_add, the gradient that reaches x along a residual branch), dgamma, dbeta. dx_dtype
+    defaults to dy's dtype; float32 is also accepted for a bfloat16 dy and a float32 x."""
+    device = native.require_cuda("layer_norm_backward", dy, x, mean, rstd, weight, dx_add)
     if dy.shape != x.shape:
         raise RuntimeError(f"layer_norm_backward: dy {tuple(dy.shape)} and x {tuple(x.shape)} differ")
+    dx_dtype = dx_dtype or dy.dtype
+    if dx_add is not None and (dx_add.shape != x.shape or dx_add.dtype != dx_dtype):
+        raise RuntimeError(
+            f"layer_norm_backward: dx_add {tuple(dx_add.shape)} {dx_add.dtype} is not a {tuple(x.shape)} {dx_dtype} tensor"
+        )
     cols = weight.numel() if weight is not None else x.shape[-1]
     if cols == 0 or x.numel() % cols != 0:
         raise RuntimeError(f"layer_norm_backward: {tuple(x.shape)} is not rows of {cols} normalised elements")
@@ -316,7 +323,8 @@ def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_
         raise RuntimeError(f"layer_norm_backward: mean / rstd have {mean_c.numel()} / {rstd_c.numel()} entries for {rows} rows")
     param_dtype = weight.dtype if weight is not None else x.dtype
     wc = None if weight is None else weight.reshape(-1).contiguous()
-    dx = torch.empty(x.shape, dtype=dy.dtype, device=device)
+    dx = torch.empty(x.shape, dtype=dx_dtype, device=device)
+    extra = None if dx_add is None else dx_add.contiguous()
     dgamma = torch.empty(cols, dtype=param_dtype, device=device) if want_weight else None
     dbeta = torch.empty(cols, dtype=param_dtype, device=device) if want_bias else None
     lib = native.lib()
@@ -325,25 +333,25 @@ def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_
     start = _prof_begin(device)
     with torch.cuda.device(device):
         status = lib.b200_layer_norm_backward(
-            g2.data_ptr(), x2.data_ptr(), mean_c.data_ptr(), rstd_c.data_ptr(), _ptr(wc), dx.data_ptr(),
+            g2.data_ptr(), x2.data_ptr(), mean_c.data_ptr(), rstd_c.data_ptr(), _ptr(wc), _ptr(extra), dx.data_ptr(),
             _ptr(dgamma), _ptr(dbeta), ws.data_ptr(), ws_bytes, rows, cols, g2.stride(0) if rows > 1 else cols,
             x2.stride(0) if rows > 1 else cols, native.dtype_enum(x.dtype), native.dtype_enum(dy.dtype),
-            native.dtype_enum(param_dtype), native.dtype_enum(dy.dtype), native.current_stream(device),
+            native.dtype_enum(param_dtype), native.dtype_enum(dx_dtype), native.current_stream(device),
         )
     native.check("layer_norm_backward", status)
-    _launched(device, start, "layer_norm_backward", 0.0, _nbytes(g2, x2, dx))
+    _launched(device, start, "layer_norm_backward", 0.0, _nbytes(g2, x2, dx) + (_nbytes(extra) if extra is not None else 0))
     if weight is not None and dgamma is not None:
         dgamma = dgamma.reshape(weight.shape)
         dbeta = dbeta.reshape(weight.shape) if dbeta is not None else None
     return dx, dgamma, dbeta
 
 
-def _layer_norm_backward_meta(dy, x, mean, rstd, weight, want_weight=True, want_bias=True):
+def _layer_norm_backward_meta(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None, dx_dtype=None):
     cols = weight.numel() if weight is not None else x.shape[-1]
     shape = weight.shape if weight is not None else (cols,)
     param_dtype = weight.dtype if weight is not None else x.dtype
     return (
-        torch.empty(x.shape, dtype=dy.dtype, device=x.device),
+        torch.empty(x.shape, dtype=dx_dtype or dy.dtype, device=x.device),
         torch.empty(shape, dtype=param_dtype, device=x.device) if want_weight else None,
         torch.empty(shape, dtype=param_dtype, device=x.device) if want_bias else None,
     )

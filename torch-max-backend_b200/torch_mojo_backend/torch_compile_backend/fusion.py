@@ -10,6 +10,9 @@ epilogues:
         => one GEMM whose epilogue applies bias, GELU, the residual add and the output dtype to
            the fp32 accumulator (an fp32 result is stored as computed, without the intermediate
            bf16 rounding the unfused graph would do)
+  * `[_to_copy(bf16 -> float32)] -> native_layer_norm_backward -> getitem[0] -> [add(residual grad, .)]`
+        => one LayerNorm backward that reads the bf16 gradient and adds the residual branch's
+           gradient before it stores dx (the backward of a pre-norm transformer block)
   * `sdpa -> getitem[0] -> transpose -> clone(contiguous)`        => no copy: the attention kernel
         already writes its output in the [B, T, H, D] order that `clone` would produce
   * `[mul | div (scalar)] -> masked_fill(mask, value) | where(keep, ., value) -> _softmax(-1)`
@@ -88,11 +91,16 @@ def _plain_cast(node) -> torch.dtype | None:
     """dtype of a `_to_copy` that only changes dtype, else None."""
     if not _is_call(node, aten._to_copy.default):
         return None
+    source = _val(node.args[0])
     for key, value in node.kwargs.items():
-        if key == "dtype":
+        if key == "dtype" or value in (None, False):
             continue
-        if value not in (None, False):
-            return None
+        # autograd spells the layout and the device out; they change nothing when they are the input's
+        if key == "layout" and value == torch.strided:
+            continue
+        if key == "device" and isinstance(source, torch.Tensor) and torch.device(value) == source.device:
+            continue
+        return None
     return node.kwargs.get("dtype")
 
 
@@ -163,6 +171,67 @@ def _fuse_layer_norm_with_statistics(graph) -> int:
         for index in (1, 2):
             if index in items:
                 items[index].args = (new, index)
+        count += 1
+    return count
+
+
+def _fuse_layer_norm_backward(graph) -> int:
+    """`_to_copy(bf16 -> fp32) -> native_layer_norm_backward -> getitem[0] -> add(residual gradient, .)`
+    as one launch: the kernel reads the bf16 gradient, and adds the gradient of the residual branch
+    before it stores dx. Either half of the chain is folded on its own when the other is absent."""
+    order = {node: i for i, node in enumerate(graph.nodes)}
+    count = 0
+    for node in list(graph.nodes):
+        if not _is_call(node, aten.native_layer_norm_backward.default) or node.kwargs:
+            continue
+        grad, x = node.args[0], node.args[1]
+        vg, vx = _val(grad), _val(x)
+        if not (isinstance(vg, torch.Tensor) and isinstance(vx, torch.Tensor) and _static_tensor(x)):
+            continue
+        if vg.dtype != torch.float32 or vx.dtype != torch.float32 or not node.args[7][0]:
+            continue
+        kwargs = {}
+        source = grad
+        while _is_call(source, *VIEW_OPS):
+            source = source.args[0]
+        narrow = source.args[0] if _plain_cast(source) == torch.float32 else None
+        if (
+            narrow is not None
+            and source is grad  # views between the cast and the kernel would have to be replayed
+            and len(grad.users) == 1
+            and isinstance(_val(narrow), torch.Tensor)
+            and _val(narrow).dtype == torch.bfloat16
+        ):
+            grad = narrow
+            kwargs["dx_dtype"] = torch.float32
+        dx = next((u for u in node.users if _is_call(u, operator.getitem) and u.args[1] == 0), None)
+        add = _only_user(dx) if dx is not None else None
+        target = None
+        if (
+            _is_call(add, aten.add.Tensor)
+            and add.kwargs.get("alpha", 1) == 1
+            and len(add.args) == 2
+            and all(isinstance(a, torch.fx.Node) for a in add.args)
+        ):
+            other = add.args[1] if add.args[0] is dx else add.args[0]
+            vo = _val(other)
+            if (
+                other is not dx
+                and isinstance(vo, torch.Tensor)
+                and vo.dtype == torch.float32
+                and tuple(vo.shape) == tuple(vx.shape) == tuple(_val(add).shape)
+                and order[other] < order[node]  # already computed where the kernel runs
+            ):
+                kwargs["dx_add"] = other
+                target = add
+        if not kwargs:
+            continue
+        with graph.inserting_after(node):
+            new = graph.call_function(af.fused_layer_norm_backward, args=(grad,) + tuple(node.args[1:]), kwargs=kwargs)
+        new.meta = dict(node.meta)
+        node.replace_all_uses_with(new)
+        if target is not None:
+            target.replace_all_uses_with(dx)
         count += 1
     return count
 
@@ -371,6 +440,7 @@ def fuse_graph(gm: torch.fx.GraphModule) -> dict[str, int]:
     graph = gm.graph
     stats = {
         "layer_norm_cast": _fuse_layer_norm(graph) + _fuse_layer_norm_with_statistics(graph),
+        "layer_norm_backward": _fuse_layer_norm_backward(graph),
         "gemm_epilogue": _fuse_gemm_epilogues(graph),
         "attention_output_copy": _drop_attention_output_copies(graph),
         "masked_softmax": _fuse_masked_softmax(graph),
