@@ -25,7 +25,8 @@ def _reset(reset_compiler):
 
 def test_public_surface():
     assert set(torch_mojo_backend.__all__) == {
-        "mojo_backend", "get_accelerators", "MAPPING_TORCH_ATEN_TO_MOJO", "MojoCompilerError"}
+        "mojo_backend", "get_accelerators", "MAPPING_TORCH_ATEN_TO_MOJO", "MojoCompilerError",
+            "make_torch_op_from_mojo"}
     assert torch_mojo_backend.get_accelerators() == []  # no CUDA device here, and no CPU device is offered
     for op in (aten.mm, aten.addmm, aten.bmm, aten._softmax, aten.native_layer_norm, aten.gelu, aten.sum,
                aten.mean, aten.amax, aten._scaled_dot_product_flash_attention, operator.getitem):
