@@ -246,6 +246,16 @@ def test_gemm_operands_with_unaligned_pitch_stay_on_the_tensor_cores(ops):
         ops.gemm(dl, w, None, None, 1.0, 1.0, 0, torch.float32)
     torch.cuda.synchronize()
     assert (time.perf_counter() - t0) / 3 < 5e-3, "52 GFLOP must take well under the CUDA-core kernel's ~15 ms"
+    # The re-pitched copy is shared by the two GEMMs (it lives on the tensor both operands are views of)
+    # and is dropped when that tensor is written to.
+    kept = dl._b200_padded_pitch[1]
+    assert kept.stride(0) % 8 == 0 and torch.equal(kept, dl)
+    ops.gemm(dl.t(), x, None, None, 1.0, 1.0, 0, torch.float32)
+    assert dl._b200_padded_pitch[1] is kept
+    dl.mul_(2.0)
+    dx2 = ops.gemm(dl, w, None, None, 1.0, 1.0, 0, torch.float32)
+    assert dl._b200_padded_pitch[1] is not kept
+    assert_parity(dx2, 2.0 * want_dx.float(), bf16=False, scale=float(want_dx.abs().max()) * 40)
 
 
 def test_batched_gemm_with_transposed_a(ops):
@@ -316,6 +326,34 @@ def test_fused_attention_backward_on_fused_qkv_views(ops):
     dq, dk, dv = ops.sdpa_backward(d_out.cuda(), qc, kc, vc, o, lse, True)
     for got, ref, name in zip((dq, dk, dv), ref_ops.sdpa_backward(d_out, q, k, v, True), "qkv"):
         assert_parity(got, ref, bf16=True, what=f"d{name}")
+
+
+def test_self_attention_gradients_share_one_buffer_and_their_cat_is_a_view(ops):
+    """Equal query and key lengths: dq, dk, dv are slices of one [B, T, 3, H, 64] buffer, so the
+    `cat` that rebuilds a fused QKV projection's output gradient returns that buffer without a copy."""
+    from torch_mojo_backend import aten_functions as af
+    from torch_mojo_backend import native
+
+    B, H, T = 2, 4, 256
+    q, k, v, d_out = (gen((B, H, T, 64), torch.bfloat16, 90 + i, std=0.8).cuda() for i in range(4))
+    o, lse = ops.sdpa(q, k, v, True)
+    dq, dk, dv = ops.sdpa_backward(d_out, q, k, v, o, lse, True)
+    flat = [t.transpose(1, 2).reshape(B, T, H * 64) for t in (dq, dk, dv)]
+    before = native.launch_count
+    joined = af.aten_cat(flat, 2)
+    assert native.launch_count == before, "no copy kernel"
+    assert joined.is_contiguous() and joined.shape == (B, T, 3 * H * 64) and joined.data_ptr() == dq.data_ptr()
+    assert torch.equal(joined, torch.cat(flat, 2))
+    # any other order or subset is an ordinary concatenation
+    swapped = af.aten_cat([flat[1], flat[0], flat[2]], 2)
+    assert swapped.data_ptr() != dq.data_ptr() and torch.equal(swapped, torch.cat([flat[1], flat[0], flat[2]], 2))
+    pair = af.aten_cat(flat[:2], 2)
+    assert pair.data_ptr() != dq.data_ptr() and torch.equal(pair, torch.cat(flat[:2], 2))
+    # cross attention keeps separate buffers
+    k2, v2 = (gen((B, H, 128, 64), torch.bfloat16, 95 + i, std=0.8).cuda() for i in range(2))
+    o2, lse2 = ops.sdpa(q, k2, v2, False)
+    g = ops.sdpa_backward(d_out, q, k2, v2, o2, lse2, False)
+    assert g[0]._base is not g[1]._base
 
 
 @pytest.mark.parametrize("attention", ["sdpa", "masked_softmax"])

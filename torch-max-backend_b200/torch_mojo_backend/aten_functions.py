@@ -849,7 +849,35 @@ def aten_cat(tensors, dim=0):
     tensors = list(tensors)
     if len({t.dtype for t in tensors}) != 1 or any(t.dim() == 0 for t in tensors):
         return torch.cat(tensors, dim)  # type promotion across inputs: shape glue
+    whole = _tiles_of_one_buffer(tensors, dim)
+    if whole is not None:
+        return whole
     return ops.cat(tensors, dim)
+
+
+def _tiles_of_one_buffer(tensors, dim):
+    """The concatenation as a view, when the inputs are views of ONE buffer that they tile exactly and
+    in order along `dim` (the dq | dk | dv slices of the packed gradient an attention backward writes:
+    their `cat` is that buffer). None when a copy is needed."""
+    first = tensors[0]
+    base = first._base
+    if base is None or len(tensors) < 2 or not base.is_contiguous():
+        return None
+    dim = dim % first.dim()
+    strides, offset, total = first.stride(), first.storage_offset(), 0
+    for t in tensors:
+        if t._base is not base or t.stride() != strides or t.storage_offset() != offset or t.dim() != first.dim():
+            return None
+        if any(t.shape[d] != first.shape[d] for d in range(first.dim()) if d != dim):
+            return None
+        offset += t.shape[dim] * strides[dim]
+        total += t.numel()
+    if total != base.numel() or first.storage_offset() != base.storage_offset():
+        return None
+    shape = list(first.shape)
+    shape[dim] = sum(t.shape[dim] for t in tensors)
+    out = first.as_strided(shape, strides, first.storage_offset())
+    return out if out.is_contiguous() else None
 
 
 def _view_or_copy(x, size):

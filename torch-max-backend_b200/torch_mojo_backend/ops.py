@@ -463,9 +463,20 @@ def _tma_pitch(t):
     if t.dim() != 2 or t.dtype != torch.bfloat16 or min(t.shape) < 64 or t.numel() < (1 << 22):
         return t
     if t.stride(1) == 1 and t.stride(0) % 8 != 0:
+        # The copy is kept on the tensor the operand is a view of, for as long as that tensor lives and
+        # is not written to: the data and the weight gradient of a layer read the same gradient.
+        root = t._base if t._base is not None else t
+        key = (t.storage_offset(), tuple(t.shape), t.stride(), root._version)
+        kept = getattr(root, "_b200_padded_pitch", None)
+        if kept is not None and kept[0] == key:
+            return kept[1]
         rows, cols = t.shape
         padded = torch.empty((rows, (cols + 7) // 8 * 8), dtype=t.dtype, device=t.device)[:, :cols]
         padded.copy_(t)
+        try:
+            root._b200_padded_pitch = (key, padded)
+        except (AttributeError, RuntimeError):  # a tensor subclass without attributes: copy again next time
+            pass
         return padded
     if t.stride(0) == 1 and t.stride(1) % 8 != 0:
         return _tma_pitch(t.t()).t()
@@ -601,9 +612,7 @@ def _sdpa_backward_cuda(d_out, q, k, v, o, lse, causal=False, scale=None):
     lse_c = lse.reshape(B, H, -1)[:, :, :T].float().contiguous()
     # Gradients laid out [B, T, H, D] in memory (returned as their [B, H, T, D] views), like the forward's
     # output: the `transpose(1, 2)` + `contiguous` that follows in a projection's backward is then a view.
-    dq = torch.empty((B, T, H, D), dtype=q.dtype, device=device).transpose(1, 2)
-    dk = torch.empty((B, S, H, D), dtype=q.dtype, device=device).transpose(1, 2)
-    dv = torch.empty((B, S, H, D), dtype=q.dtype, device=device).transpose(1, 2)
+    dq, dk, dv = _sdpa_gradient_buffers(B, H, T, S, D, q.dtype, device)
     lib = native.lib()
 
     def args_for(b0, b1):
@@ -634,14 +643,23 @@ def _sdpa_backward_cuda(d_out, q, k, v, o, lse, causal=False, scale=None):
     return dq, dk, dv
 
 
+def _sdpa_gradient_buffers(B, H, T, S, D, dtype, device):
+    """dq, dk, dv as [B, H, T, D] views of memory laid out [B, T, H, D]. For self-attention the three
+    share one [B, T, 3, H, D] buffer: the gradient of a fused QKV projection's output, which the graph
+    builds with `cat([dq, dk, dv], -1)`, is then that buffer and the concatenation copies nothing."""
+    if T == S:
+        packed = torch.empty((B, T, 3, H, D), dtype=dtype, device=device)
+        return tuple(packed[:, :, i].transpose(1, 2) for i in range(3))
+    return (
+        torch.empty((B, T, H, D), dtype=dtype, device=device).transpose(1, 2),
+        torch.empty((B, S, H, D), dtype=dtype, device=device).transpose(1, 2),
+        torch.empty((B, S, H, D), dtype=dtype, device=device).transpose(1, 2),
+    )
+
+
 def _sdpa_backward_meta(d_out, q, k, v, o, lse, causal=False, scale=None):
     B, H, T, D = q.shape
-    S = k.shape[2]
-    return (
-        torch.empty((B, T, H, D), dtype=q.dtype, device=q.device).transpose(1, 2),
-        torch.empty((B, S, H, D), dtype=k.dtype, device=k.device).transpose(1, 2),
-        torch.empty((B, S, H, D), dtype=v.dtype, device=v.device).transpose(1, 2),
-    )
+    return _sdpa_gradient_buffers(B, H, T, k.shape[2], D, q.dtype, q.device)
 
 
 # ---- embedding (+ second table) ---------------------------------------------------------------
