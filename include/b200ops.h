@@ -161,7 +161,11 @@ B200_API int32_t b200_softmax_backward(const void* dy, const void* y, void* dx, 
  * param_dtype; dx is contiguous and has the dtype of dy, or fp32 when x is fp32 and dy bf16 (the
  * gradient a bf16 consumer sends back into an fp32 stream: no widening pass before the kernel).
  * dx_add may be NULL; otherwise it is a contiguous [rows, cols] tensor of dx's dtype that is added to
- * dx in the same pass (the gradient that reaches x along a residual branch). The workspace holds the
+ * dx in the same pass (the gradient that reaches x along a residual branch). dx_cast may be NULL;
+ * otherwise (dx fp32 only) it receives the same values rounded to bf16, contiguous: the operand of the
+ * gradient GEMMs of the layer that produced x. dx_sum may be NULL; otherwise it receives, in
+ * dx_sum_dtype, the column sums over the rows of dx_cast when that is given and of dx as stored
+ * otherwise (that layer's bias gradient), fp32 accumulation in a fixed order. The workspace holds the
  * per-CTA column sums (b200_layer_norm_backward_workspace_bytes, 16-byte aligned).
  * Replaces: the decomposition of aten.native_layer_norm_backward
  * (torch_mojo_backend/aten_functions.py:2871) and the reference's eager kernels
@@ -171,11 +175,12 @@ B200_API int32_t b200_softmax_backward(const void* dy, const void* y, void* dx, 
 B200_API size_t b200_layer_norm_backward_workspace_bytes(int64_t rows, int64_t cols);
 B200_API int32_t b200_layer_norm_backward(const void* dy, const void* x, const float* mean,
                                  const float* rstd, const void* gamma, const void* dx_add,
-                                 void* dx, void* dgamma, void* dbeta, void* workspace,
-                                 size_t workspace_bytes,
+                                 void* dx, void* dgamma, void* dbeta, void* dx_cast, void* dx_sum,
+                                 void* workspace, size_t workspace_bytes,
                                  int64_t rows, int64_t cols, int64_t dy_row_stride,
                                  int64_t x_row_stride, int32_t x_dtype, int32_t dy_dtype,
-                                 int32_t param_dtype, int32_t dx_dtype, b200_stream_t stream);
+                                 int32_t param_dtype, int32_t dx_dtype, int32_t dx_sum_dtype,
+                                 b200_stream_t stream);
 
 /* y[cols] = sum over the rows of x[rows, cols] (unit column stride): the bias gradient of a linear
  * layer, aten.sum(dy, [0]). fp32 accumulation in a fixed order; workspace as above.

@@ -144,6 +144,49 @@ def test_layer_norm_backward_widening_with_residual_gradient(ops, shape, param_d
     assert torch.equal(dx, plain + extra.cuda()), "dx_add is added to the fp32 value that would have been stored"
 
 
+@pytest.mark.parametrize("shape", [(8192, 1600), (4096, 768), (37, 40), (5, 7), (3, 5000), (700, 2048)])
+@pytest.mark.parametrize("with_add", [False, True])
+def test_layer_norm_backward_with_bf16_copy_and_column_sums(ops, shape, with_add):
+    """The fp32 dx, its bf16 copy and the copy's column sums from one launch: the copy is the rounded dx
+    bit for bit, and the sums are those of the rounded values (what `dx.to(bf16).sum(0)` would give)."""
+    cols = shape[-1]
+    x, dy = gen(shape, torch.float32, 100), gen(shape, torch.bfloat16, 101)
+    extra = gen(shape, torch.float32, 102) if with_add else None
+    w = gen((cols,), torch.float32, 103, mean=1.0, std=0.2)
+    _, mean, rstd = ref_ops.layer_norm(x, [cols], w, None, 1e-5)
+    dev = (dy.cuda(), x.cuda(), mean.cuda(), rstd.cuda(), w.cuda())
+    add = extra.cuda() if with_add else None
+    dx, dgamma, dbeta, narrow, sums = ops.layer_norm_backward_with_copy(
+        *dev, True, True, add, torch.float32, True, torch.bfloat16)
+    plain = ops.layer_norm_backward(*dev, True, True, add, torch.float32)
+    assert torch.equal(dx, plain[0]) and torch.equal(dgamma, plain[1]) and torch.equal(dbeta, plain[2])
+    assert narrow.dtype == torch.bfloat16 and torch.equal(narrow, dx.to(torch.bfloat16))
+    want = narrow.double().sum(0).cpu()
+    assert sums.dtype == torch.bfloat16 and sums.shape == (cols,)
+    assert_parity(sums, want.float(), bf16=True, scale=max(float(want.abs().max()), 1.0), what="column sums")
+    fp32_sums = ops.layer_norm_backward_with_copy(*dev, False, False, add, torch.float32, True, torch.float32)[4]
+    assert_parity(fp32_sums, want.float(), bf16=False, scale=max(float(want.abs().max()), 1.0) * 4, what="fp32 column sums")
+    again = ops.layer_norm_backward_with_copy(*dev, True, True, add, torch.float32, True, torch.bfloat16)
+    assert torch.equal(again[4], sums) and torch.equal(again[3], narrow), "fixed-order sums: bit-identical reruns"
+    # sums without the copy: over dx as stored
+    only = ops.layer_norm_backward_with_copy(*dev, False, False, add, torch.float32, False, torch.float32)
+    assert only[3] is None
+    want32 = dx.double().sum(0).cpu()
+    assert_parity(only[4], want32.float(), bf16=False, scale=max(float(want32.abs().max()), 1.0) * 4, what="sums of fp32 dx")
+
+
+def test_layer_norm_backward_copy_needs_an_fp32_dx(ops):
+    x, dy = gen((64, 256), torch.bfloat16, 104).cuda(), gen((64, 256), torch.bfloat16, 105).cuda()
+    mean, rstd = torch.zeros(64, device="cuda"), torch.ones(64, device="cuda")
+    with pytest.raises(RuntimeError, match="float32 dx"):
+        ops.layer_norm_backward_with_copy(dy, x, mean, rstd, None, False, False, None, None, True, None)
+    # bf16 dx with sums: of the stored (rounded) values
+    dx, _, _, narrow, sums = ops.layer_norm_backward_with_copy(dy, x, mean, rstd, None, False, False, None, None, False,
+                                                              torch.float32)
+    assert narrow is None
+    assert_parity(sums, dx.double().sum(0).float().cpu(), bf16=False, scale=64.0)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_layer_norm_backward_residual_gradient_same_dtype_and_errors(ops, dtype):
     x, dy, extra = gen((300, 1600), dtype, 74), gen((300, 1600), dtype, 75), gen((300, 1600), dtype, 76)

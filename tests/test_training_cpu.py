@@ -63,6 +63,17 @@ class _TrainingStandIns(_StandIns):
         )
 
     @staticmethod
+    def layer_norm_backward_with_copy(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None,
+                                      dx_dtype=None, want_cast=False, sum_dtype=None):
+        dx, dg, db = _TrainingStandIns.layer_norm_backward(dy, x, mean, rstd, weight, want_weight, want_bias, dx_add, dx_dtype)
+        _StandIns._record(x, ("layer_norm_backward_with_copy", want_cast, sum_dtype))
+        assert not want_cast or dx.dtype == torch.float32
+        narrow = dx.to(torch.bfloat16) if want_cast else None
+        summed = narrow if narrow is not None else dx
+        sums = summed.reshape(-1, x.shape[-1]).float().sum(0).to(sum_dtype) if sum_dtype is not None else None
+        return dx, dg, db, narrow, sums
+
+    @staticmethod
     def sum_rows(x, out_dtype=None):
         _StandIns._record(x, ("sum_rows",))
         return x.float().reshape(-1, x.shape[-1]).sum(0).to(out_dtype or x.dtype)
@@ -145,6 +156,10 @@ def test_bf16_policy_training_graph_folds_the_layer_norm_cast(training_stand_ins
     kinds = [c for c in training_stand_ins.calls if c[0] == "layer_norm_backward"]
     assert len(kinds) == 5 and all(c[4] == torch.float32 for c in kinds)
     assert sum(1 for c in kinds if c[3]) == 4
+    # all five residual-stream gradients also leave the launch as bf16: four feed a projection's backward,
+    # one the embedding's
+    copies = [c for c in training_stand_ins.calls if c[0] == "layer_norm_backward_with_copy"]
+    assert sum(1 for c in copies if c[1] and c[2] is None) == 5
     for name in want:
         scale = float(want[name].float().abs().max())
         err = float((got[name].float() - want[name].float()).abs().max())

@@ -307,6 +307,27 @@ def main():
                 us, rot = time_case(make, lambda t: ops.layer_norm_backward(t[0], t[1], t[2], t[3], t[4], True, True, t[5], f32),
                                     nbytes, args.iters, use_graph)
                 report(name, us, rot, nbytes=nbytes)
+            # ... and with the bf16 copy of dx and its column sums (the next projection's operand and bias gradient)
+            name = f"layer_norm_backward x fp32, dy bf16, dx fp32 + residual gradient + bf16 copy + sums {rows}x1600"
+            if keep(name):
+                nbytes = rows * 1600 * (4 + 2 + 4 + 4 + 2) + 8 * rows
+                make = lambda i, rows=rows: (randn((rows, 1600), bf), randn((rows, 1600), f32), randn((rows,), f32),
+                                             randn((rows,), f32).abs() + 0.5, randn((1600,), f32, 0.02, 1.0),
+                                             randn((rows, 1600), f32))
+                us, rot = time_case(make, lambda t: ops.layer_norm_backward_with_copy(t[0], t[1], t[2], t[3], t[4], True, True,
+                                                                                     t[5], f32, True, bf),
+                                    nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
+            name = f"layer_norm_backward x fp32, dy bf16, dx fp32 + residual gradient + bf16 copy {rows}x1600"
+            if keep(name):
+                nbytes = rows * 1600 * (4 + 2 + 4 + 4 + 2) + 8 * rows
+                make = lambda i, rows=rows: (randn((rows, 1600), bf), randn((rows, 1600), f32), randn((rows,), f32),
+                                             randn((rows,), f32).abs() + 0.5, randn((1600,), f32, 0.02, 1.0),
+                                             randn((rows, 1600), f32))
+                us, rot = time_case(make, lambda t: ops.layer_norm_backward_with_copy(t[0], t[1], t[2], t[3], t[4], True, True,
+                                                                                     t[5], f32, True, None),
+                                    nbytes, args.iters, use_graph)
+                report(name, us, rot, nbytes=nbytes)
             name = f"layer_norm_backward fp32 {rows}x1600"
             if keep(name):
                 nbytes = rows * 1600 * 12 + 8 * rows

@@ -347,16 +347,20 @@ template <typename Tx, typename Tg, typename Tp, typename Td, int MAXC>
 __global__ void __launch_bounds__(kLnbWarps * 32, kLnbCtasPerSm)
 layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, const float* __restrict__ mean,
                            const float* __restrict__ rstd, const Tp* __restrict__ gamma, const Td* __restrict__ dx_add,
-                           Td* __restrict__ dx, float* __restrict__ part_g, float* __restrict__ part_b, int64_t rows,
-                           int cols, int64_t dy_rs, int64_t x_rs) {
-  // [kLnbWarps][2][cols] floats: every warp's column sums of dy xhat and dy; then, with a dx_add,
-  // [kLnbWarps][cols] Td: the dx_add row of the warp's next row, copied asynchronously
+                           Td* __restrict__ dx, __nv_bfloat16* __restrict__ dx_cast, float* __restrict__ part_g,
+                           float* __restrict__ part_b, float* __restrict__ part_s, int64_t rows, int cols, int64_t dy_rs,
+                           int64_t x_rs) {
+  // [kLnbWarps][2][cols] floats: every warp's column sums of dy xhat and dy; with a part_s,
+  // [kLnbWarps][cols] floats: its column sums of dx; with a dx_add, [kLnbWarps][cols] Td: the dx_add
+  // row of the warp's next row, copied asynchronously
   extern __shared__ float lnb_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t total_warps = (int64_t)gridDim.x * kLnbWarps;
   float* sm_g = lnb_smem + (size_t)warp * 2 * cols;
   float* sm_b = sm_g + cols;
-  Td* sm_add = reinterpret_cast<Td*>(lnb_smem + (size_t)kLnbWarps * 2 * cols) + (size_t)warp * cols;
+  float* sm_sums = lnb_smem + (size_t)kLnbWarps * 2 * cols;  // all warps' strips of dx column sums
+  float* sm_s = sm_sums + (size_t)warp * cols;
+  Td* sm_add = reinterpret_cast<Td*>(sm_sums + (part_s != nullptr ? (size_t)kLnbWarps * cols : 0)) + (size_t)warp * cols;
   // Every lane copies the columns it will add itself, so no other lane waits for the copy. The row
   // is asked for one row ahead (after the previous row's values were read and used), which leaves
   // the whole first pass of the row to cover the latency without holding registers for it.
@@ -374,6 +378,7 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
     if (c < cols) {
       *reinterpret_cast<float4*>(sm_g + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       *reinterpret_cast<float4*>(sm_b + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (part_s != nullptr) *reinterpret_cast<float4*>(sm_s + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
   }
   const float inv_cols = 1.0f / (float)cols;
@@ -468,6 +473,24 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
           for (int j = 0; j < 4; ++j) o[j] += extra[j];
         }
         store_vec4<Td>(dr + c, o);
+        // the same values once more as bf16 (the operand of the next gradient GEMMs), and their
+        // column sums (the bias gradient of the layer that produced x): of the rounded values when
+        // the bf16 copy is written, as a sum over that copy would give
+        uint2 narrow;  // two packed conversions (the unpacked form runs at a quarter of their rate)
+        if (dx_cast != nullptr || (part_s != nullptr && sizeof(Td) == 2)) {
+          narrow.x = pack_bf16x2(o[0], o[1]);
+          narrow.y = pack_bf16x2(o[2], o[3]);
+        }
+        if (dx_cast != nullptr) __stcs(reinterpret_cast<uint2*>(dx_cast + row * (int64_t)cols + c), narrow);
+        if (part_s != nullptr) {
+          if (dx_cast != nullptr || sizeof(Td) == 2) {
+            o[0] = __uint_as_float(narrow.x << 16); o[1] = __uint_as_float(narrow.x & 0xffff0000u);
+            o[2] = __uint_as_float(narrow.y << 16); o[3] = __uint_as_float(narrow.y & 0xffff0000u);
+          }
+          float4 acc = *reinterpret_cast<const float4*>(sm_s + c);
+          acc.x += o[0]; acc.y += o[1]; acc.z += o[2]; acc.w += o[3];
+          *reinterpret_cast<float4*>(sm_s + c) = acc;
+        }
       }
     }
     if (dx_add != nullptr && next_row < rows) stage_add(next_row);
@@ -499,6 +522,12 @@ layer_norm_backward_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x, 
     }
     part_g[(int64_t)blockIdx.x * cols + c] = g;
     part_b[(int64_t)blockIdx.x * cols + c] = b;
+    if (part_s != nullptr) {
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kLnbWarps; ++w) t += sm_sums[(size_t)w * cols + c];
+      part_s[(int64_t)blockIdx.x * cols + c] = t;
+    }
   }
 }
 
@@ -560,7 +589,7 @@ __global__ void __launch_bounds__(kGenThreads)
 layer_norm_backward_dx_generic_kernel(const Tg* __restrict__ dy, const Tx* __restrict__ x,
                                       const float* __restrict__ mean, const float* __restrict__ rstd,
                                       const Tp* __restrict__ gamma, const Td* __restrict__ dx_add, Td* __restrict__ dx,
-                                      int64_t cols, int64_t dy_rs, int64_t x_rs) {
+                                      __nv_bfloat16* __restrict__ dx_cast, int64_t cols, int64_t dy_rs, int64_t x_rs) {
   __shared__ float red[kGenThreads / 32][2];
   const int64_t row = blockIdx.x;
   const float mu = mean[row], rs = rstd[row];
@@ -577,7 +606,9 @@ layer_norm_backward_dx_generic_kernel(const Tg* __restrict__ dy, const Tx* __res
     const float xh = (Elem<Tx>::to_f32(x[row * x_rs + c]) - mu) * rs;
     const float extra = dx_add != nullptr ? Elem<Td>::to_f32(dx_add[row * cols + c]) : 0.0f;
     // a separate rounding for the add: the sum equals (dx as it would be stored in fp32) + dx_add
-    dx[row * cols + c] = Elem<Td>::from_f32(__fadd_rn(__fmul_rn(rs, g - c1 - xh * c2), extra));
+    const float out = __fadd_rn(__fmul_rn(rs, g - c1 - xh * c2), extra);
+    dx[row * cols + c] = Elem<Td>::from_f32(out);
+    if (dx_cast != nullptr) dx_cast[row * cols + c] = __float2bfloat16_rn(out);
   }
 }
 
@@ -627,8 +658,9 @@ int64_t lnb_parts(int64_t rows, int64_t cols) {
 
 template <typename Tx, typename Tg, typename Tp, typename Td>
 int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* mean, const float* rstd,
-                                   const void* gamma, const void* dx_add, void* dx, void* dgamma, void* dbeta, float* ws,
-                                   int64_t rows, int64_t cols, int64_t dy_rs, int64_t x_rs, cudaStream_t stream) {
+                                   const void* gamma, const void* dx_add, void* dx, void* dgamma, void* dbeta,
+                                   void* dx_cast, void* dx_sum, int32_t dx_sum_dtype, float* ws, int64_t rows,
+                                   int64_t cols, int64_t dy_rs, int64_t x_rs, cudaStream_t stream) {
   const Tg* gp = static_cast<const Tg*>(dy);
   const Tx* xp = static_cast<const Tx*>(x);
   const Tp* wp = static_cast<const Tp*>(gamma);
@@ -637,13 +669,16 @@ int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* m
   const int64_t nparts = lnb_parts(rows, cols);
   float* part_g = ws;
   float* part_b = ws + nparts * cols;
-  const bool fast = lnb_fast(cols) && dy_rs % 4 == 0 && x_rs % 4 == 0 && aligned_to(dy, 4 * sizeof(Tg)) &&
+  float* part_s = dx_sum != nullptr ? ws + 2 * nparts * cols : nullptr;
+  __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(dx_cast);
+  const bool fast = lnb_fast(cols) && (dx_cast == nullptr || aligned_to(dx_cast, 8)) && dy_rs % 4 == 0 && x_rs % 4 == 0 && aligned_to(dy, 4 * sizeof(Tg)) &&
                     aligned_to(x, 4 * sizeof(Tx)) && aligned_to(dx, 4 * sizeof(Td)) &&
                     (dx_add == nullptr || aligned_to(dx_add, 4 * sizeof(Td)));
   if (fast) {
     const int chunks = (int)((cols + 127) / 128);
-    // at most 64 KiB of column sums and 32 KiB for the staged dx_add rows
-    const size_t smem = (size_t)kLnbWarps * (size_t)cols * (2 * sizeof(float) + (dx_add != nullptr ? sizeof(Td) : 0));
+    // at most 64 KiB of column sums, 32 KiB for those of dx and 32 KiB for the staged dx_add rows
+    const size_t smem = (size_t)kLnbWarps * (size_t)cols *
+                        (2 * sizeof(float) + (part_s != nullptr ? sizeof(float) : 0) + (dx_add != nullptr ? sizeof(Td) : 0));
 #define LNB(MAXC)                                                                                              \
   do {                                                                                                         \
     auto kernel = layer_norm_backward_kernel<Tx, Tg, Tp, Td, MAXC>;                                            \
@@ -653,14 +688,14 @@ int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* m
     cudaGetDevice(&dev);                                                                                       \
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {                                                              \
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
-                                           kLnbWarps * 128 * kLnbMaxChunks * (int)(2 * sizeof(float) + sizeof(Td))); \
+                                           kLnbWarps * 128 * kLnbMaxChunks * (int)(3 * sizeof(float) + sizeof(Td))); \
       if (e != cudaSuccess)                                                                                    \
         B200_FAIL(B200_ERR_CUDA, "layer_norm_backward: cannot opt in to shared memory: %s",                    \
                   cudaGetErrorString(e));                                                                      \
       attr_set[dev] = true;                                                                                    \
     }                                                                                                          \
-    kernel<<<(unsigned)nparts, kLnbWarps * 32, smem, stream>>>(gp, xp, mean, rstd, wp, ap, op, part_g, part_b,  \
-                                                               rows, (int)cols, dy_rs, x_rs);                  \
+    kernel<<<(unsigned)nparts, kLnbWarps * 32, smem, stream>>>(gp, xp, mean, rstd, wp, ap, op, cp, part_g,      \
+                                                               part_b, part_s, rows, (int)cols, dy_rs, x_rs);  \
   } while (0)
     if (chunks <= 2) LNB(2);
     else if (chunks <= 4) LNB(4);
@@ -673,13 +708,30 @@ int32_t launch_layer_norm_backward(const void* dy, const void* x, const float* m
   } else {
     B200_REQUIRE(rows <= INT32_MAX, B200_ERR_UNSUPPORTED, "layer_norm_backward: too many rows");
     layer_norm_backward_dx_generic_kernel<Tx, Tg, Tp, Td><<<(unsigned)rows, kGenThreads, 0, stream>>>(
-        gp, xp, mean, rstd, wp, ap, op, cols, dy_rs, x_rs);
+        gp, xp, mean, rstd, wp, ap, op, cp, cols, dy_rs, x_rs);
     B200_CHECK_LAUNCH("layer_norm_backward(dx)");
     const int64_t per_slab = (rows + nparts - 1) / nparts;
     const int64_t bx = (cols + 255) / 256;
     layer_norm_backward_params_generic_kernel<Tx, Tg><<<dim3((unsigned)bx, (unsigned)nparts), 256, 0, stream>>>(
         gp, xp, mean, rstd, part_g, part_b, rows, cols, dy_rs, x_rs, per_slab);
     B200_CHECK_LAUNCH("layer_norm_backward(params)");
+    if (part_s != nullptr) {  // column sums of what was just written (the bf16 copy when there is one)
+      if (cp != nullptr)
+        sum_rows_generic_kernel<__nv_bfloat16><<<dim3((unsigned)bx, (unsigned)nparts), 256, 0, stream>>>(
+            cp, part_s, rows, cols, cols, per_slab);
+      else
+        sum_rows_generic_kernel<Td><<<dim3((unsigned)bx, (unsigned)nparts), 256, 0, stream>>>(op, part_s, rows, cols, cols,
+                                                                                              per_slab);
+      B200_CHECK_LAUNCH("layer_norm_backward(dx sums)");
+    }
+  }
+  if (part_s != nullptr) {
+    const int32_t st = dx_sum_dtype == B200_F32
+                           ? launch_sum_partials<float>(part_s, dx_sum, nullptr, nullptr, nparts, cols, stream,
+                                                        "layer_norm_backward(dx sums)")
+                           : launch_sum_partials<__nv_bfloat16>(part_s, dx_sum, nullptr, nullptr, nparts, cols, stream,
+                                                                "layer_norm_backward(dx sums)");
+    if (st != B200_OK) return st;
   }
   return launch_sum_partials<Tp>(part_g, dgamma, part_b, dbeta, nparts, cols, stream, "layer_norm_backward(sums)");
 }
@@ -770,17 +822,22 @@ extern "C" B200_API int32_t b200_softmax_backward(const void* dy, const void* y,
 
 extern "C" B200_API size_t b200_layer_norm_backward_workspace_bytes(int64_t rows, int64_t cols) {
   if (rows <= 0 || cols <= 0) return 0;
-  return (size_t)lnb_parts(rows, cols) * (size_t)cols * 2 * sizeof(float);
+  return (size_t)lnb_parts(rows, cols) * (size_t)cols * 3 * sizeof(float);  // dgamma, dbeta and dx_sum partial rows
 }
 
 extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void* x, const float* mean,
                                                      const float* rstd, const void* gamma, const void* dx_add,
-                                                     void* dx, void* dgamma, void* dbeta, void* workspace,
-                                                     size_t workspace_bytes,
+                                                     void* dx, void* dgamma, void* dbeta, void* dx_cast, void* dx_sum,
+                                                     void* workspace, size_t workspace_bytes,
                                                      int64_t rows, int64_t cols, int64_t dy_row_stride,
                                                      int64_t x_row_stride, int32_t x_dtype, int32_t dy_dtype,
-                                                     int32_t param_dtype, int32_t dx_dtype, b200_stream_t stream_) {
+                                                     int32_t param_dtype, int32_t dx_dtype, int32_t dx_sum_dtype,
+                                                     b200_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(dx_cast == nullptr || dx_dtype == B200_F32, B200_ERR_UNSUPPORTED,
+               "layer_norm_backward: the bf16 copy of dx is offered for an fp32 dx");
+  B200_REQUIRE(dx_sum == nullptr || valid_dtype(dx_sum_dtype), B200_ERR_INVALID_ARG,
+               "layer_norm_backward: bad dx_sum dtype enum");
   B200_REQUIRE(rows >= 0 && cols >= 0, B200_ERR_INVALID_ARG, "layer_norm_backward: negative size");
   B200_REQUIRE(valid_dtype(x_dtype) && valid_dtype(dy_dtype) && valid_dtype(param_dtype) && valid_dtype(dx_dtype),
                B200_ERR_INVALID_ARG, "layer_norm_backward: bad dtype enum");
@@ -795,6 +852,8 @@ extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void*
       B200_FAIL(B200_ERR_CUDA, "layer_norm_backward: memset failed");
     if (dbeta != nullptr && cudaMemsetAsync(dbeta, 0, (size_t)cols * dtype_size(param_dtype), stream) != cudaSuccess)
       B200_FAIL(B200_ERR_CUDA, "layer_norm_backward: memset failed");
+    if (dx_sum != nullptr && cudaMemsetAsync(dx_sum, 0, (size_t)cols * dtype_size(dx_sum_dtype), stream) != cudaSuccess)
+      B200_FAIL(B200_ERR_CUDA, "layer_norm_backward: memset failed");
     return B200_OK;
   }
   B200_REQUIRE(dy != nullptr && x != nullptr && mean != nullptr && rstd != nullptr && dx != nullptr,
@@ -802,7 +861,8 @@ extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void*
   B200_REQUIRE((dy_row_stride >= cols && x_row_stride >= cols) || rows == 1, B200_ERR_INVALID_ARG,
                "layer_norm_backward: row stride smaller than cols");
   B200_REQUIRE(aligned_to(dy, dtype_size(dy_dtype)) && aligned_to(x, dtype_size(x_dtype)) &&
-                   aligned_to(dx, dtype_size(dx_dtype)) && aligned_to(dx_add, dtype_size(dx_dtype)),
+                   aligned_to(dx, dtype_size(dx_dtype)) && aligned_to(dx_add, dtype_size(dx_dtype)) &&
+                   aligned_to(dx_cast, 2) && (dx_sum == nullptr || aligned_to(dx_sum, dtype_size(dx_sum_dtype))),
                B200_ERR_ALIGNMENT, "layer_norm_backward: pointer not element aligned");
   const size_t need = b200_layer_norm_backward_workspace_bytes(rows, cols);
   B200_REQUIRE(workspace != nullptr && workspace_bytes >= need, B200_ERR_WORKSPACE,
@@ -810,8 +870,9 @@ extern "C" B200_API int32_t b200_layer_norm_backward(const void* dy, const void*
   B200_REQUIRE(aligned_to(workspace, 16), B200_ERR_ALIGNMENT, "layer_norm_backward: workspace not 16-byte aligned");
   float* ws = static_cast<float*>(workspace);
 #define LNB_CASE_D(TX, TG, TP, TD)                                                                                  \
-  return launch_layer_norm_backward<TX, TG, TP, TD>(dy, x, mean, rstd, gamma, dx_add, dx, dgamma, dbeta, ws, rows, cols, \
-                                                    dy_row_stride, x_row_stride, stream)
+  return launch_layer_norm_backward<TX, TG, TP, TD>(dy, x, mean, rstd, gamma, dx_add, dx, dgamma, dbeta, dx_cast,   \
+                                                    dx_sum, dx_sum_dtype, ws, rows, cols, dy_row_stride,             \
+                                                    x_row_stride, stream)
 #define LNB_CASE(TX, TG, TP) LNB_CASE_D(TX, TG, TP, TG)
   if (dx_dtype != dy_dtype) {  // fp32 x, bf16 dy, fp32 dx: the gradient of a bf16 consumer of an fp32 stream
     if (param_dtype == B200_F32) LNB_CASE_D(float, bf16, float, float);

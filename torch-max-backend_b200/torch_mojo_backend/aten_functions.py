@@ -269,7 +269,7 @@ def aten__softmax_backward_data(grad_output, output, dim, input_dtype):
 #   Tensor rstd, Tensor? weight, Tensor? bias, bool[3] output_mask) -> (Tensor, Tensor, Tensor)
 @map_to(aten.native_layer_norm_backward)
 def aten_native_layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask,
-                                    *, dx_add=None, dx_dtype=None):
+                                    *, dx_add=None, dx_dtype=None, want_cast=False, sum_dtype=None, sum_shape=None):
     _require_kernel_dtype("aten.native_layer_norm_backward", grad_out, input, weight)
     norm = 1
     for d in normalized_shape:
@@ -281,16 +281,25 @@ def aten_native_layer_norm_backward(grad_out, input, normalized_shape, mean, rst
         # no weight to carry the normalised extent: flatten the normalised dims ourselves
         input = input.reshape(*input.shape[: input.dim() - len(normalized_shape)], norm)
         grad_out = grad_out.reshape(input.shape)
-    dx, dgamma, dbeta = ops.layer_norm_backward(
-        grad_out, input, mean, rstd, w, bool(output_mask[1]) and weight is not None,
-        bool(output_mask[2]) and bias is not None, dx_add, dx_dtype,
-    )
+    want_w, want_b = bool(output_mask[1]) and weight is not None, bool(output_mask[2]) and bias is not None
+    extras = want_cast or sum_dtype is not None
+    if extras:
+        dx, dgamma, dbeta, dx_cast, dx_sum = ops.layer_norm_backward_with_copy(
+            grad_out, input, mean, rstd, w, want_w, want_b, dx_add, dx_dtype, want_cast, sum_dtype)
+    else:
+        dx, dgamma, dbeta = ops.layer_norm_backward(grad_out, input, mean, rstd, w, want_w, want_b, dx_add, dx_dtype)
     if dx.dtype != input.dtype:
         dx = dx.to(input.dtype)
     dx = dx.reshape(grad_out.shape) if output_mask[0] else None
     if dbeta is not None and bias is not None:
         dbeta = dbeta.reshape(bias.shape)
-    return dx, dgamma, dbeta
+    if not extras:
+        return dx, dgamma, dbeta
+    if dx_cast is not None:
+        dx_cast = dx_cast.reshape(grad_out.shape)
+    if dx_sum is not None and sum_shape is not None:
+        dx_sum = dx_sum.reshape(sum_shape)
+    return dx, dgamma, dbeta, dx_cast, dx_sum
 
 
 def _reduce_dims(input, dim, keepdim, op, dtype):
@@ -737,12 +746,16 @@ def fused_layer_norm_with_statistics(input, normalized_shape, weight, bias, eps,
 
 @_count_calls
 def fused_layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask,
-                              *, dx_add=None, dx_dtype=None):
+                              *, dx_add=None, dx_dtype=None, want_cast=False, sum_dtype=None, sum_shape=None):
     """native_layer_norm_backward whose grad_out was a bf16 tensor widened to fp32 just before it
     (`dx_dtype`: the kernel reads the bf16 tensor and writes fp32), and / or whose dx only fed an add
-    with the gradient of the residual branch (`dx_add`: added before dx is stored)."""
+    with the gradient of the residual branch (`dx_add`: added before dx is stored). With `want_cast` /
+    `sum_dtype` the result has two more entries: that sum as bf16 (the operand of the gradient GEMMs
+    of the layer before) and the sums of the bf16 tensor over its rows, shaped `sum_shape` (that
+    layer's bias gradient)."""
     return aten_native_layer_norm_backward(
-        grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask, dx_add=dx_add, dx_dtype=dx_dtype
+        grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask, dx_add=dx_add, dx_dtype=dx_dtype,
+        want_cast=want_cast, sum_dtype=sum_dtype, sum_shape=sum_shape,
     )
 
 

@@ -252,7 +252,7 @@ def _declare(dll: ctypes.CDLL) -> None:
     dll.b200_layer_norm_backward_workspace_bytes.argtypes = [i64, i64]
     dll.b200_layer_norm_backward.restype = i32
     dll.b200_layer_norm_backward.argtypes = [
-        vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, i64, i64, i64, i64, i32, i32, i32, i32, vp,
+        vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, i64, i64, i64, i64, i32, i32, i32, i32, i32, vp,
     ]
     dll.b200_sum_rows_workspace_bytes.restype = ctypes.c_size_t
     dll.b200_sum_rows_workspace_bytes.argtypes = [i64, i64, i32]

@@ -56,6 +56,11 @@ _lib.define(
     "layer_norm_backward(Tensor dy, Tensor x, Tensor mean, Tensor rstd, Tensor? weight, bool want_weight=True,"
     " bool want_bias=True, Tensor? dx_add=None, ScalarType? dx_dtype=None) -> (Tensor, Tensor?, Tensor?)"
 )
+_lib.define(
+    "layer_norm_backward_with_copy(Tensor dy, Tensor x, Tensor mean, Tensor rstd, Tensor? weight, bool want_weight=True,"
+    " bool want_bias=True, Tensor? dx_add=None, ScalarType? dx_dtype=None, bool want_cast=False,"
+    " ScalarType? sum_dtype=None) -> (Tensor, Tensor?, Tensor?, Tensor?, Tensor?)"
+)
 _lib.define("sum_rows(Tensor x, ScalarType? out_dtype=None) -> Tensor")
 _lib.define("argmax(Tensor x) -> Tensor")
 _lib.define("cat(Tensor[] tensors, int dim=0) -> Tensor")
@@ -301,6 +306,14 @@ def _softmax_backward_meta(dy, y, scale=1.0, out_dtype=None):
 def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None, dx_dtype=None):
     """dx (+ dx_add, the gradient that reaches x along a residual branch), dgamma, dbeta. dx_dtype
     defaults to dy's dtype; float32 is also accepted for a bfloat16 dy and a float32 x."""
+    return _layer_norm_backward_with_copy_cuda(dy, x, mean, rstd, weight, want_weight, want_bias, dx_add, dx_dtype)[:3]
+
+
+def _layer_norm_backward_with_copy_cuda(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None,
+                                        dx_dtype=None, want_cast=False, sum_dtype=None):
+    """The same launch with two more results: a bfloat16 copy of a float32 dx (`want_cast`) and the sums
+    of dx over the rows as [cols] in `sum_dtype` -- of the bfloat16 copy when there is one. They are what
+    the gradient GEMMs and the bias gradient of the layer that produced x read."""
     device = native.require_cuda("layer_norm_backward", dy, x, mean, rstd, weight, dx_add)
     if dy.shape != x.shape:
         raise RuntimeError(f"layer_norm_backward: dy {tuple(dy.shape)} and x {tuple(x.shape)} differ")
@@ -325,6 +338,10 @@ def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_
     wc = None if weight is None else weight.reshape(-1).contiguous()
     dx = torch.empty(x.shape, dtype=dx_dtype, device=device)
     extra = None if dx_add is None else dx_add.contiguous()
+    if want_cast and dx_dtype != torch.float32:
+        raise RuntimeError(f"layer_norm_backward: the bfloat16 copy is offered for a float32 dx, not {dx_dtype}")
+    dx_cast = torch.empty(x.shape, dtype=torch.bfloat16, device=device) if want_cast else None
+    dx_sum = torch.empty(cols, dtype=sum_dtype, device=device) if sum_dtype is not None else None
     dgamma = torch.empty(cols, dtype=param_dtype, device=device) if want_weight else None
     dbeta = torch.empty(cols, dtype=param_dtype, device=device) if want_bias else None
     lib = native.lib()
@@ -334,16 +351,26 @@ def _layer_norm_backward_cuda(dy, x, mean, rstd, weight, want_weight=True, want_
     with torch.cuda.device(device):
         status = lib.b200_layer_norm_backward(
             g2.data_ptr(), x2.data_ptr(), mean_c.data_ptr(), rstd_c.data_ptr(), _ptr(wc), _ptr(extra), dx.data_ptr(),
-            _ptr(dgamma), _ptr(dbeta), ws.data_ptr(), ws_bytes, rows, cols, g2.stride(0) if rows > 1 else cols,
-            x2.stride(0) if rows > 1 else cols, native.dtype_enum(x.dtype), native.dtype_enum(dy.dtype),
-            native.dtype_enum(param_dtype), native.dtype_enum(dx_dtype), native.current_stream(device),
+            _ptr(dgamma), _ptr(dbeta), _ptr(dx_cast), _ptr(dx_sum), ws.data_ptr(), ws_bytes, rows, cols,
+            g2.stride(0) if rows > 1 else cols, x2.stride(0) if rows > 1 else cols, native.dtype_enum(x.dtype),
+            native.dtype_enum(dy.dtype), native.dtype_enum(param_dtype), native.dtype_enum(dx_dtype),
+            native.dtype_enum(sum_dtype) if sum_dtype is not None else 0, native.current_stream(device),
         )
     native.check("layer_norm_backward", status)
-    _launched(device, start, "layer_norm_backward", 0.0, _nbytes(g2, x2, dx) + (_nbytes(extra) if extra is not None else 0))
+    _launched(device, start, "layer_norm_backward", 0.0, _nbytes(g2, x2, dx, extra, dx_cast))
     if weight is not None and dgamma is not None:
         dgamma = dgamma.reshape(weight.shape)
         dbeta = dbeta.reshape(weight.shape) if dbeta is not None else None
-    return dx, dgamma, dbeta
+    return dx, dgamma, dbeta, dx_cast, dx_sum
+
+
+def _layer_norm_backward_with_copy_meta(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None,
+                                        dx_dtype=None, want_cast=False, sum_dtype=None):
+    cols = weight.numel() if weight is not None else x.shape[-1]
+    return _layer_norm_backward_meta(dy, x, mean, rstd, weight, want_weight, want_bias, dx_add, dx_dtype) + (
+        torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if want_cast else None,
+        torch.empty(cols, dtype=sum_dtype, device=x.device) if sum_dtype is not None else None,
+    )
 
 
 def _layer_norm_backward_meta(dy, x, mean, rstd, weight, want_weight=True, want_bias=True, dx_add=None, dx_dtype=None):
@@ -822,6 +849,7 @@ for _name, _cuda, _meta in (
     ("gelu_backward", _gelu_backward_cuda, _gelu_backward_meta),
     ("softmax_backward", _softmax_backward_cuda, _softmax_backward_meta),
     ("layer_norm_backward", _layer_norm_backward_cuda, _layer_norm_backward_meta),
+    ("layer_norm_backward_with_copy", _layer_norm_backward_with_copy_cuda, _layer_norm_backward_with_copy_meta),
     ("sum_rows", _sum_rows_cuda, _sum_rows_meta),
     ("gemm", _gemm_cuda, _gemm_meta),
     ("sdpa", _sdpa_cuda, _sdpa_meta),
@@ -843,6 +871,7 @@ reduce = torch.ops.b200.reduce
 gelu_backward = torch.ops.b200.gelu_backward
 softmax_backward = torch.ops.b200.softmax_backward
 layer_norm_backward = torch.ops.b200.layer_norm_backward
+layer_norm_backward_with_copy = torch.ops.b200.layer_norm_backward_with_copy
 sum_rows = torch.ops.b200.sum_rows
 gemm = torch.ops.b200.gemm
 sdpa = torch.ops.b200.sdpa

@@ -224,14 +224,34 @@ def _fuse_layer_norm_backward(graph) -> int:
             ):
                 kwargs["dx_add"] = other
                 target = add
+        # What reads the fp32 sum next is `_to_copy(bf16) -> view [rows, C] -> {mm, t -> mm, sum([0])}`, the
+        # gradient GEMMs and the bias gradient of the layer before: the bf16 tensor leaves the same
+        # launch. (The kernel can also emit that tensor's column sums, the bias gradient; the extra
+        # shared-memory accumulator made the launch 21 us slower at [8192, 1600] where the separate
+        # column-sum kernel over the L2-resident bf16 tensor takes 10 us, so the sum stays a node.)
+        total = target if target is not None else dx
+        cast = None
+        if total is not None and kwargs:
+            casts = [u for u in total.users if _plain_cast(u) == torch.bfloat16 and u.args[0] is total]
+            if len(casts) == 1 and _static_tensor(casts[0]) and tuple(_val(casts[0]).shape) == tuple(vx.shape):
+                cast = casts[0]
         if not kwargs:
             continue
+        if cast is not None:
+            kwargs["want_cast"] = True
         with graph.inserting_after(node):
             new = graph.call_function(af.fused_layer_norm_backward, args=(grad,) + tuple(node.args[1:]), kwargs=kwargs)
         new.meta = dict(node.meta)
         node.replace_all_uses_with(new)
         if target is not None:
             target.replace_all_uses_with(dx)
+        if cast is not None:
+            old_val = _val(node)
+            new.meta["val"] = tuple(old_val) + (_val(cast), None)
+            with graph.inserting_after(dx):
+                narrow = graph.call_function(operator.getitem, args=(new, 3))
+            narrow.meta = dict(cast.meta)
+            cast.replace_all_uses_with(narrow)
         count += 1
     return count
 
