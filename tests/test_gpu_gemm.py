@@ -327,7 +327,10 @@ def test_small_m_split_k_route(ops, m, k, n, b_layout):
     g = ops.fill_gemm_args(ag, b_gpu, bias.cuda(), res.cuda(), c, 1.0, 1.0, 1, 0)
     auto = native.lib().b200_gemm_route(ctypes.byref(g))
     need = native.lib().b200_gemm_workspace_bytes(ctypes.byref(g))
-    assert (auto == ROUTE_SKINNY) == (need > 0)
+    # up to eight rows against a K-contiguous weight: partial sums, their sum and the epilogue are one
+    # launch (the slices of a column block form a cluster) and nothing is written to scratch
+    one_launch = auto == ROUTE_SKINNY and m <= 8 and b_layout == "nk"
+    assert (auto == ROUTE_SKINNY and not one_launch) == (need > 0)
     want = torch.nn.functional.gelu(a.float() @ b_cpu.float() + bias.float(), approximate="tanh") + res
     y = ops.gemm(ag, b_gpu, bias.cuda(), res.cuda(), 1.0, 1.0, 1, torch.float32)
     assert_parity(y, want, bf16=False)
@@ -338,7 +341,7 @@ def test_small_m_split_k_route(ops, m, k, n, b_layout):
         assert_parity(y, y_tc, bf16=False)
         # a missing workspace is an error, not a silent reroute
         st = native.lib().b200_gemm(ctypes.byref(g), None, 0, None)
-        assert st == -4
+        assert st == (0 if one_launch else -4)
 
 
 def test_auto_route_choices(ops):

@@ -28,6 +28,8 @@ const char* gemm_gemv_ineligible(const b200_gemm_args& g);
 int gemm_gemv_slices(const b200_gemm_args& g);
 size_t gemm_gemv_scratch_bytes(const b200_gemm_args& g);
 int32_t launch_gemm_gemv_partials(const b200_gemm_args& g, float* partial, int slices, cudaStream_t stream);
+bool gemm_gemv_one_launch(const b200_gemm_args& g);
+int32_t launch_gemm_gemv_one_launch(const b200_gemm_args& g, cudaStream_t stream);
 
 // fp32 operands on the tensor cores: each operand is split into bf16 halves (x = hi + lo), written
 // K-major into scratch, and one tensor-core launch accumulates a_hi b_lo + a_lo b_hi + a_hi b_hi.

@@ -110,6 +110,8 @@ size_t gemm_skinny_scratch_bytes(const b200_gemm_args& g) {
 
 int32_t launch_gemm_skinny(const b200_gemm_args& g, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
   const bool gemv = gemm_gemv_ineligible(g) == nullptr;
+  // up to eight rows against a K-contiguous weight: partial sums, their sum and the epilogue in one launch
+  if (gemv && gemm_gemv_one_launch(g)) return launch_gemm_gemv_one_launch(g, stream);
   const int splits = gemv ? gemm_gemv_slices(g) : gemm_skinny_splits(g);
   B200_REQUIRE(gemv || splits >= 2, B200_ERR_UNSUPPORTED, "gemm(skinny): no K split for these arguments");
   const size_t need = (size_t)splits * (size_t)g.m * (size_t)g.n * sizeof(float);
