@@ -190,3 +190,60 @@ def test_attention_backward_composition_matches_autograd(training_stand_ins, cau
         torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)
     if with_bias:
         torch.testing.assert_close(dbias, want[3], rtol=1e-4, atol=1e-5)
+
+
+def test_cat_of_slices_that_tile_one_buffer_is_a_view():
+    """`aten_cat` returns the common buffer when its inputs tile it exactly and in order (the dq | dk | dv
+    slices of a packed attention gradient); anything else takes the copying path."""
+    packed = torch.arange(2 * 8 * 3 * 2 * 4, dtype=torch.float32).reshape(2, 8, 3, 2, 4).clone()
+    parts = [packed[:, :, i].reshape(2, 8, 8) for i in range(3)]  # [B, T, H * D] views, row pitch 3 * H * D
+    assert all(p._base is packed for p in parts)
+    whole = af._tiles_of_one_buffer(parts, 2)
+    assert whole is not None and whole.data_ptr() == packed.data_ptr() and whole.is_contiguous()
+    assert torch.equal(whole, torch.cat(parts, 2))
+    assert torch.equal(af._tiles_of_one_buffer(parts, -1), whole)
+    # wrong order, a subset, another dim, a different base, tensors that own their memory
+    assert af._tiles_of_one_buffer([parts[1], parts[0], parts[2]], 2) is None
+    assert af._tiles_of_one_buffer(parts[:2], 2) is None
+    assert af._tiles_of_one_buffer(parts, 1) is None
+    other = torch.zeros(2, 8, 3, 2, 4)
+    assert af._tiles_of_one_buffer([parts[0], other[:, :, 1].reshape(2, 8, 8), parts[2]], 2) is None
+    assert af._tiles_of_one_buffer([p.clone() for p in parts], 2) is None
+    # a buffer with room after the slices is not "exactly tiled"
+    roomy = torch.zeros(2, 8, 4, 2, 4)
+    assert af._tiles_of_one_buffer([roomy[:, :, i].reshape(2, 8, 8) for i in range(3)], 2) is None
+
+
+def test_packed_attention_gradient_buffers():
+    from torch_mojo_backend import ops
+
+    dq, dk, dv = ops._sdpa_gradient_buffers(2, 3, 16, 16, 64, torch.bfloat16, "cpu")
+    assert dq._base is dk._base is dv._base and dq._base.shape == (2, 16, 3, 3, 64)
+    assert dq.shape == dk.shape == dv.shape == (2, 3, 16, 64)
+    assert dq.stride() == (16 * 3 * 3 * 64, 64, 3 * 3 * 64, 1)
+    assert dk.storage_offset() - dq.storage_offset() == 3 * 64
+    # the views the backward graph builds from them concatenate back to the buffer
+    flat = [t.transpose(1, 2).reshape(2, 16, 3 * 64) for t in (dq, dk, dv)]
+    assert af._tiles_of_one_buffer(flat, 2).data_ptr() == dq._base.data_ptr()
+    # cross attention: separate buffers in the same [B, T, H, D] memory order
+    dq, dk, dv = ops._sdpa_gradient_buffers(2, 3, 16, 24, 64, torch.bfloat16, "cpu")
+    assert dq._base is not dk._base and dk.shape == (2, 3, 24, 64) and dk.transpose(1, 2).is_contiguous()
+
+
+def test_repitched_operand_is_kept_on_its_base_tensor():
+    from torch_mojo_backend import ops
+
+    dl = torch.randn(4096, 1031).to(torch.bfloat16)  # 2062-byte pitch: not a multiple of 16
+    view = dl[:]                                      # what a graph's view node hands to the GEMM
+    a = ops._tma_pitch(view)
+    assert a.stride(0) % 8 == 0 and torch.equal(a, dl)
+    assert ops._tma_pitch(dl[:]) is a, "a second view of the same tensor shares the copy"
+    at = ops._tma_pitch(dl[:].t())                    # the weight gradient reads the transposed view
+    assert at.shape == (1031, 4096) and at.data_ptr() == a.data_ptr()
+    dl.add_(1.0)                                      # written to: the copy is stale and is made again
+    b = ops._tma_pitch(dl[:])
+    assert b is not a and torch.equal(b, dl)
+    small = torch.randn(64, 1031).to(torch.bfloat16)
+    assert ops._tma_pitch(small) is small             # too small to be worth a copy
+    aligned = torch.randn(4096, 1024).to(torch.bfloat16)
+    assert ops._tma_pitch(aligned) is aligned
