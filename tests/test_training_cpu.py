@@ -245,5 +245,9 @@ def test_repitched_operand_is_kept_on_its_base_tensor():
     assert b is not a and torch.equal(b, dl)
     small = torch.randn(64, 1031).to(torch.bfloat16)
     assert ops._tma_pitch(small) is small             # too small to be worth a copy
+    with torch.inference_mode():                      # no version counter to tell a write by: copied every time
+        frozen = torch.randn(4096, 1031).to(torch.bfloat16)
+        first, second = ops._tma_pitch(frozen), ops._tma_pitch(frozen)
+        assert first is not second and torch.equal(first, frozen) and torch.equal(second, frozen)
     aligned = torch.randn(4096, 1024).to(torch.bfloat16)
     assert ops._tma_pitch(aligned) is aligned

@@ -493,17 +493,21 @@ def _tma_pitch(t):
         # The copy is kept on the tensor the operand is a view of, for as long as that tensor lives and
         # is not written to: the data and the weight gradient of a layer read the same gradient.
         root = t._base if t._base is not None else t
-        key = (t.storage_offset(), tuple(t.shape), t.stride(), root._version)
-        kept = getattr(root, "_b200_padded_pitch", None)
+        try:
+            key = (t.storage_offset(), tuple(t.shape), t.stride(), root._version)
+        except RuntimeError:  # an inference tensor has no version counter: nothing to tell a write by
+            key = None
+        kept = getattr(root, "_b200_padded_pitch", None) if key is not None else None
         if kept is not None and kept[0] == key:
             return kept[1]
         rows, cols = t.shape
         padded = torch.empty((rows, (cols + 7) // 8 * 8), dtype=t.dtype, device=t.device)[:, :cols]
         padded.copy_(t)
-        try:
-            root._b200_padded_pitch = (key, padded)
-        except (AttributeError, RuntimeError):  # a tensor subclass without attributes: copy again next time
-            pass
+        if key is not None:
+            try:
+                root._b200_padded_pitch = (key, padded)
+            except (AttributeError, RuntimeError):  # a tensor subclass without attributes: copy again next time
+                pass
         return padded
     if t.stride(0) == 1 and t.stride(1) % 8 != 0:
         return _tma_pitch(t.t()).t()
