@@ -30,7 +30,8 @@ extern "C" {
 #define B200_API
 #endif
 
-#define B200_ABI_VERSION 1
+/* 2: b200_layer_norm_backward takes dx_add, dx_cast, dx_sum and dx_sum_dtype. */
+#define B200_ABI_VERSION 2
 
 /* status codes */
 #define B200_OK 0

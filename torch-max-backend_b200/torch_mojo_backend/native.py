@@ -17,7 +17,7 @@ from pathlib import Path
 
 import torch
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 F32 = 0
 BF16 = 1
