@@ -47,17 +47,17 @@ def test_map_to_single_overload_and_type_check(monkeypatch):
     monkeypatch.setattr(af, "DECOMPOSITION_TABLE", table)
     mapping = dict(MAPPING_TORCH_ATEN_TO_MOJO)
     monkeypatch.setattr(af, "MAPPING_TORCH_ATEN_TO_MOJO", mapping)
-    assert aten.addcmul.default in table and aten.addcmul.out in table
+    assert aten.lerp.Scalar in table and aten.lerp.Tensor in table
 
-    @af.map_to(aten.addcmul.default)
-    def aten_addcmul(x, a, b, *, value=1):
-        return x + value * a * b
+    @af.map_to(aten.lerp.Scalar)
+    def aten_lerp(x, end, weight):
+        return x + weight * (end - x)
 
-    assert aten.addcmul.default not in table and aten.addcmul.out in table
-    assert mapping[aten.addcmul.default] is aten_addcmul
-    assert aten_addcmul.call_count == 0  # test runs instrument lowerings with call counters
+    assert aten.lerp.Scalar not in table and aten.lerp.Tensor in table
+    assert mapping[aten.lerp.Scalar] is aten_lerp
+    assert aten_lerp.call_count == 0  # test runs instrument lowerings with call counters
     with pytest.raises(TypeError):
-        af.map_to("aten.addcmul")(lambda x: x)
+        af.map_to("aten.lerp")(lambda x: x)
 
 
 def test_error_message_op_not_supported(monkeypatch):
@@ -239,3 +239,42 @@ def test_hot_ops_refuse_floating_dtypes_without_a_kernel(dtype):
     ):
         with pytest.raises(NotImplementedError, match="not supported by the b200 kernels"):
             call()
+
+
+def test_glue_targets_of_the_reference_registry_run_through_the_backend():
+    """Elementwise, fill, allocation and multi-tensor (optimizer) targets that the reference's registry
+    names beside the hot ops: shape glue here (stock torch ops on any device), so a graph that uses
+    them compiles instead of raising. Checked against eager on the CPU."""
+    from torch_mojo_backend.testing import check_functions_are_equivalent
+
+    def elementwise(x, y):
+        a = torch.cos(x) + torch.sin(x) * torch.tan(x * 0.1) + torch.cosh(x * 0.1) - torch.sinh(x * 0.1)
+        b = torch.acos(torch.clamp(x * 0.1, -0.9, 0.9)) + torch.asinh(x) + torch.atanh(torch.clamp(y * 0.1, -0.9, 0.9))
+        c = torch.floor(x) + torch.ceil(y) + torch.sign(x) + torch.log1p(x.abs()) + torch.remainder(x, 1.5)
+        return a + b + c, torch.isnan(x / y), torch.logical_xor(x > 0, y > 0), (x > 0).int() ^ (y > 0).int()
+
+    def fills_and_pads(x, y):
+        padded = torch.nn.functional.pad(x, (1, 2, 0, 1), value=-1.0)
+        filled = torch.full_like(x, 0.0).fill_(3.0)
+        scattered = torch.select_scatter(x, y[0], 0, 1)
+        return padded, filled + torch.addcmul(x, x, y, value=0.5) + torch.addcdiv(x, x, y.abs() + 1.0, value=2.0), scattered
+
+    def reductions(x, y):
+        return x.var(dim=1), x.argmin(dim=1), torch.isin(x.int(), torch.tensor([0, 1, 2]))
+
+    def optimizer_like(p0, p1, g0, g1):
+        # what a compiled multi-tensor optimizer step is made of
+        avg = torch._foreach_mul([g0, g1], 0.9)
+        sq = torch._foreach_addcmul([p0.abs(), p1.abs()], [g0, g1], [g0, g1], 0.1)
+        denom = torch._foreach_sqrt(torch._foreach_add(sq, 1e-8))
+        step = torch._foreach_addcdiv([p0, p1], avg, denom, -0.01)
+        step = torch._foreach_sub(step, torch._foreach_div(torch._foreach_neg(avg), 4.0))
+        return tuple(torch._foreach_pow(torch._foreach_reciprocal(torch._foreach_add(torch._foreach_mul(step, step), 1.0)), 2.0))
+
+    g = torch.Generator().manual_seed(5)
+    x, y = torch.randn(4, 6, generator=g), torch.randn(4, 6, generator=g)
+    for fn, inputs in ((elementwise, [x, y]), (fills_and_pads, [x, y]), (reductions, [x, y]),
+                       (optimizer_like, [x, y, x * 0.5, y * 0.5])):
+        torch._dynamo.reset()
+        compiled = torch.compile(fn, backend=mojo_backend, fullgraph=True)
+        check_functions_are_equivalent(fn, None, inputs, fn_compiled=compiled, rtol=1e-6, atol=1e-6)

@@ -932,6 +932,15 @@ _GLUE_OPS = [
     # loss and embedding gradients of a training step
     aten._log_softmax, aten._log_softmax_backward_data, aten.nll_loss_forward, aten.nll_loss_backward,
     aten.scatter, aten.scatter_add, aten.index_put, aten.embedding_dense_backward, aten.new_zeros,
+    # the rest of the elementwise, fill and allocation targets the reference's registry names
+    # (torch_mojo_backend/aten_functions.py: acos 781 ... var 3379); none is on the hot path
+    aten.acos, aten.asinh, aten.atanh, aten.ceil, aten.floor, aten.cos, aten.cosh, aten.sin, aten.sinh, aten.tan,
+    aten.sign, aten.isnan, aten.log1p, aten.remainder, aten.logical_xor, aten.bitwise_xor, aten.addcmul,
+    aten.addcdiv, aten.fill, aten.select_scatter, aten.empty_strided, aten.empty_permuted, aten.constant_pad_nd,
+    aten.argmin, aten.var, aten.isin,
+    # an optimizer step compiled with the backend (the reference maps the same multi-tensor ops)
+    aten._foreach_add, aten._foreach_sub, aten._foreach_mul, aten._foreach_div, aten._foreach_neg,
+    aten._foreach_pow, aten._foreach_sqrt, aten._foreach_reciprocal, aten._foreach_addcmul, aten._foreach_addcdiv,
 ]
 
 for _packet in _GLUE_OPS:
